@@ -1,0 +1,53 @@
+"""Helpers for the GPU tests: torch owns device memory and streams; every
+computation goes through the C ABI of libtnsr_b200.so."""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from tnsr_b200 import _native
+
+F32, BF16 = 0, 1
+
+
+def lib():
+    return _native.lib()
+
+
+def stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t.to(dtype) if dtype is not None else t
+
+
+def ok(code):
+    assert code == 0, f"{_native.STATUS.get(code, code)}: {_native.last_error(None)}"
+
+
+def bf16_round(a):
+    """numpy f32 -> nearest bf16 value, as f32 (torch's rounding is RNE too)."""
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(torch.bfloat16).to(torch.float32).numpy()
+
+
+def rel_err(actual, expected):
+    actual = np.asarray(actual, dtype=np.float64)
+    expected = np.asarray(expected, dtype=np.float64)
+    return float(np.max(np.abs(actual - expected)) / max(np.max(np.abs(expected)), 1e-30))
+
+
+def gemm_bf16(a, bt, bias=None, residual=None, activation=-1, out_dtype=F32):
+    """a [m,k] bf16 cuda, bt [n,k] bf16 cuda -> out [m,n]."""
+    m, k = a.shape
+    n = bt.shape[0]
+    out = torch.empty((m, n), dtype=torch.float32 if out_dtype == F32 else torch.bfloat16, device="cuda")
+    ok(lib().tnsr_b200_gemm_bf16(ptr(a), ptr(bt), ptr(bias), ptr(residual), ptr(out), m, n, k, activation, out_dtype,
+                                 stream()))
+    torch.cuda.synchronize()
+    return out

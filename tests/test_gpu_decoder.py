@@ -1,0 +1,267 @@
+"""tnsr's tests/kv_cache.rs, CUDA half, and the configuration-level parity
+checks: the B200 session behind the shared GptDecoder wrapper against the CPU
+checker on the same weights and token ids."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+from tests.gpu_util import bf16_round, rel_err  # noqa: E402
+from tests.helpers import close, cpu_decoder, cpu_forward, cpu_generate, kv_model  # noqa: E402
+from tests.test_kv_cache_host import chunks_match, validate_inputs_and_weights  # noqa: E402
+from tests.workloads import (config0_model, config0_prompt, kv_test_tokens, normal_model_arrays,  # noqa: E402
+                             set_model_arrays)
+from tnsr_b200.nn import (Backend, Gpt, GptAttentionPrecision, GptConfig, GptDecoder, GptDecoderOptions,  # noqa: E402
+                          GptPrefillMode, model_parameters)
+from tnsr_b200.session import B200Session  # noqa: E402
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def gpu_decoder(model, batch, capacity=None, options=GptDecoderOptions()):
+    capacity = model.config().max_sequence_length if capacity is None else capacity
+    return model.decoder_with_options(Backend.Ptx, batch, capacity, options)
+
+
+def test_cuda_kv_cache_matches_full_decode_for_batches_and_chunks():
+    """tests/kv_cache.rs:92-98 (tolerance 2e-4 absolute, :19-27)."""
+    assert chunks_match(gpu_decoder, cpu_forward, tol=2e-4)
+
+
+def test_cuda_kv_cache_reset_refreshes_weights_and_reuses_programs():
+    """tests/kv_cache.rs:100-106."""
+    validate_inputs_and_weights(gpu_decoder, cpu_forward)
+
+
+def test_cuda_cached_generation_matches_sliding_context():
+    """tests/kv_cache.rs:170-185."""
+    model = kv_model(3)
+    prompt = [365, 2, 3, 4]
+    assert model.generate_cached(Backend.Ptx, prompt, 6) == cpu_generate(model, prompt, 6)
+    assert kv_model(1).generate_cached(Backend.Cuda, [365, 3], 4) == cpu_generate(kv_model(1), [365, 3], 4)
+
+
+def test_cuda_kv_cache_crosses_scan_tiles_with_one_session():
+    """tests/kv_cache.rs:198-243: 140 single-token steps, batch 2, twice with reset."""
+    model = kv_model(140)
+    batch = 2
+    rows = kv_test_tokens(batch, 140)
+    decoder = gpu_decoder(model, batch)
+    checked = {0, 1, 30, 31, 32, 33, 62, 63, 64, 65, 126, 127, 128, 129, 139}
+    expected = {p: cpu_forward(model, [r[:p + 1] for r in rows])[:, p, :] for p in checked}
+    for _ in range(2):
+        decoder.reset()
+        for position in range(140):
+            actual = decoder.decode([r[position] for r in rows])
+            if position in checked:
+                close(actual, expected[position])
+
+
+def test_strict_session_cache_rows_match_checker():
+    """The appended K/V rows (src/nn/kv_cache.rs:347-361) and untouched slots."""
+    model = kv_model(12)
+    rows = kv_test_tokens(2, 9)
+    gpu, cpu = gpu_decoder(model, 2), cpu_decoder(model, 2)
+    for lo, hi in ((0, 4), (4, 5), (5, 9)):
+        tokens = [t for r in rows for t in r[lo:hi]]
+        close(gpu.decode(tokens), cpu.decode(tokens))
+    for index in range(4):
+        a, b = gpu._backend.read_cache(index), cpu._backend.read_cache(index)
+        assert np.max(np.abs(a - b)) <= 2e-6
+        assert np.all(a[:, 9:] == 0)
+
+
+@pytest.mark.parametrize("width", [8, 66, 128, 258])
+def test_bf16_cuda_cache_matches_cpu_for_prefill_decode_and_reset(width):
+    """tests/kv_cache.rs:283-333: GptAttentionPrecision::Bf16 on f32 weights, tolerance max|expected|/128."""
+    model = Gpt(GptConfig(vocab_size=32, max_sequence_length=160, embed_dim=width, num_heads=2,
+                          feed_forward_dim=width * 2, num_layers=2, layer_norm_epsilon=1e-5))
+    for prefill in (GptPrefillMode.Scalar, GptPrefillMode.Auto):
+        options = GptDecoderOptions(attention_precision=GptAttentionPrecision.Bf16, prefill=prefill)
+        cpu, gpu = cpu_decoder(model, 2, 160, options), gpu_decoder(model, 2, 160, options)
+        for _ in range(2):
+            sizes = [17, 1, 17, 3, 16, 75, 1] if width == 8 else [17, 1, 17, 3, 16]
+            for size in sizes:
+                tokens = [(i * 17 + cpu.len() + 3) % 32 for i in range(2 * size)]
+                expected = cpu.decode(tokens)
+                actual = gpu.decode(tokens)
+                scale = max(1.0, float(np.max(np.abs(expected))))
+                assert np.all(np.isfinite(actual))
+                assert np.max(np.abs(actual - expected)) <= scale / 128
+            gpu.reset()
+            cpu.reset()
+
+
+@pytest.mark.parametrize("activation", ["relu", "gelu"])
+def test_config0_greedy_tokens_bit_exact_and_logits_within_1e3(activation, oracle):
+    """Configuration 0: vocab 96, d 128, 4 layers, 4 heads, FFN 512, ctx 128, f32;
+    prompt 16 + 64 greedy steps.  Token ids must equal the CPU executor's
+    (fixture made by tests/golden/make_golden.py); logits within 1e-3 relative."""
+    with open(os.path.join(GOLDEN, "config0_greedy.json")) as f:
+        golden = json.load(f)[activation]
+    cfg, arrays = config0_model(activation)
+    model = Gpt(cfg)
+    set_model_arrays(model, arrays)
+    prompt = [int(t) for t in config0_prompt()]
+    assert prompt == golden["prompt"]
+    tokens = model.generate_cached(Backend.Cuda, prompt, 64)
+    assert tokens == golden["tokens"]
+    # logits of every step against the checker run on the same ids
+    m = oracle.OracleModel(cfg.vocab_size, cfg.max_sequence_length, cfg.embed_dim, cfg.num_heads,
+                           cfg.feed_forward_dim, cfg.num_layers, cfg.layer_norm_epsilon, activation)
+    m.set_params(arrays)
+    full = m.forward(np.asarray(tokens[:-1], np.uint32)[None])[0]          # [79, 96]
+    decoder = model.decoder(Backend.Cuda, 1)
+    got = [decoder.decode(prompt).reshape(16, 96)]
+    for t in tokens[16:-1]:
+        got.append(decoder.decode([t]).reshape(1, 96))
+    got = np.concatenate(got)
+    assert rel_err(got, full) <= 1e-3
+    assert np.array_equal(full[-1].view(np.uint32), np.asarray(golden["last_logits_bits"], np.uint32))
+    margins = np.sort(full[15:], axis=1)
+    print(f"config0[{activation}] max rel err {rel_err(got, full):.3e}; min top1-top2 margin "
+          f"{float((margins[:, -1] - margins[:, -2]).min()):.4f}")
+
+
+def small_bf16_model(activation="swiglu", d=128, heads=2, f=256, vocab=512, ctx=96, layers=2, seed=21, bias_std=0.02):
+    cfg = GptConfig(vocab_size=vocab, max_sequence_length=ctx, embed_dim=d, num_heads=heads, feed_forward_dim=f,
+                    num_layers=layers, layer_norm_epsilon=1e-5, activation=activation, weight_dtype="bf16")
+    arrays = normal_model_arrays(cfg, seed=seed, std=0.05, bias_std=bias_std)
+    # the checker runs the f32 arithmetic on the bf16-rounded matrices (vectors stay f32)
+    rounded = [bf16_round(a) if a.ndim == 2 else a for a in arrays]
+    model = Gpt(cfg)
+    set_model_arrays(model, arrays)
+    return cfg, model, rounded
+
+
+def oracle_model(oracle, cfg, arrays):
+    m = oracle.OracleModel(cfg.vocab_size, cfg.max_sequence_length, cfg.embed_dim, cfg.num_heads, cfg.feed_forward_dim,
+                           cfg.num_layers, cfg.layer_norm_epsilon, cfg.activation)
+    m.set_params(arrays)
+    return m
+
+
+@pytest.mark.parametrize("engine", [1, 0])
+@pytest.mark.parametrize("activation,d,heads,f", [("swiglu", 128, 2, 256), ("relu", 128, 2, 256), ("gelu", 96, 3, 104),
+                                                  ("swiglu", 64, 2, 40), ("swiglu", 72, 3, 36)])
+def test_bf16_session_matches_checker_within_2e2(oracle, activation, d, heads, f, engine):
+    """bf16 tensor-core path vs the f32 checker on bf16-rounded weights: <= 2e-2 relative."""
+    from tnsr_b200 import _native
+    cfg, model, rounded = small_bf16_model(activation, d, heads, f)
+    m = oracle_model(oracle, cfg, rounded)
+    rng = np.random.default_rng(5)
+    batch, total = 3, 40
+    ids = rng.integers(0, cfg.vocab_size, size=(batch, total)).astype(np.uint32)
+    full = m.forward(ids)
+    try:
+        _native.lib().tnsr_b200_set_gemm_engine(engine)
+        decoder = model.decoder(Backend.Cuda, batch)
+        position = 0
+        for chunk in (17, 1, 1, 5, 16):
+            tokens = ids[:, position:position + chunk].reshape(-1).tolist()
+            got = decoder.decode(tokens).reshape(batch, chunk, cfg.vocab_size)
+            assert np.all(np.isfinite(got))
+            assert rel_err(got, full[:, position:position + chunk]) <= 2e-2
+            position += chunk
+    finally:
+        _native.lib().tnsr_b200_set_gemm_engine(0)
+
+
+def test_bf16_session_logits_modes_argmax_and_device_loop(oracle):
+    cfg, model, rounded = small_bf16_model("swiglu", 128, 2, 256, vocab=300)
+    params = [p.values() for p in model_parameters(model)]
+    rng = np.random.default_rng(6)
+    batch, prompt_len, steps = 4, 9, 12
+    prompt = rng.integers(0, cfg.vocab_size, size=(batch, prompt_len)).astype(np.uint32)
+
+    def session(mode):
+        s = B200Session(cfg, batch, cfg.max_sequence_length, logits_mode=mode)
+        for i, p in enumerate(params):
+            s.refresh(i, p)
+        return s
+
+    all_s, last_s, none_s = session("all"), session("last"), session("none")
+    la, aa = all_s.decode_full(prompt, 0)
+    ll, al = last_s.decode_full(prompt, 0)
+    ln, an = none_s.decode_full(prompt, 0)
+    assert ln is None
+    la = la.reshape(batch, prompt_len, cfg.vocab_size)
+    assert np.array_equal(la[:, -1].reshape(-1).view(np.uint32), ll.view(np.uint32))
+    assert aa.tolist() == al.tolist() == an.tolist()
+    assert aa.tolist() == [oracle.argmax_last(la[b, -1]) for b in range(batch)]
+    # host-driven greedy loop vs device-resident loop (ids never leave the GPU)
+    host_tokens = [aa.copy()]
+    for step in range(steps):
+        _, nxt = last_s.decode_full(host_tokens[-1].reshape(batch, 1), prompt_len + step)
+        host_tokens.append(nxt.copy())
+    cur = torch.from_numpy(an.astype(np.int32)).cuda()
+    trace = [cur.clone()]
+    for step in range(steps):
+        none_s.decode_device(cur.data_ptr(), 1, prompt_len + step, cur.data_ptr())
+        none_s.synchronize()
+        trace.append(cur.clone())
+    dev_tokens = [t.cpu().numpy().astype(np.uint32) for t in trace]
+    assert [t.tolist() for t in dev_tokens] == [t.tolist() for t in host_tokens]
+
+
+def test_bf16_session_rejects_bad_ids_on_the_device_path():
+    from tnsr_b200.nn import TnsrError
+    cfg, model, _ = small_bf16_model("relu", 64, 2, 64, vocab=50)
+    s = B200Session(cfg, 2, 16, logits_mode="none")
+    for i, p in enumerate(model_parameters(model)):
+        s.refresh(i, p.values())
+    bad = torch.tensor([3, 50], dtype=torch.int32, device="cuda")
+    out = torch.zeros(2, dtype=torch.int32, device="cuda")
+    s.decode_device(bad.data_ptr(), 1, 0, out.data_ptr())
+    with pytest.raises(TnsrError) as err:
+        s.synchronize()
+    assert "outside the vocabulary" in str(err.value)
+    s.reset()
+    good = torch.tensor([3, 49], dtype=torch.int32, device="cuda")
+    s.decode_device(good.data_ptr(), 1, 0, out.data_ptr())
+    s.synchronize()
+    with pytest.raises(TnsrError):
+        s.decode_full(np.asarray([[1], [50]], np.uint32), 1)   # host path validates before any device work
+    with pytest.raises(TnsrError):
+        s.decode_full(np.zeros((2, 17), np.uint32), 0)         # capacity
+
+
+def test_serving_shape_two_layers_against_checker(oracle):
+    """Configuration 4's layer shape (d 768, 12 heads x 64, SwiGLU 2048, vocab 32000) with 2 layers:
+    prefill 70 tokens then greedy decode, 4 sessions, against the checker on bf16-rounded weights."""
+    cfg = GptConfig(vocab_size=32000, max_sequence_length=128, embed_dim=768, num_heads=12, feed_forward_dim=2048,
+                    num_layers=2, layer_norm_epsilon=1e-5, activation="swiglu", weight_dtype="bf16")
+    arrays = normal_model_arrays(cfg, seed=5, std=0.02)
+    rounded = [bf16_round(a) if a.ndim == 2 else a for a in arrays]
+    model = Gpt(cfg)
+    set_model_arrays(model, arrays)
+    m = oracle_model(oracle, cfg, rounded)
+    rng = np.random.default_rng(50)
+    batch, prefill, steps = 4, 70, 6
+    ids = rng.integers(0, cfg.vocab_size, size=(batch, prefill)).astype(np.uint32)
+    s = B200Session(cfg, batch, 128, logits_mode="last")
+    for i, p in enumerate(model_parameters(model)):
+        s.refresh(i, p.values())
+    oracle.set_threads(oracle.max_threads())
+    try:
+        seq = ids.copy()
+        logits, nxt = s.decode_full(ids, 0)
+        for step in range(steps):
+            full = m.forward(seq)[:, -1]
+            got = logits.reshape(batch, cfg.vocab_size)
+            assert rel_err(got, full) <= 2e-2
+            ref_next = [oracle.argmax_last(full[b]) for b in range(batch)]
+            top2 = np.sort(full, axis=1)[:, -2:]
+            margin = top2[:, 1] - top2[:, 0]
+            for b in range(batch):
+                if margin[b] > 0.05 * float(np.max(np.abs(full[b]))):
+                    assert int(nxt[b]) == ref_next[b]
+            seq = np.concatenate([seq, nxt.reshape(batch, 1).astype(np.uint32)], axis=1)
+            logits, nxt = s.decode_full(nxt.reshape(batch, 1), prefill + step)
+    finally:
+        oracle.set_threads(1)

@@ -1,0 +1,620 @@
+// KV-cache attention on bf16 caches.
+//
+//  * decode_attention_*: one query per (session, head) scanned over the live
+//    prefix only, split over the key axis so that every SM streams a contiguous
+//    slab of K and V rows (all heads) through a shared-memory ring filled by
+//    bulk async copies (cp.async.bulk, mbarrier completion); f32 online softmax;
+//    partials (max, sum, numerator) merged by a second small kernel.  This is
+//    the job of the reference's AttentionScan / MergeScan pair
+//    (src/nn/kv_cache/attention.rs:31-239, :242-393; fixed 16/32 partitions,
+//    src/nn/kv_cache/cuda.rs:31-32,110-116) with two differences: the split is
+//    by fixed key-slab size chosen from the total live length, so ragged
+//    per-session lengths balance across SMs, and K/V are read as whole cache
+//    rows (all heads at once) so HBM sees only long contiguous bursts.
+//  * attention_generic: any head width and chunk, one warp per query/head.
+//
+// HBM traffic per decode step is the live K and V rows once: 4 * d bytes per
+// live key per session (d = heads * head_dim) plus q / out / partials.
+#include "common.cuh"
+
+namespace tb {
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// ===========================================================================
+// Generic kernel (bf16): one warp per (session, head, query); lane c owns dims
+// c, c+32, ...; keys walked in order with a running max / sum / numerator.
+// ===========================================================================
+constexpr int GEN_MAX_SLOTS = 8;  // head_dim <= 256
+
+__global__ void __launch_bounds__(128)
+attention_generic_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
+                         bf16* __restrict__ out, uint32_t total_queries, uint32_t chunk, uint32_t position,
+                         const uint32_t* __restrict__ d_position, uint32_t capacity, uint32_t heads, uint32_t hd,
+                         float scale_log2) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t idx = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (idx >= total_queries) return;
+    const uint32_t t = idx % chunk, h = (idx / chunk) % heads, s = idx / (chunk * heads);
+    const uint32_t d = heads * hd;
+    const uint32_t past = d_position ? *d_position : position;
+    uint32_t total = past + t + 1;
+    if (total > capacity) total = capacity;
+    float qv[GEN_MAX_SLOTS], acc[GEN_MAX_SLOTS];
+    const bf16* qr = q + ((size_t)s * chunk + t) * d + (size_t)h * hd;
+#pragma unroll
+    for (int i = 0; i < GEN_MAX_SLOTS; ++i) {
+        uint32_t c = lane + 32 * i;
+        qv[i] = c < hd ? __bfloat162float(qr[c]) * scale_log2 : 0.0f;
+        acc[i] = 0.0f;
+    }
+    const bf16* kb = kc + (size_t)s * capacity * d + (size_t)h * hd;
+    const bf16* vb = vc + (size_t)s * capacity * d + (size_t)h * hd;
+    float m = -INFINITY, l = 0.0f;
+    for (uint32_t j = 0; j < total; ++j) {
+        float part = 0.0f;
+#pragma unroll
+        for (int i = 0; i < GEN_MAX_SLOTS; ++i) {
+            uint32_t c = lane + 32 * i;
+            if (c < hd) part = fmaf(qv[i], __bfloat162float(kb[(size_t)j * d + c]), part);
+        }
+        const float sc = warp_sum_f(part);
+        const float m_new = fmaxf(m, sc);
+        const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
+        const float corr = ex2(m - m_safe), p = ex2(sc - m_safe);
+        l = l * corr + p;
+#pragma unroll
+        for (int i = 0; i < GEN_MAX_SLOTS; ++i) {
+            uint32_t c = lane + 32 * i;
+            if (c < hd) acc[i] = acc[i] * corr + p * __bfloat162float(vb[(size_t)j * d + c]);
+        }
+        m = m_new;
+    }
+    bf16* orow = out + ((size_t)s * chunk + t) * d + (size_t)h * hd;
+#pragma unroll
+    for (int i = 0; i < GEN_MAX_SLOTS; ++i) {
+        uint32_t c = lane + 32 * i;
+        if (c < hd) orow[c] = __float2bfloat16_rn(acc[i] / l);
+    }
+}
+
+int launch_attention_generic(const bf16* q, const bf16* k_cache, const bf16* v_cache, bf16* out,
+                             uint32_t sessions, uint32_t chunk, uint32_t position,
+                             const uint32_t* d_position, uint32_t capacity, uint32_t heads,
+                             uint32_t head_dim, cudaStream_t stream) {
+    if (sessions == 0 || chunk == 0) return TNSR_B200_OK;
+    if (head_dim > 32 * GEN_MAX_SLOTS) {
+        set_thread_error("attention: head_dim above 256 is outside the bf16 kernels");
+        return TNSR_B200_ERR_UNSUPPORTED;
+    }
+    uint64_t total = (uint64_t)sessions * heads * chunk;
+    if (total > 0x7fffffffull) return TNSR_B200_ERR_UNSUPPORTED;
+    const float scale_log2 = (1.0f / sqrtf((float)head_dim)) * 1.4426950408889634f;
+    attention_generic_kernel<<<(unsigned)ceil_div64(total, 4), 128, 0, stream>>>(
+        q, k_cache, v_cache, out, (uint32_t)total, chunk, position, d_position, capacity, heads, head_dim, scale_log2);
+    count_launch();
+    return check_launch("attention_generic");
+}
+
+// ===========================================================================
+// Split-KV decode attention
+// ===========================================================================
+constexpr uint32_t DA_KS = 16;             // keys per ring stage
+constexpr uint32_t DA_MAX_STAGES = 8;
+constexpr uint32_t DA_SMEM_BUDGET = 200 * 1024;
+constexpr uint64_t DA_WAIT_LIMIT_NS = 2000000000ull;
+constexpr uint32_t DA_MIN_SLAB = 32;       // smallest key slab per work item
+
+struct DaItem {
+    uint32_t session, key0, nkeys, pad;
+};
+
+// Workspace layout (all offsets 256-byte aligned):
+//   header  : uint32 n_items, slab
+//   first   : uint32 [batch]      first item of each session
+//   count   : uint32 [batch]      items of each session
+//   items   : DaItem [max_items]
+//   partial : float  [max_items][heads][head_dim + 2]   (numerator, then max, then sum)
+struct DaLayout {
+    uint64_t first, count, items, partial, bytes;
+    uint32_t max_items;
+};
+
+static uint64_t align256(uint64_t x) { return (x + 255) & ~255ull; }
+
+static DaLayout da_layout(uint32_t batch, uint32_t capacity, uint32_t heads, uint32_t head_dim, uint64_t budget) {
+    DaLayout L;
+    // Enough items for the smallest slab, but never more partial storage than ~256 MiB.
+    uint64_t per_item = (uint64_t)heads * (head_dim + 2) * 4;
+    uint64_t want = (uint64_t)batch * ceil_div(capacity, DA_MIN_SLAB);
+    uint64_t cap_items = (256ull << 20) / per_item;
+    if (cap_items < batch) cap_items = batch;
+    uint64_t items = want < cap_items ? want : cap_items;
+    L.first = 256;
+    L.count = align256(L.first + 4ull * batch);
+    L.items = align256(L.count + 4ull * batch);
+    if (budget) {
+        // shrink to what the caller gave us, keeping at least one item per session
+        uint64_t fixed = align256(L.items);
+        if (budget > fixed) {
+            uint64_t fit = (budget - fixed - 256) / (per_item + sizeof(DaItem));
+            if (fit < items) items = fit;
+        } else {
+            items = 0;
+        }
+    }
+    L.max_items = (uint32_t)(items > 0x7fffffffull ? 0x7fffffffull : items);
+    L.partial = align256(L.items + sizeof(DaItem) * (uint64_t)L.max_items);
+    L.bytes = L.partial + per_item * L.max_items;
+    return L;
+}
+
+uint64_t decode_attention_workspace_bytes(uint32_t batch, uint32_t capacity, uint32_t heads, uint32_t head_dim) {
+    return da_layout(batch, capacity, heads, head_dim, 0).bytes;
+}
+
+bool decode_attention_supported(uint32_t heads, uint32_t head_dim) {
+    if (!(head_dim == 32 || head_dim == 64 || head_dim == 128)) return false;
+    if (heads == 0 || heads > 32) return false;
+    uint64_t stage = 2ull * DA_KS * heads * head_dim * 2 + (uint64_t)heads * head_dim * 2;
+    return stage * 2 <= DA_SMEM_BUDGET;  // at least a double buffer
+}
+
+// ---- plan: choose the slab, build the item list --------------------------------
+// One block.  lengths == nullptr means every session has *d_position + extra keys.
+__global__ void __launch_bounds__(1024)
+da_plan_kernel(const uint32_t* __restrict__ lengths, const uint32_t* __restrict__ d_position, uint32_t extra,
+               uint32_t batch, uint32_t capacity, uint32_t target_items, uint32_t max_items,
+               uint32_t* __restrict__ header, uint32_t* __restrict__ first, uint32_t* __restrict__ count,
+               DaItem* __restrict__ items, int* __restrict__ d_status) {
+    __shared__ unsigned long long red[32];
+    __shared__ uint32_t s_slab;
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    auto len_of = [&](uint32_t b) -> uint32_t {
+        uint32_t L = lengths ? lengths[b] : (*d_position + extra);
+        if (L > capacity) {
+            if (d_status) atomicCAS(d_status, DEV_OK, DEV_BAD_LENGTH);
+            L = capacity;
+        }
+        return L;
+    };
+    auto block_sum = [&](unsigned long long v) -> unsigned long long {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        __syncthreads();
+        if (lane == 0) red[warp] = v;
+        __syncthreads();
+        unsigned long long t = 0;
+        for (uint32_t w = 0; w < (blockDim.x >> 5); ++w) t += red[w];
+        return t;
+    };
+    unsigned long long mine = 0;
+    for (uint32_t b = tid; b < batch; b += blockDim.x) mine += len_of(b);
+    const unsigned long long total = block_sum(mine);
+    // largest slab (a power of two from 256 down to DA_MIN_SLAB) that still yields target_items
+    uint32_t slab = 256;
+    while (slab > DA_MIN_SLAB && total / slab < target_items) slab >>= 1;
+    // ... but never more items than the workspace holds
+    for (;;) {
+        unsigned long long n = 0;
+        for (uint32_t b = tid; b < batch; b += blockDim.x) n += (len_of(b) + slab - 1) / slab;
+        n = block_sum(n);
+        if (n <= max_items || slab >= (1u << 30)) break;
+        slab <<= 1;
+    }
+    if (tid == 0) s_slab = slab;
+    __syncthreads();
+    slab = s_slab;
+    if (tid == 0) {
+        uint32_t run = 0;
+        for (uint32_t b = 0; b < batch; ++b) {
+            uint32_t c = (len_of(b) + slab - 1) / slab;
+            first[b] = run;
+            count[b] = c;
+            run += c;
+        }
+        header[0] = run;
+        header[1] = slab;
+    }
+    __syncthreads();
+    for (uint32_t b = tid; b < batch; b += blockDim.x) {
+        const uint32_t L = len_of(b), f = first[b], c = count[b];
+        for (uint32_t i = 0; i < c; ++i) {
+            DaItem it;
+            it.session = b;
+            it.key0 = i * slab;
+            it.nkeys = min(slab, L - i * slab);
+            it.pad = 0;
+            items[f + i] = it;
+        }
+    }
+}
+
+// ---- main kernel ------------------------------------------------------------------
+__device__ __forceinline__ uint32_t da_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void da_mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(da_smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void da_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(da_smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void da_mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(da_smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool da_mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(da_smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t da_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool da_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (da_mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = da_timer_ns();
+    for (uint32_t it = 1;; ++it) {
+        if (da_mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (da_timer_ns() - start > DA_WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+// Plain (untiled) bulk copy global -> this CTA's shared memory; 16-byte aligned, size % 16 == 0.
+__device__ __forceinline__ void da_bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(da_smem_u32(dst)), "l"(src), "r"(bytes), "r"(da_smem_u32(bar))
+                 : "memory");
+}
+
+struct DaStageMeta {
+    uint32_t item;    // index into items / partial
+    uint32_t nk;      // valid keys in this stage (1..DA_KS)
+    uint32_t flags;   // bit 0: first stage of the item, bit 1: last stage
+    uint32_t session;
+};
+
+struct DaParams {
+    const bf16* q;
+    const bf16* kc;
+    const bf16* vc;
+    const uint32_t* header;
+    const DaItem* items;
+    float* partial;
+    uint32_t capacity, heads;
+    uint32_t stages;
+    float scale_log2;
+    int* d_status;
+};
+
+// HD: head width; LPK = HD / 8 lanes share one (key, head) row slice, each lane
+// owning 8 consecutive dims (one 16-byte shared-memory load); KPW = 32 / LPK keys
+// are processed side by side in a warp.  HPW: heads per consumer warp.
+template <int HD, int HPW>
+__global__ void __launch_bounds__(576, 1)
+decode_attention_kernel(DaParams P) {
+    constexpr uint32_t LPK = HD / 8, KPW = 32 / LPK, ITERS = DA_KS / KPW;
+    static_assert(DA_KS % KPW == 0, "stage must hold whole key groups");
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t d = P.heads * HD, row_bytes = d * 2;
+    const uint32_t k_bytes = DA_KS * row_bytes;
+    const uint32_t stage_bytes = 2 * k_bytes + row_bytes;  // K slab, V slab, q row
+    uint8_t* ring = smem;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)P.stages * stage_bytes);
+    uint64_t* empty_bar = full_bar + DA_MAX_STAGES;
+    DaStageMeta* meta = reinterpret_cast<DaStageMeta*>(empty_bar + DA_MAX_STAGES);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(meta + DA_MAX_STAGES);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t consumers = (blockDim.x >> 5) - 1;  // last warp is the producer
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < P.stages; ++s) { da_mbar_init(full_bar + s, 1); da_mbar_init(empty_bar + s, consumers); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const uint32_t n_items = P.header[0];
+
+    if (warp == consumers) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+                const DaItem it = P.items[item];
+                const size_t base = ((size_t)it.session * P.capacity + it.key0) * d;
+                const uint32_t n_stages = (it.nkeys + DA_KS - 1) / DA_KS;
+                for (uint32_t s = 0; s < n_stages; ++s) {
+                    if (!da_mbar_wait(empty_bar + stage, phase ^ 1, abort_flag)) { ok = false; break; }
+                    const uint32_t nk = min(DA_KS, it.nkeys - s * DA_KS);
+                    uint8_t* sk = ring + (size_t)stage * stage_bytes;
+                    DaStageMeta mt;
+                    mt.item = item;
+                    mt.nk = nk;
+                    mt.flags = (s == 0 ? 1u : 0u) | (s + 1 == n_stages ? 2u : 0u);
+                    mt.session = it.session;
+                    meta[stage] = mt;
+                    const uint32_t bytes = nk * row_bytes;
+                    da_mbar_expect_tx(full_bar + stage, 2 * bytes + (s == 0 ? row_bytes : 0));
+                    da_bulk_load(sk, P.kc + base + (size_t)s * DA_KS * d, bytes, full_bar + stage);
+                    da_bulk_load(sk + k_bytes, P.vc + base + (size_t)s * DA_KS * d, bytes, full_bar + stage);
+                    if (s == 0) da_bulk_load(sk + 2 * k_bytes, P.q + (size_t)it.session * d, row_bytes, full_bar + stage);
+                    if (++stage == P.stages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else {
+        // ---------------- consumers ----------------
+        const uint32_t grp = lane / LPK;       // which of the KPW parallel keys
+        const uint32_t sub = lane % LPK;       // which 8-dim slice of the head
+        float qf[HPW][8], acc[HPW][8], m[HPW], l[HPW];
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        for (uint32_t item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+            for (;;) {
+                if (!da_mbar_wait(full_bar + stage, phase, abort_flag)) { ok = false; break; }
+                const DaStageMeta mt = meta[stage];
+                const uint8_t* sk = ring + (size_t)stage * stage_bytes;
+                const uint8_t* sv = sk + k_bytes;
+                if (mt.flags & 1u) {
+                    const uint8_t* sq = sk + 2 * k_bytes;
+#pragma unroll
+                    for (int hh = 0; hh < HPW; ++hh) {
+                        const uint32_t h = warp + hh * consumers;
+                        m[hh] = -INFINITY;
+                        l[hh] = 0.0f;
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) acc[hh][e] = 0.0f;
+                        if (h < P.heads) {
+                            const uint4 qq = *reinterpret_cast<const uint4*>(sq + ((size_t)h * HD + sub * 8) * 2);
+                            const uint32_t w[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                float2 f = bf16x2_to_f32(w[e]);
+                                qf[hh][2 * e] = f.x * P.scale_log2;
+                                qf[hh][2 * e + 1] = f.y * P.scale_log2;
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int hh = 0; hh < HPW; ++hh) {
+                    const uint32_t h = warp + hh * consumers;
+                    if (h >= P.heads) continue;
+                    const uint32_t col = (h * HD + sub * 8) * 2;
+                    float sc[ITERS];
+#pragma unroll
+                    for (uint32_t itr = 0; itr < ITERS; ++itr) {
+                        const uint32_t key = itr * KPW + grp;
+                        const uint4 kk = *reinterpret_cast<const uint4*>(sk + (size_t)key * row_bytes + col);
+                        const uint32_t w[4] = {kk.x, kk.y, kk.z, kk.w};
+                        float part = 0.0f;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            float2 f = bf16x2_to_f32(w[e]);
+                            part = fmaf(qf[hh][2 * e], f.x, part);
+                            part = fmaf(qf[hh][2 * e + 1], f.y, part);
+                        }
+#pragma unroll
+                        for (uint32_t o = LPK / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+                        sc[itr] = key < mt.nk ? part : -INFINITY;
+                    }
+                    float m_new = m[hh];
+#pragma unroll
+                    for (uint32_t itr = 0; itr < ITERS; ++itr) m_new = fmaxf(m_new, sc[itr]);
+                    const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
+                    const float corr = ex2(m[hh] - m_safe);
+                    m[hh] = m_new;
+                    float lsum = l[hh] * corr;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[hh][e] *= corr;
+#pragma unroll
+                    for (uint32_t itr = 0; itr < ITERS; ++itr) {
+                        const uint32_t key = itr * KPW + grp;
+                        const float p = ex2(sc[itr] - m_safe);  // 0 for masked keys
+                        lsum += p;
+                        if (key < mt.nk) {
+                            const uint4 vv = *reinterpret_cast<const uint4*>(sv + (size_t)key * row_bytes + col);
+                            const uint32_t w[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                float2 f = bf16x2_to_f32(w[e]);
+                                acc[hh][2 * e] = fmaf(p, f.x, acc[hh][2 * e]);
+                                acc[hh][2 * e + 1] = fmaf(p, f.y, acc[hh][2 * e + 1]);
+                            }
+                        }
+                    }
+                    l[hh] = lsum;
+                }
+                const bool last = (mt.flags & 2u) != 0;
+                if (last) {
+                    // fold the KPW side-by-side key groups together and store the partial
+#pragma unroll
+                    for (int hh = 0; hh < HPW; ++hh) {
+                        const uint32_t h = warp + hh * consumers;
+                        if (h >= P.heads) continue;
+                        float mm = m[hh];
+#pragma unroll
+                        for (uint32_t o = LPK; o < 32; o <<= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+                        const float m_safe = (mm == -INFINITY) ? 0.0f : mm;
+                        const float f = ex2(m[hh] - m_safe);
+                        float ll = l[hh] * f;
+                        float a[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) a[e] = acc[hh][e] * f;
+#pragma unroll
+                        for (uint32_t o = LPK; o < 32; o <<= 1) {
+                            ll += __shfl_xor_sync(0xffffffffu, ll, o);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) a[e] += __shfl_xor_sync(0xffffffffu, a[e], o);
+                        }
+                        if (grp == 0) {
+                            float* dst = P.partial + ((size_t)mt.item * P.heads + h) * (HD + 2);
+                            // (HD + 2) floats per head keeps 8-byte alignment only: store as float2
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                *reinterpret_cast<float2*>(dst + sub * 8 + 2 * e) = make_float2(a[2 * e], a[2 * e + 1]);
+                            if (sub == 0) *reinterpret_cast<float2*>(dst + HD) = make_float2(mm, ll);
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) da_mbar_arrive(empty_bar + stage);
+                if (++stage == P.stages) { stage = 0; phase ^= 1; }
+                if (last) break;
+            }
+        }
+    }
+    __syncthreads();
+    if (*abort_flag) {
+        const uint64_t start = da_timer_ns();
+        while (da_timer_ns() - start < 200000ull) __nanosleep(1000);
+        if (threadIdx.x == 0 && P.d_status) atomicCAS(P.d_status, DEV_OK, DEV_TIMEOUT);
+        __syncthreads();
+    }
+}
+
+// ---- merge: one block per session, one thread per 4 output dims -----------------
+__global__ void __launch_bounds__(1024)
+da_merge_kernel(const float* __restrict__ partial, const uint32_t* __restrict__ first, const uint32_t* __restrict__ count,
+                bf16* __restrict__ out, uint32_t heads, uint32_t hd) {
+    const uint32_t b = blockIdx.x, d = heads * hd;
+    const uint32_t f = first[b], n = count[b];
+    for (uint32_t c4 = threadIdx.x * 4; c4 < d; c4 += blockDim.x * 4) {
+        const uint32_t h = c4 / hd, c = c4 % hd;
+        float mx = -INFINITY;
+        for (uint32_t i = 0; i < n; ++i) mx = fmaxf(mx, partial[((size_t)(f + i) * heads + h) * (hd + 2) + hd]);
+        const float m_safe = (mx == -INFINITY) ? 0.0f : mx;
+        float l = 0.0f, a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+        for (uint32_t i = 0; i < n; ++i) {
+            const float* p = partial + ((size_t)(f + i) * heads + h) * (hd + 2);
+            const float w = ex2(p[hd] - m_safe);
+            l = fmaf(p[hd + 1], w, l);
+            const float2 x = *reinterpret_cast<const float2*>(p + c), y = *reinterpret_cast<const float2*>(p + c + 2);
+            a0 = fmaf(x.x, w, a0); a1 = fmaf(x.y, w, a1); a2 = fmaf(y.x, w, a2); a3 = fmaf(y.y, w, a3);
+        }
+        uint2 o = make_uint2(0u, 0u);
+        if (n > 0) {
+            const float inv = 1.0f / l;
+            o = make_uint2(pack_bf16x2(a0 * inv, a1 * inv), pack_bf16x2(a2 * inv, a3 * inv));
+        }
+        *reinterpret_cast<uint2*>(out + (size_t)b * d + c4) = o;
+    }
+}
+
+template <int HD, int HPW>
+static int launch_da_t(const DaParams& P, uint32_t threads, size_t smem, uint32_t grid, cudaStream_t stream) {
+    if (cudaFuncSetAttribute(decode_attention_kernel<HD, HPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return check_launch("decode_attention attribute");
+    decode_attention_kernel<HD, HPW><<<grid, threads, smem, stream>>>(P);
+    count_launch();
+    return check_launch("decode_attention");
+}
+
+static int da_sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+// lengths may be nullptr: then every session holds *d_position + extra keys.
+int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v_cache, const uint32_t* d_lengths,
+                               const uint32_t* d_position, uint32_t extra, bf16* out, void* workspace,
+                               uint64_t workspace_bytes, uint32_t batch, uint32_t capacity, uint32_t heads,
+                               uint32_t head_dim, bool plan, int* d_status, cudaStream_t stream) {
+    if (batch == 0) return TNSR_B200_OK;
+    if (!decode_attention_supported(heads, head_dim)) {
+        set_thread_error("decode attention: head_dim must be 32, 64 or 128 and heads <= 32");
+        return TNSR_B200_ERR_UNSUPPORTED;
+    }
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+         reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(workspace)) % 16) {
+        set_thread_error("decode attention: pointers must be 16-byte aligned");
+        return TNSR_B200_ERR_INVALID_ARGUMENT;
+    }
+    const DaLayout L = da_layout(batch, capacity, heads, head_dim, workspace_bytes);
+    if (L.max_items < batch || L.bytes > workspace_bytes) {
+        set_thread_error("decode attention: workspace too small");
+        return TNSR_B200_ERR_INVALID_ARGUMENT;
+    }
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    uint32_t* header = reinterpret_cast<uint32_t*>(ws);
+    uint32_t* first = reinterpret_cast<uint32_t*>(ws + L.first);
+    uint32_t* count = reinterpret_cast<uint32_t*>(ws + L.count);
+    DaItem* items = reinterpret_cast<DaItem*>(ws + L.items);
+    float* partial = reinterpret_cast<float*>(ws + L.partial);
+    const uint32_t grid = (uint32_t)da_sm_count();
+    if (plan) {
+        da_plan_kernel<<<1, 1024, 0, stream>>>(d_lengths, d_position, extra, batch, capacity, 8 * grid, L.max_items, header,
+                                               first, count, items, d_status);
+        count_launch();
+        int rc = check_launch("decode_attention plan");
+        if (rc) return rc;
+    }
+    const uint32_t d = heads * head_dim, row_bytes = d * 2;
+    const uint32_t stage_bytes = 2 * DA_KS * row_bytes + row_bytes;
+    uint32_t stages = DA_SMEM_BUDGET / stage_bytes;
+    if (stages > DA_MAX_STAGES) stages = DA_MAX_STAGES;
+    const size_t smem = (size_t)stages * stage_bytes + 2 * DA_MAX_STAGES * 8 + DA_MAX_STAGES * sizeof(DaStageMeta) + 16;
+    const uint32_t hpw = heads > 16 ? 2 : 1;
+    const uint32_t consumers = ceil_div(heads, hpw);
+    DaParams P;
+    P.q = q; P.kc = k_cache; P.vc = v_cache;
+    P.header = header; P.items = items; P.partial = partial;
+    P.capacity = capacity; P.heads = heads; P.stages = stages;
+    P.scale_log2 = (1.0f / sqrtf((float)head_dim)) * 1.4426950408889634f;
+    P.d_status = d_status;
+    const uint32_t threads = (consumers + 1) * 32;
+    int rc;
+    if (hpw == 1) {
+        rc = head_dim == 32 ? launch_da_t<32, 1>(P, threads, smem, grid, stream)
+           : head_dim == 64 ? launch_da_t<64, 1>(P, threads, smem, grid, stream)
+                            : launch_da_t<128, 1>(P, threads, smem, grid, stream);
+    } else {
+        rc = head_dim == 32 ? launch_da_t<32, 2>(P, threads, smem, grid, stream)
+           : head_dim == 64 ? launch_da_t<64, 2>(P, threads, smem, grid, stream)
+                            : launch_da_t<128, 2>(P, threads, smem, grid, stream);
+    }
+    if (rc) return rc;
+    uint32_t mthreads = d / 4;
+    if (mthreads > 1024) mthreads = 1024;
+    mthreads = (mthreads + 31) / 32 * 32;
+    da_merge_kernel<<<batch, mthreads, 0, stream>>>(partial, first, count, out, heads, head_dim);
+    count_launch();
+    return check_launch("decode_attention merge");
+}
+
+int launch_decode_attention(const bf16* q, const bf16* k_cache, const bf16* v_cache, const uint32_t* d_lengths,
+                            bf16* out, void* workspace, uint64_t workspace_bytes, uint32_t batch,
+                            uint32_t capacity, uint32_t heads, uint32_t head_dim, int* d_status,
+                            cudaStream_t stream) {
+    return launch_decode_attention_ex(q, k_cache, v_cache, d_lengths, nullptr, 0, out, workspace, workspace_bytes, batch,
+                                      capacity, heads, head_dim, true, d_status, stream);
+}
+
+}  // namespace tb

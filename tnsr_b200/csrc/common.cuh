@@ -1,0 +1,193 @@
+// Shared declarations of the sm_100a kernels behind the C ABI in include/tnsr_b200.h.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <string>
+
+#include "../../include/tnsr_b200.h"
+
+namespace tb {
+
+typedef __nv_bfloat16 bf16;
+
+// ---- host-side plumbing ----------------------------------------------------
+
+extern std::atomic<uint64_t> g_launches;       // kernels launched by this library
+void set_thread_error(const std::string& msg);  // message for calls without a handle
+const char* thread_error();
+
+inline void count_launch(uint64_t n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+// Status of the last launch on the current thread's device, as a tnsr_b200 code.
+inline int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_thread_error(std::string(what) + ": " + cudaGetErrorString(e));
+        return TNSR_B200_ERR_CUDA;
+    }
+    return TNSR_B200_OK;
+}
+
+inline uint32_t ceil_div(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
+inline uint64_t ceil_div64(uint64_t a, uint64_t b) { return (a + b - 1) / b; }
+
+// FFN / epilogue activation codes shared by host and device.
+enum : int { ACT_NONE = -1, ACT_RELU = 0, ACT_GELU = 1 };
+
+// Device-side status word: kernels never trap; they record the first problem
+// here and carry on with harmless values.
+enum : int {
+    DEV_OK = 0,
+    DEV_TOKEN_RANGE = 1,    // an id >= vocab reached the gather
+    DEV_TIMEOUT = 2,        // a bounded mbarrier wait gave up
+    DEV_BAD_LENGTH = 3      // a session length beyond the cache capacity
+};
+
+// ---- operator launchers (one per kernel family) -----------------------------
+// Every launcher queues work on `stream` and returns a tnsr_b200 status; none
+// synchronises.  `d_position` arguments are device scalars so that one captured
+// graph of a decode step can be replayed while the position advances.
+
+struct GemmEpilogue {
+    const float* bias = nullptr;      // [n] f32, added after accumulation
+    const float* residual = nullptr;  // [m, ldr] f32, added last (f32 output only)
+    uint32_t ldr = 0;
+    int activation = ACT_NONE;        // applied to acc + bias
+    int out_dtype = TNSR_B200_F32;    // f32 or bf16
+    int round_bf16 = 0;               // strict path: round the f32 result to bf16 precision
+    // Output row mapping: logical row r = s * rows_per_session + t lands at
+    // out + ((s * out_session_rows + row_offset + t) * ldc).  rows_per_session == 0
+    // means the identity mapping.  row_offset is *d_row_offset when that is set.
+    uint32_t rows_per_session = 0;
+    uint32_t out_session_rows = 0;
+    uint32_t row_offset = 0;
+    const uint32_t* d_row_offset = nullptr;
+};
+
+// strict f32: out = a[m,k] . b (+bias)(act)(+residual), reference operation order.
+int launch_gemm_strict(const float* a, const float* b, void* out, uint32_t ldc, uint32_t m, uint32_t k,
+                       uint32_t n, bool b_transposed, const GemmEpilogue& ep, cudaStream_t stream);
+
+// bf16 operands, f32 accumulation.  `bt` is [n, k] K-major.  `mode` selects the
+// epilogue family.
+enum GemmMode : int {
+    GEMM_PLAIN = 0,   // out[m, n] (f32 or bf16) = act(acc + bias) (+ residual)
+    GEMM_QKV = 1,     // n = 3*d: columns [0,d) -> q (bf16), [d,2d) -> K cache rows, [2d,3d) -> V cache rows
+    GEMM_SWIGLU = 2   // n = 2*f packed in blocks of 16: out[m, f] bf16 = silu(gate) * up
+};
+struct GemmQkvTargets {
+    bf16* q = nullptr;        // [m, d]
+    bf16* k_cache = nullptr;  // [sessions, capacity, d]
+    bf16* v_cache = nullptr;
+    uint32_t d = 0, chunk = 0, capacity = 0;
+    const uint32_t* d_position = nullptr;  // device scalar: first new row
+    uint32_t position = 0;                 // used when d_position == nullptr
+};
+int launch_gemm_bf16(const bf16* a, const bf16* bt, void* out, uint32_t ldc, uint32_t m, uint32_t n,
+                     uint32_t k, GemmMode mode, const GemmEpilogue& ep, const GemmQkvTargets* qkv,
+                     int* d_status, cudaStream_t stream);
+extern int g_gemm_engine;  // 0 auto, 1 CUDA-core only, 2 tcgen05 only
+
+int launch_embedding(const void* tok, const void* pos, const uint32_t* ids, float* out, uint32_t rows,
+                     uint32_t chunk, uint32_t position0, const uint32_t* d_position, uint32_t vocab,
+                     uint32_t width, int dtype, int* d_status, cudaStream_t stream);
+int launch_layernorm(const float* x, const float* w, const float* b, void* out, uint32_t rows,
+                     uint32_t width, float eps, int out_dtype, bool strict, cudaStream_t stream);
+// Gathers row (s * chunk + chunk - 1) of x for every session s into out[s, :] (f32).
+int launch_gather_last_rows(const float* x, float* out, uint32_t sessions, uint32_t chunk, uint32_t width,
+                            cudaStream_t stream);
+int launch_argmax(const float* logits, uint32_t* out, uint32_t rows, uint32_t vocab, uint32_t row_stride,
+                  cudaStream_t stream);
+int launch_swiglu(const bf16* gate, const bf16* up, bf16* out, uint64_t elems, cudaStream_t stream);
+int launch_transpose_bf16(const bf16* in, bf16* out, uint32_t k, uint32_t n, cudaStream_t stream);
+int launch_f32_to_bf16(const float* in, bf16* out, uint64_t elems, cudaStream_t stream);
+int launch_bf16_to_f32(const bf16* in, float* out, uint64_t elems, cudaStream_t stream);
+// in [k, n] f32 row-major -> out [n, k] bf16 (round to nearest even)
+int launch_transpose_f32_to_bf16(const float* in, bf16* out, uint32_t k, uint32_t n, cudaStream_t stream);
+int launch_transpose_f32_to_bf16_mapped(const float* in, bf16* out, uint32_t k, uint32_t n, uint32_t row0,
+                                        uint32_t block, uint32_t block_stride, cudaStream_t stream);
+int launch_layernorm_strict(const float* x, const float* w, const float* b, float* out, uint32_t rows,
+                            uint32_t width, float eps, cudaStream_t stream);
+int launch_swiglu_strict(const float* gate, const float* up, float* out, size_t n, cudaStream_t stream);
+int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v_cache, const uint32_t* d_lengths,
+                               const uint32_t* d_position, uint32_t extra, bf16* out, void* workspace,
+                               uint64_t workspace_bytes, uint32_t batch, uint32_t capacity, uint32_t heads,
+                               uint32_t head_dim, bool plan, int* d_status, cudaStream_t stream);
+int launch_pack_gate_up(const bf16* wg, const bf16* wu, const float* bg, const float* bu, bf16* w_out,
+                        float* b_out, uint32_t d, uint32_t f, cudaStream_t stream);
+int launch_fill_u32(uint32_t* p, uint32_t value, uint32_t n, cudaStream_t stream);
+int launch_add_u32(uint32_t* p, uint32_t delta, cudaStream_t stream);
+
+// Strict f32 attention in the reference's order over a cache that already holds
+// the new rows: q [sessions*chunk, d] f32; caches f32 or bf16 [sessions, capacity, d].
+int launch_attention_strict(const float* q, const void* k_cache, const void* v_cache, float* out,
+                            uint32_t sessions, uint32_t chunk, uint32_t position,
+                            const uint32_t* d_position, uint32_t capacity, uint32_t heads,
+                            uint32_t head_dim, int kv_dtype, int round_bf16, cudaStream_t stream);
+
+// bf16 attention for any head_dim and chunk (online softmax, one warp per query/head).
+int launch_attention_generic(const bf16* q, const bf16* k_cache, const bf16* v_cache, bf16* out,
+                             uint32_t sessions, uint32_t chunk, uint32_t position,
+                             const uint32_t* d_position, uint32_t capacity, uint32_t heads,
+                             uint32_t head_dim, cudaStream_t stream);
+
+// Split-KV decode attention (one query per session/head) with per-session lengths.
+uint64_t decode_attention_workspace_bytes(uint32_t batch, uint32_t capacity, uint32_t heads,
+                                          uint32_t head_dim);
+bool decode_attention_supported(uint32_t heads, uint32_t head_dim);
+int launch_decode_attention(const bf16* q, const bf16* k_cache, const bf16* v_cache,
+                            const uint32_t* d_lengths, bf16* out, void* workspace, uint64_t workspace_bytes,
+                            uint32_t batch, uint32_t capacity, uint32_t heads, uint32_t head_dim,
+                            int* d_status, cudaStream_t stream);
+
+// Tiled causal prefill attention over the cache (tensor cores).
+bool prefill_attention_supported(uint32_t head_dim);
+int launch_prefill_attention(const bf16* q, const bf16* k_cache, const bf16* v_cache, bf16* out,
+                             uint32_t sessions, uint32_t chunk, uint32_t position,
+                             const uint32_t* d_position, uint32_t capacity, uint32_t heads,
+                             uint32_t head_dim, cudaStream_t stream);
+
+// ---- device helpers ----------------------------------------------------------
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t hi16) { return __uint_as_float(hi16 << 16); }
+// Two packed bf16 (low half = element 0) -> two f32.
+__device__ __forceinline__ float2 bf16x2_to_f32(uint32_t v) {
+    return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+}
+// Round to nearest even to bf16 and widen again; NaN stays a quiet NaN.
+__device__ __forceinline__ float round_to_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// nn::sigmoid / nn::silu / nn::gelu (src/nn/activations.rs:5-47) for the fast
+// path: same formulas, f32, with the hardware exponential.
+__device__ __forceinline__ float fast_sigmoid(float x) {
+    float z = __expf(-fabsf(x));
+    float den = z + 1.0f;
+    return (x < 0.0f) ? __fdividef(z, den) : __fdividef(1.0f, den);
+}
+__device__ __forceinline__ float fast_silu(float x) { return x * fast_sigmoid(x); }
+__device__ __forceinline__ float fast_gelu(float x) {
+    float mag = fabsf(x) * 0.70710678118654752440f;
+    float t = __fdividef(1.0f, fmaf(mag, 0.3275911f, 1.0f));
+    float poly = ((((t * 1.0614054f - 1.4531521f) * t + 1.4214138f) * t - 0.28449672f) * t + 0.2548296f) * t;
+    float tail = poly * __expf(-mag * mag) * 0.5f;
+    float cdf = (x < 0.0f) ? tail : 1.0f - tail;
+    return x * cdf;
+}
+__device__ __forceinline__ float apply_activation(float x, int act) {
+    if (act == ACT_RELU) return fmaxf(x, 0.0f);
+    if (act == ACT_GELU) return fast_gelu(x);
+    return x;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace tb

@@ -1,0 +1,811 @@
+// The session object behind tnsr_b200_decoder_*: the B200 counterpart of
+// cuda::CudaDecoder (tnsr src/nn/kv_cache/cuda.rs:47-596).  It owns a private
+// stream, resident weights (repacked once at upload), the K/V cache, activation
+// buffers sized for the largest chunk seen so far, and runs one decode step as a
+// fixed sequence of kernels -- there is no graph to compile and no program
+// cache to evict.
+#include <cstring>
+#include <vector>
+
+#include "common.cuh"
+
+namespace tb {
+std::atomic<uint64_t> g_launches{0};
+static thread_local std::string t_error;
+void set_thread_error(const std::string& msg) { t_error = msg; }
+const char* thread_error() { return t_error.c_str(); }
+}  // namespace tb
+
+using namespace tb;
+
+namespace {
+
+struct Buffer {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+};
+
+enum ParamKind { P_TOK, P_POS, P_VEC, P_QKV_W, P_QKV_B, P_O_W, P_FF_IN_W, P_FF_IN_B, P_FF_OUT_W, P_GATE_W, P_GATE_B, P_UP_W, P_UP_B };
+
+struct ParamInfo {
+    ParamKind kind;
+    uint64_t elems;
+    uint32_t rows, cols;  // [rows, cols] as the reference stores it ([in, out] for matrices)
+    uint32_t layer;
+    uint32_t slot;        // 0/1/2 = q/k/v for QKV params
+    void* dev = nullptr;  // where the values live (f32 path: as given; bf16 path: see upload)
+};
+
+struct Layer {
+    // f32 path: the reference layout, f32.  bf16 path: matrices are [out, in] bf16.
+    void *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr;
+    float *bq = nullptr, *bk = nullptr, *bv = nullptr, *bo = nullptr;
+    float *ln1w = nullptr, *ln1b = nullptr, *ln2w = nullptr, *ln2b = nullptr;
+    void *w_in = nullptr, *w_out = nullptr, *w_gate = nullptr, *w_up = nullptr;
+    float *b_in = nullptr, *b_out = nullptr, *b_gate = nullptr, *b_up = nullptr;
+    // bf16 path fused forms
+    bf16* wqkv = nullptr;  // [3d, d]
+    float* bqkv = nullptr; // [3d]
+    bf16* wgu = nullptr;   // packed [2f, d] when f % 16 == 0
+    float* bgu = nullptr;  // packed [2f]
+    void *kcache = nullptr, *vcache = nullptr;
+};
+
+}  // namespace
+
+struct tnsr_b200_decoder {
+    tnsr_b200_config cfg;
+    cudaStream_t stream = nullptr;
+    bool bf16_path = false, kv_bf16 = false, swiglu = false, fused_gu = false;
+    bool failed = false;
+    std::string error;
+    std::vector<ParamInfo> params;
+    std::vector<Layer> layers;
+    void *tok = nullptr, *pos = nullptr;
+    float *fnw = nullptr, *fnb = nullptr;
+    std::vector<void*> allocations;
+    // activations (grow with the chunk)
+    uint32_t rows_cap = 0, logit_rows_cap = 0;
+    float* h = nullptr;      // residual stream [rows, d] f32
+    void* n = nullptr;       // normalised rows: f32 (strict) or bf16
+    void* q = nullptr;       // queries: f32 (strict) or bf16
+    void* att = nullptr;     // attention output: f32 (strict) or bf16
+    void* ff = nullptr;      // FFN hidden [rows, f]
+    void* ff2 = nullptr;     // second FFN buffer (up projection) when gate/up are not fused
+    float* hl = nullptr;     // last rows [batch, d] f32
+    float* logits = nullptr; // [logit_rows, vocab]
+    uint32_t* d_tokens = nullptr;
+    uint32_t tokens_cap = 0;
+    uint32_t* d_argmax = nullptr;
+    int* d_status = nullptr;
+    void* attn_ws = nullptr;
+    uint64_t attn_ws_bytes = 0;
+    // pinned staging
+    uint32_t* h_tokens = nullptr;
+    uint32_t* h_argmax = nullptr;
+    int* h_status = nullptr;
+    float* h_stage = nullptr;  // upload staging (pinned)
+    size_t h_stage_bytes = 0;
+    float* d_stage = nullptr;  // upload staging (device, f32)
+    size_t d_stage_bytes = 0;
+    std::vector<float> host_bqkv, host_bgu;
+};
+
+namespace {
+
+int fail(tnsr_b200_decoder* dec, int code, const std::string& msg) {
+    if (dec) dec->error = msg;
+    set_thread_error(msg);
+    return code;
+}
+
+int cuda_fail(tnsr_b200_decoder* dec, cudaError_t e, const char* what) {
+    std::string msg = std::string(what) + ": " + cudaGetErrorString(e);
+    int code = (e == cudaErrorMemoryAllocation) ? TNSR_B200_ERR_OUT_OF_MEMORY : TNSR_B200_ERR_CUDA;
+    if (dec && code == TNSR_B200_ERR_CUDA) dec->failed = true;
+    cudaGetLastError();
+    return fail(dec, code, msg);
+}
+
+#define CU(dec, call)                                                   \
+    do {                                                                \
+        cudaError_t e__ = (call);                                       \
+        if (e__ != cudaSuccess) return cuda_fail(dec, e__, #call);      \
+    } while (0)
+
+#define RUN(dec, call)                                                  \
+    do {                                                                \
+        int rc__ = (call);                                              \
+        if (rc__ != TNSR_B200_OK) {                                     \
+            (dec)->error = thread_error();                              \
+            if (rc__ == TNSR_B200_ERR_CUDA) (dec)->failed = true;       \
+            return rc__;                                                \
+        }                                                               \
+    } while (0)
+
+int dev_alloc(tnsr_b200_decoder* dec, void** out, size_t bytes, bool zero) {
+    if (bytes == 0) bytes = 16;
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) return cuda_fail(dec, e, "cudaMalloc");
+    dec->allocations.push_back(p);
+    if (zero) {
+        e = cudaMemsetAsync(p, 0, bytes, dec->stream);
+        if (e != cudaSuccess) return cuda_fail(dec, e, "cudaMemsetAsync");
+    }
+    *out = p;
+    return TNSR_B200_OK;
+}
+
+void dev_free(tnsr_b200_decoder* dec, void* p) {
+    if (!p) return;
+    for (size_t i = 0; i < dec->allocations.size(); ++i)
+        if (dec->allocations[i] == p) {
+            dec->allocations.erase(dec->allocations.begin() + i);
+            break;
+        }
+    cudaFree(p);
+}
+
+size_t elt(const tnsr_b200_decoder* dec) { return dec->bf16_path ? 2 : 4; }
+size_t kv_elt(const tnsr_b200_decoder* dec) { return dec->kv_bf16 ? 2 : 4; }
+
+bool mul_overflow(uint64_t a, uint64_t b, uint64_t* out) { return __builtin_mul_overflow(a, b, out); }
+
+// model_parameters order (src/nn/kv_cache.rs:392-421) + the SwiGLU extension.
+void describe_params(tnsr_b200_decoder* dec) {
+    const tnsr_b200_config& c = dec->cfg;
+    const uint32_t d = c.embed_dim, f = c.feed_forward_dim;
+    auto add = [&](ParamKind k, uint32_t rows, uint32_t cols, uint32_t layer, uint32_t slot) {
+        ParamInfo p;
+        p.kind = k; p.rows = rows; p.cols = cols; p.elems = (uint64_t)rows * cols; p.layer = layer; p.slot = slot;
+        dec->params.push_back(p);
+    };
+    add(P_TOK, c.vocab_size, d, 0, 0);
+    add(P_POS, c.max_sequence_length, d, 0, 0);
+    add(P_VEC, 1, d, 0, 100);  // final norm weight
+    add(P_VEC, 1, d, 0, 101);  // final norm bias
+    for (uint32_t l = 0; l < c.num_layers; ++l) {
+        for (uint32_t s = 0; s < 3; ++s) { add(P_QKV_W, d, d, l, s); add(P_QKV_B, 1, d, l, s); }
+        add(P_O_W, d, d, l, 0);
+        add(P_VEC, 1, d, l, 0);   // o bias
+        add(P_VEC, 1, d, l, 1);   // ln1 w
+        add(P_VEC, 1, d, l, 2);   // ln1 b
+        add(P_VEC, 1, d, l, 3);   // ln2 w
+        add(P_VEC, 1, d, l, 4);   // ln2 b
+        if (dec->swiglu) {
+            add(P_GATE_W, d, f, l, 0); add(P_GATE_B, 1, f, l, 0);
+            add(P_UP_W, d, f, l, 0);   add(P_UP_B, 1, f, l, 0);
+            add(P_FF_OUT_W, f, d, l, 0); add(P_VEC, 1, d, l, 5);
+        } else {
+            add(P_FF_IN_W, d, f, l, 0); add(P_FF_IN_B, 1, f, l, 0);
+            add(P_FF_OUT_W, f, d, l, 0); add(P_VEC, 1, d, l, 5);
+        }
+    }
+}
+
+int allocate_weights(tnsr_b200_decoder* dec) {
+    const tnsr_b200_config& c = dec->cfg;
+    const uint64_t d = c.embed_dim, f = c.feed_forward_dim;
+    const size_t e = elt(dec);
+    int rc;
+    if ((rc = dev_alloc(dec, &dec->tok, (size_t)c.vocab_size * d * e, true))) return rc;
+    if ((rc = dev_alloc(dec, &dec->pos, (size_t)c.max_sequence_length * d * e, true))) return rc;
+    if ((rc = dev_alloc(dec, (void**)&dec->fnw, d * 4, true))) return rc;
+    if ((rc = dev_alloc(dec, (void**)&dec->fnb, d * 4, true))) return rc;
+    dec->layers.resize(c.num_layers);
+    const size_t cache_bytes = (size_t)c.batch * c.capacity * d * kv_elt(dec);
+    for (Layer& L : dec->layers) {
+        if (dec->bf16_path) {
+            if ((rc = dev_alloc(dec, (void**)&L.wqkv, 3 * d * d * 2, true))) return rc;
+            if ((rc = dev_alloc(dec, (void**)&L.bqkv, 3 * d * 4, true))) return rc;
+            L.wq = L.wqkv; L.wk = L.wqkv + d * d; L.wv = L.wqkv + 2 * d * d;
+            L.bq = L.bqkv; L.bk = L.bqkv + d; L.bv = L.bqkv + 2 * d;
+        } else {
+            if ((rc = dev_alloc(dec, &L.wq, d * d * 4, true))) return rc;
+            if ((rc = dev_alloc(dec, &L.wk, d * d * 4, true))) return rc;
+            if ((rc = dev_alloc(dec, &L.wv, d * d * 4, true))) return rc;
+            if ((rc = dev_alloc(dec, (void**)&L.bq, d * 4, true))) return rc;
+            if ((rc = dev_alloc(dec, (void**)&L.bk, d * 4, true))) return rc;
+            if ((rc = dev_alloc(dec, (void**)&L.bv, d * 4, true))) return rc;
+        }
+        if ((rc = dev_alloc(dec, &L.wo, d * d * e, true))) return rc;
+        if ((rc = dev_alloc(dec, (void**)&L.bo, d * 4, true))) return rc;
+        if ((rc = dev_alloc(dec, (void**)&L.ln1w, d * 4, true))) return rc;
+        if ((rc = dev_alloc(dec, (void**)&L.ln1b, d * 4, true))) return rc;
+        if ((rc = dev_alloc(dec, (void**)&L.ln2w, d * 4, true))) return rc;
+        if ((rc = dev_alloc(dec, (void**)&L.ln2b, d * 4, true))) return rc;
+        if (dec->swiglu) {
+            if (dec->fused_gu) {
+                if ((rc = dev_alloc(dec, (void**)&L.wgu, 2 * f * d * 2, true))) return rc;
+                if ((rc = dev_alloc(dec, (void**)&L.bgu, 2 * f * 4, true))) return rc;
+            } else {
+                if ((rc = dev_alloc(dec, &L.w_gate, d * f * e, true))) return rc;
+                if ((rc = dev_alloc(dec, &L.w_up, d * f * e, true))) return rc;
+                if ((rc = dev_alloc(dec, (void**)&L.b_gate, f * 4, true))) return rc;
+                if ((rc = dev_alloc(dec, (void**)&L.b_up, f * 4, true))) return rc;
+            }
+        } else {
+            if ((rc = dev_alloc(dec, &L.w_in, d * f * e, true))) return rc;
+            if ((rc = dev_alloc(dec, (void**)&L.b_in, f * 4, true))) return rc;
+        }
+        if ((rc = dev_alloc(dec, &L.w_out, f * d * e, true))) return rc;
+        if ((rc = dev_alloc(dec, (void**)&L.b_out, d * 4, true))) return rc;
+        if ((rc = dev_alloc(dec, &L.kcache, cache_bytes, true))) return rc;
+        if ((rc = dev_alloc(dec, &L.vcache, cache_bytes, true))) return rc;
+    }
+    return TNSR_B200_OK;
+}
+
+int ensure_rows(tnsr_b200_decoder* dec, uint32_t rows, uint32_t logit_rows) {
+    const tnsr_b200_config& c = dec->cfg;
+    const uint64_t d = c.embed_dim, f = c.feed_forward_dim;
+    const size_t a = dec->bf16_path ? 2 : 4;
+    int rc;
+    if (rows > dec->rows_cap) {
+        CU(dec, cudaStreamSynchronize(dec->stream));
+        dev_free(dec, dec->h); dev_free(dec, dec->n); dev_free(dec, dec->q); dev_free(dec, dec->att);
+        dev_free(dec, dec->ff); dev_free(dec, dec->ff2);
+        dec->h = nullptr; dec->n = dec->q = dec->att = dec->ff = dec->ff2 = nullptr;
+        dec->rows_cap = 0;
+        if ((rc = dev_alloc(dec, (void**)&dec->h, rows * d * 4, false))) return rc;
+        if ((rc = dev_alloc(dec, &dec->n, rows * d * a, false))) return rc;
+        if ((rc = dev_alloc(dec, &dec->q, rows * d * a, false))) return rc;
+        if ((rc = dev_alloc(dec, &dec->att, rows * d * a, false))) return rc;
+        if ((rc = dev_alloc(dec, &dec->ff, rows * f * a, false))) return rc;
+        if (dec->swiglu && !dec->fused_gu)
+            if ((rc = dev_alloc(dec, &dec->ff2, rows * f * a, false))) return rc;
+        dec->rows_cap = rows;
+    }
+    if (logit_rows > dec->logit_rows_cap) {
+        CU(dec, cudaStreamSynchronize(dec->stream));
+        dev_free(dec, dec->logits);
+        dec->logits = nullptr;
+        dec->logit_rows_cap = 0;
+        uint64_t bytes;
+        if (mul_overflow((uint64_t)logit_rows * c.vocab_size, 4, &bytes)) return fail(dec, TNSR_B200_ERR_OUT_OF_MEMORY, "logits size overflow");
+        if ((rc = dev_alloc(dec, (void**)&dec->logits, bytes, false))) return rc;
+        dec->logit_rows_cap = logit_rows;
+    }
+    if (rows > dec->tokens_cap) {
+        CU(dec, cudaStreamSynchronize(dec->stream));
+        dev_free(dec, dec->d_tokens);
+        if (dec->h_tokens) cudaFreeHost(dec->h_tokens);
+        dec->d_tokens = nullptr; dec->h_tokens = nullptr; dec->tokens_cap = 0;
+        if ((rc = dev_alloc(dec, (void**)&dec->d_tokens, (size_t)rows * 4, false))) return rc;
+        CU(dec, cudaMallocHost((void**)&dec->h_tokens, (size_t)rows * 4));
+        dec->tokens_cap = rows;
+    }
+    return TNSR_B200_OK;
+}
+
+// ---- one step on the strict f32 path -----------------------------------------
+int step_strict(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, uint32_t position, uint32_t logit_rows) {
+    const tnsr_b200_config& c = dec->cfg;
+    const uint32_t d = c.embed_dim, f = c.feed_forward_dim, H = c.num_heads, B = c.batch, rows = B * chunk;
+    cudaStream_t st = dec->stream;
+    const int kvdt = dec->kv_bf16 ? TNSR_B200_BF16 : TNSR_B200_F32;
+    RUN(dec, launch_embedding(dec->tok, dec->pos, d_tokens, dec->h, rows, chunk, position, nullptr, c.vocab_size, d,
+                              TNSR_B200_F32, dec->d_status, st));
+    float* n = (float*)dec->n; float* q = (float*)dec->q; float* att = (float*)dec->att; float* ff = (float*)dec->ff;
+    for (Layer& L : dec->layers) {
+        RUN(dec, launch_layernorm(dec->h, L.ln1w, L.ln1b, n, rows, d, c.layer_norm_epsilon, TNSR_B200_F32, true, st));
+        GemmEpilogue eq;
+        eq.bias = L.bq;
+        eq.round_bf16 = dec->kv_bf16;
+        RUN(dec, launch_gemm_strict(n, (const float*)L.wq, q, d, rows, d, d, false, eq, st));
+        GemmEpilogue ek;
+        ek.round_bf16 = dec->kv_bf16;
+        ek.out_dtype = kvdt;
+        ek.rows_per_session = chunk; ek.out_session_rows = c.capacity; ek.row_offset = position;
+        ek.bias = L.bk;
+        RUN(dec, launch_gemm_strict(n, (const float*)L.wk, L.kcache, d, rows, d, d, false, ek, st));
+        ek.bias = L.bv;
+        RUN(dec, launch_gemm_strict(n, (const float*)L.wv, L.vcache, d, rows, d, d, false, ek, st));
+        RUN(dec, launch_attention_strict(q, L.kcache, L.vcache, att, B, chunk, position, nullptr, c.capacity, H, d / H, kvdt,
+                                         dec->kv_bf16, st));
+        GemmEpilogue eo;
+        eo.bias = L.bo; eo.residual = dec->h; eo.ldr = d;
+        RUN(dec, launch_gemm_strict(att, (const float*)L.wo, dec->h, d, rows, d, d, false, eo, st));
+        RUN(dec, launch_layernorm(dec->h, L.ln2w, L.ln2b, n, rows, d, c.layer_norm_epsilon, TNSR_B200_F32, true, st));
+        if (dec->swiglu) {
+            GemmEpilogue eg; eg.bias = L.b_gate;
+            RUN(dec, launch_gemm_strict(n, (const float*)L.w_gate, ff, f, rows, d, f, false, eg, st));
+            GemmEpilogue eu; eu.bias = L.b_up;
+            RUN(dec, launch_gemm_strict(n, (const float*)L.w_up, dec->ff2, f, rows, d, f, false, eu, st));
+            RUN(dec, launch_swiglu_strict(ff, (const float*)dec->ff2, ff, (size_t)rows * f, st));
+        } else {
+            GemmEpilogue ei; ei.bias = L.b_in;
+            ei.activation = c.activation == TNSR_B200_ACT_GELU ? ACT_GELU : ACT_RELU;
+            RUN(dec, launch_gemm_strict(n, (const float*)L.w_in, ff, f, rows, d, f, false, ei, st));
+        }
+        GemmEpilogue ef; ef.bias = L.b_out; ef.residual = dec->h; ef.ldr = d;
+        RUN(dec, launch_gemm_strict(ff, (const float*)L.w_out, dec->h, d, rows, f, d, false, ef, st));
+    }
+    const float* src = dec->h;
+    if (logit_rows != rows) {
+        RUN(dec, launch_gather_last_rows(dec->h, dec->hl, B, chunk, d, st));
+        src = dec->hl;
+    }
+    RUN(dec, launch_layernorm(src, dec->fnw, dec->fnb, n, logit_rows, d, c.layer_norm_epsilon, TNSR_B200_F32, true, st));
+    GemmEpilogue el;
+    RUN(dec, launch_gemm_strict(n, (const float*)dec->tok, dec->logits, c.vocab_size, logit_rows, d, c.vocab_size, true, el, st));
+    return TNSR_B200_OK;
+}
+
+// ---- one step on the bf16 tensor-core path -----------------------------------
+int step_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, uint32_t position, uint32_t logit_rows) {
+    const tnsr_b200_config& c = dec->cfg;
+    const uint32_t d = c.embed_dim, f = c.feed_forward_dim, H = c.num_heads, hd = d / H, B = c.batch, rows = B * chunk;
+    cudaStream_t st = dec->stream;
+    bf16* n = (bf16*)dec->n; bf16* q = (bf16*)dec->q; bf16* att = (bf16*)dec->att; bf16* ff = (bf16*)dec->ff;
+    RUN(dec, launch_embedding(dec->tok, dec->pos, d_tokens, dec->h, rows, chunk, position, nullptr, c.vocab_size, d,
+                              TNSR_B200_BF16, dec->d_status, st));
+    const bool fast_decode = chunk == 1 && dec->attn_ws && decode_attention_supported(H, hd);
+    bool planned = false;
+    for (Layer& L : dec->layers) {
+        RUN(dec, launch_layernorm(dec->h, L.ln1w, L.ln1b, n, rows, d, c.layer_norm_epsilon, TNSR_B200_BF16, false, st));
+        GemmEpilogue eq;
+        eq.bias = L.bqkv;
+        GemmQkvTargets tg;
+        tg.q = q; tg.k_cache = (bf16*)L.kcache; tg.v_cache = (bf16*)L.vcache;
+        tg.d = d; tg.chunk = chunk; tg.capacity = c.capacity; tg.position = position;
+        RUN(dec, launch_gemm_bf16(n, L.wqkv, nullptr, 0, rows, 3 * d, d, GEMM_QKV, eq, &tg, dec->d_status, st));
+        if (fast_decode) {
+            // every session holds position + 1 keys; the item list is the same for all layers of this step
+            RUN(dec, launch_decode_attention_ex(q, (const bf16*)L.kcache, (const bf16*)L.vcache, nullptr, nullptr, position + 1,
+                                                att, dec->attn_ws, dec->attn_ws_bytes, B, c.capacity, H, hd, !planned,
+                                                dec->d_status, st));
+            planned = true;
+        } else if (chunk > 1 && prefill_attention_supported(hd)) {
+            RUN(dec, launch_prefill_attention(q, (const bf16*)L.kcache, (const bf16*)L.vcache, att, B, chunk, position, nullptr,
+                                              c.capacity, H, hd, st));
+        } else {
+            RUN(dec, launch_attention_generic(q, (const bf16*)L.kcache, (const bf16*)L.vcache, att, B, chunk, position, nullptr,
+                                              c.capacity, H, hd, st));
+        }
+        GemmEpilogue eo;
+        eo.bias = L.bo; eo.residual = dec->h; eo.ldr = d; eo.out_dtype = TNSR_B200_F32;
+        RUN(dec, launch_gemm_bf16(att, (const bf16*)L.wo, dec->h, d, rows, d, d, GEMM_PLAIN, eo, nullptr, dec->d_status, st));
+        RUN(dec, launch_layernorm(dec->h, L.ln2w, L.ln2b, n, rows, d, c.layer_norm_epsilon, TNSR_B200_BF16, false, st));
+        if (dec->swiglu) {
+            if (dec->fused_gu) {
+                GemmEpilogue eg; eg.bias = L.bgu; eg.out_dtype = TNSR_B200_BF16;
+                RUN(dec, launch_gemm_bf16(n, L.wgu, ff, f, rows, 2 * f, d, GEMM_SWIGLU, eg, nullptr, dec->d_status, st));
+            } else {
+                GemmEpilogue eg; eg.bias = L.b_gate; eg.out_dtype = TNSR_B200_BF16;
+                RUN(dec, launch_gemm_bf16(n, (const bf16*)L.w_gate, ff, f, rows, f, d, GEMM_PLAIN, eg, nullptr, dec->d_status, st));
+                GemmEpilogue eu; eu.bias = L.b_up; eu.out_dtype = TNSR_B200_BF16;
+                RUN(dec, launch_gemm_bf16(n, (const bf16*)L.w_up, dec->ff2, f, rows, f, d, GEMM_PLAIN, eu, nullptr, dec->d_status, st));
+                RUN(dec, launch_swiglu(ff, (const bf16*)dec->ff2, ff, (uint64_t)rows * f, st));
+            }
+        } else {
+            GemmEpilogue ei; ei.bias = L.b_in; ei.out_dtype = TNSR_B200_BF16;
+            ei.activation = c.activation == TNSR_B200_ACT_GELU ? ACT_GELU : ACT_RELU;
+            RUN(dec, launch_gemm_bf16(n, (const bf16*)L.w_in, ff, f, rows, f, d, GEMM_PLAIN, ei, nullptr, dec->d_status, st));
+        }
+        GemmEpilogue ef; ef.bias = L.b_out; ef.residual = dec->h; ef.ldr = d; ef.out_dtype = TNSR_B200_F32;
+        RUN(dec, launch_gemm_bf16(ff, (const bf16*)L.w_out, dec->h, d, rows, d, f, GEMM_PLAIN, ef, nullptr, dec->d_status, st));
+    }
+    const float* src = dec->h;
+    if (logit_rows != rows) {
+        RUN(dec, launch_gather_last_rows(dec->h, dec->hl, B, chunk, d, st));
+        src = dec->hl;
+    }
+    RUN(dec, launch_layernorm(src, dec->fnw, dec->fnb, n, logit_rows, d, c.layer_norm_epsilon, TNSR_B200_BF16, false, st));
+    GemmEpilogue el; el.out_dtype = TNSR_B200_F32;
+    // the tied head: the token table [vocab, d] already is the K-major operand
+    RUN(dec, launch_gemm_bf16(n, (const bf16*)dec->tok, dec->logits, c.vocab_size, logit_rows, c.vocab_size, d, GEMM_PLAIN, el,
+                              nullptr, dec->d_status, st));
+    return TNSR_B200_OK;
+}
+
+int run_step(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, uint32_t position, uint32_t* d_argmax_out) {
+    const tnsr_b200_config& c = dec->cfg;
+    const uint32_t rows = c.batch * chunk;
+    const uint32_t logit_rows = c.logits_mode == TNSR_B200_LOGITS_ALL ? rows : c.batch;
+    int rc = dec->bf16_path ? step_bf16(dec, d_tokens, chunk, position, logit_rows)
+                            : step_strict(dec, d_tokens, chunk, position, logit_rows);
+    if (rc) return rc;
+    if (d_argmax_out) {
+        // last position of every session
+        const float* base = dec->logits;
+        uint32_t stride = c.vocab_size;
+        if (logit_rows == rows && chunk > 1) {
+            base = dec->logits + (size_t)(chunk - 1) * c.vocab_size;
+            stride = chunk * c.vocab_size;
+        }
+        RUN(dec, launch_argmax(base, d_argmax_out, c.batch, c.vocab_size, stride, dec->stream));
+    }
+    return TNSR_B200_OK;
+}
+
+int validate_config(const tnsr_b200_config* c, std::string& why) {
+    if (!c) { why = "null configuration"; return TNSR_B200_ERR_INVALID_ARGUMENT; }
+    if (c->vocab_size == 0 || c->max_sequence_length == 0 || c->embed_dim == 0 || c->num_layers == 0 ||
+        c->feed_forward_dim == 0 || c->num_heads == 0 || c->embed_dim % c->num_heads != 0 ||
+        !(c->layer_norm_epsilon > 0.0f) || !std::isfinite(c->layer_norm_epsilon)) {
+        why = "invalid model configuration";
+        return TNSR_B200_ERR_INVALID_ARGUMENT;
+    }
+    if (c->activation > TNSR_B200_ACT_SWIGLU || c->weight_dtype > TNSR_B200_BF16 || c->kv_dtype > TNSR_B200_BF16 ||
+        c->logits_mode > TNSR_B200_LOGITS_NONE) {
+        why = "invalid enum value in configuration";
+        return TNSR_B200_ERR_INVALID_ARGUMENT;
+    }
+    if (c->weight_dtype == TNSR_B200_BF16 && c->kv_dtype != TNSR_B200_BF16) {
+        why = "bf16 weights require a bf16 K/V cache";
+        return TNSR_B200_ERR_INVALID_ARGUMENT;
+    }
+    if (c->batch == 0) { why = "decoder batch size must be non-zero"; return TNSR_B200_ERR_INVALID_ARGUMENT; }
+    if (c->capacity == 0 || c->capacity > c->max_sequence_length) {
+        why = "decoder capacity must fit the model context";
+        return TNSR_B200_ERR_INVALID_ARGUMENT;
+    }
+    uint64_t elements, bytes, total;
+    if (mul_overflow((uint64_t)c->batch * c->capacity, c->embed_dim, &elements) || mul_overflow(elements, 4, &bytes) ||
+        mul_overflow(bytes, 2ull * c->num_layers, &total) || (uint64_t)c->batch * c->capacity > 0xffffffffull) {
+        why = "decoder cache size overflow";
+        return TNSR_B200_ERR_INVALID_ARGUMENT;
+    }
+    return TNSR_B200_OK;
+}
+
+}  // namespace
+
+// ==============================================================================
+// C ABI
+// ==============================================================================
+extern "C" {
+
+const char* tnsr_b200_version(void) { return "tnsr_b200 0.1 (sm_100a)"; }
+
+int tnsr_b200_device_count(void) {
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        set_thread_error(std::string("cudaGetDeviceCount: ") + cudaGetErrorString(e));
+        return e == cudaErrorNoDevice ? 0 : TNSR_B200_ERR_NO_DEVICE;
+    }
+    return n;
+}
+
+const char* tnsr_b200_last_error(const tnsr_b200_decoder* dec) { return dec ? dec->error.c_str() : thread_error(); }
+
+uint64_t tnsr_b200_kernel_launches(void) { return g_launches.load(); }
+
+int tnsr_b200_set_gemm_engine(int engine) {
+    if (engine < 0 || engine > 2) return TNSR_B200_ERR_INVALID_ARGUMENT;
+    g_gemm_engine = engine;
+    return TNSR_B200_OK;
+}
+
+int tnsr_b200_decoder_create(const tnsr_b200_config* config, tnsr_b200_decoder** out) {
+    if (!out) return fail(nullptr, TNSR_B200_ERR_INVALID_ARGUMENT, "null output handle");
+    *out = nullptr;
+    std::string why;
+    int rc = validate_config(config, why);
+    if (rc) return fail(nullptr, rc, why);
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return fail(nullptr, TNSR_B200_ERR_NO_DEVICE, "initialize CUDA decoder: no CUDA device");
+    }
+    if (config->device < 0 || config->device >= count)
+        return fail(nullptr, TNSR_B200_ERR_NO_DEVICE, "initialize CUDA decoder: device ordinal out of range");
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, config->device) != cudaSuccess || prop.major < 10) {
+        cudaGetLastError();
+        return fail(nullptr, TNSR_B200_ERR_NO_DEVICE, "initialize CUDA decoder: an sm_100 class device is required");
+    }
+    tnsr_b200_decoder* dec = new (std::nothrow) tnsr_b200_decoder();
+    if (!dec) return fail(nullptr, TNSR_B200_ERR_OUT_OF_MEMORY, "host allocation failed");
+    dec->cfg = *config;
+    dec->bf16_path = config->weight_dtype == TNSR_B200_BF16;
+    dec->kv_bf16 = config->kv_dtype == TNSR_B200_BF16;
+    dec->swiglu = config->activation == TNSR_B200_ACT_SWIGLU;
+    dec->fused_gu = dec->bf16_path && dec->swiglu && config->feed_forward_dim % 16 == 0;
+    auto bail = [&](int code) {
+        std::string msg = dec->error;
+        tnsr_b200_decoder_destroy(dec);
+        set_thread_error(msg);
+        return code;
+    };
+    if (cudaSetDevice(config->device) != cudaSuccess) return bail(cuda_fail(dec, cudaGetLastError(), "cudaSetDevice"));
+    cudaError_t e = cudaStreamCreateWithFlags(&dec->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) return bail(cuda_fail(dec, e, "cudaStreamCreate"));
+    describe_params(dec);
+    if ((rc = allocate_weights(dec))) return bail(rc);
+    const uint64_t d = config->embed_dim;
+    if ((rc = dev_alloc(dec, (void**)&dec->hl, (size_t)config->batch * d * 4, false))) return bail(rc);
+    if ((rc = dev_alloc(dec, (void**)&dec->d_argmax, (size_t)config->batch * 4, true))) return bail(rc);
+    if ((rc = dev_alloc(dec, (void**)&dec->d_status, 16, true))) return bail(rc);
+    if (cudaMallocHost((void**)&dec->h_argmax, (size_t)config->batch * 4) != cudaSuccess ||
+        cudaMallocHost((void**)&dec->h_status, 16) != cudaSuccess)
+        return bail(cuda_fail(dec, cudaGetLastError(), "cudaMallocHost"));
+    *dec->h_status = 0;
+    if (dec->bf16_path && decode_attention_supported(config->num_heads, config->embed_dim / config->num_heads)) {
+        dec->attn_ws_bytes = decode_attention_workspace_bytes(config->batch, config->capacity, config->num_heads,
+                                                              config->embed_dim / config->num_heads);
+        if ((rc = dev_alloc(dec, &dec->attn_ws, dec->attn_ws_bytes, true))) return bail(rc);
+    }
+    if (dec->bf16_path) {
+        dec->host_bqkv.assign((size_t)config->num_layers * 3 * d, 0.0f);
+        if (dec->fused_gu) dec->host_bgu.assign((size_t)config->num_layers * 2 * config->feed_forward_dim, 0.0f);
+    }
+    e = cudaStreamSynchronize(dec->stream);
+    if (e != cudaSuccess) return bail(cuda_fail(dec, e, "cudaStreamSynchronize"));
+    *out = dec;
+    return TNSR_B200_OK;
+}
+
+void tnsr_b200_decoder_destroy(tnsr_b200_decoder* dec) {
+    if (!dec) return;
+    cudaSetDevice(dec->cfg.device);
+    if (dec->stream) cudaStreamSynchronize(dec->stream);
+    for (void* p : dec->allocations) cudaFree(p);
+    if (dec->h_tokens) cudaFreeHost(dec->h_tokens);
+    if (dec->h_argmax) cudaFreeHost(dec->h_argmax);
+    if (dec->h_status) cudaFreeHost(dec->h_status);
+    if (dec->h_stage) cudaFreeHost(dec->h_stage);
+    if (dec->stream) cudaStreamDestroy(dec->stream);
+    cudaGetLastError();
+    delete dec;
+}
+
+uint32_t tnsr_b200_decoder_param_count(const tnsr_b200_decoder* dec) { return dec ? (uint32_t)dec->params.size() : 0; }
+
+uint64_t tnsr_b200_decoder_param_elems(const tnsr_b200_decoder* dec, uint32_t index) {
+    return (dec && index < dec->params.size()) ? dec->params[index].elems : 0;
+}
+
+int tnsr_b200_decoder_upload(tnsr_b200_decoder* dec, uint32_t index, const float* host, uint64_t elems) {
+    if (!dec) return fail(nullptr, TNSR_B200_ERR_INVALID_ARGUMENT, "null decoder");
+    if (index >= dec->params.size() || !host) return fail(dec, TNSR_B200_ERR_INVALID_ARGUMENT, "parameter index or pointer invalid");
+    const ParamInfo& p = dec->params[index];
+    if (elems != p.elems) return fail(dec, TNSR_B200_ERR_INVALID_ARGUMENT, "parameter length mismatch");
+    CU(dec, cudaSetDevice(dec->cfg.device));
+    const tnsr_b200_config& c = dec->cfg;
+    const uint32_t d = c.embed_dim, f = c.feed_forward_dim;
+    cudaStream_t st = dec->stream;
+    Layer* L = p.kind == P_TOK || p.kind == P_POS ? nullptr : (p.layer < dec->layers.size() ? &dec->layers[p.layer] : nullptr);
+    const size_t bytes = (size_t)elems * 4;
+    // f32 destinations (vectors on both paths, everything on the strict path)
+    auto vec_target = [&]() -> float* {
+        if (p.slot == 100) return dec->fnw;
+        if (p.slot == 101) return dec->fnb;
+        switch (p.slot) {
+            case 0: return L->bo;
+            case 1: return L->ln1w;
+            case 2: return L->ln1b;
+            case 3: return L->ln2w;
+            case 4: return L->ln2b;
+            default: return L->b_out;
+        }
+    };
+    auto copy_f32 = [&](void* dst) -> int {
+        CU(dec, cudaMemcpyAsync(dst, host, bytes, cudaMemcpyHostToDevice, st));
+        CU(dec, cudaStreamSynchronize(st));  // `host` is pageable and not retained
+        return TNSR_B200_OK;
+    };
+    if (p.kind == P_VEC) return copy_f32(vec_target());
+    if (!dec->bf16_path) {
+        switch (p.kind) {
+            case P_TOK: return copy_f32(dec->tok);
+            case P_POS: return copy_f32(dec->pos);
+            case P_QKV_W: return copy_f32(p.slot == 0 ? L->wq : p.slot == 1 ? L->wk : L->wv);
+            case P_QKV_B: return copy_f32(p.slot == 0 ? L->bq : p.slot == 1 ? L->bk : L->bv);
+            case P_O_W: return copy_f32(L->wo);
+            case P_FF_IN_W: return copy_f32(L->w_in);
+            case P_FF_IN_B: return copy_f32(L->b_in);
+            case P_FF_OUT_W: return copy_f32(L->w_out);
+            case P_GATE_W: return copy_f32(L->w_gate);
+            case P_GATE_B: return copy_f32(L->b_gate);
+            case P_UP_W: return copy_f32(L->w_up);
+            case P_UP_B: return copy_f32(L->b_up);
+            default: return fail(dec, TNSR_B200_ERR_INVALID_ARGUMENT, "unknown parameter kind");
+        }
+    }
+    // bf16 path: biases stay f32 (possibly packed); matrices are staged in f32 on the device, then repacked
+    if (p.kind == P_QKV_B) {
+        float* hb = dec->host_bqkv.data() + ((size_t)p.layer * 3 + p.slot) * d;
+        std::memcpy(hb, host, bytes);
+        CU(dec, cudaMemcpyAsync(L->bqkv + (size_t)p.slot * d, hb, bytes, cudaMemcpyHostToDevice, st));
+        CU(dec, cudaStreamSynchronize(st));
+        return TNSR_B200_OK;
+    }
+    if (p.kind == P_FF_IN_B) return copy_f32(L->b_in);
+    if (p.kind == P_GATE_B || p.kind == P_UP_B) {
+        if (!dec->fused_gu) return copy_f32(p.kind == P_GATE_B ? L->b_gate : L->b_up);
+        float* hb = dec->host_bgu.data() + (size_t)p.layer * 2 * f;
+        const uint32_t off = p.kind == P_GATE_B ? 0 : 16;
+        for (uint32_t cidx = 0; cidx < f; ++cidx) hb[(cidx / 16) * 32 + off + cidx % 16] = host[cidx];
+        CU(dec, cudaMemcpyAsync(L->bgu, hb, (size_t)2 * f * 4, cudaMemcpyHostToDevice, st));
+        CU(dec, cudaStreamSynchronize(st));
+        return TNSR_B200_OK;
+    }
+    if (bytes > dec->d_stage_bytes) {
+        CU(dec, cudaStreamSynchronize(st));
+        dev_free(dec, dec->d_stage);
+        dec->d_stage = nullptr;
+        dec->d_stage_bytes = 0;
+        int rc = dev_alloc(dec, (void**)&dec->d_stage, bytes, false);
+        if (rc) return rc;
+        dec->d_stage_bytes = bytes;
+    }
+    CU(dec, cudaMemcpyAsync(dec->d_stage, host, bytes, cudaMemcpyHostToDevice, st));
+    int rc = TNSR_B200_OK;
+    switch (p.kind) {
+        case P_TOK: rc = launch_f32_to_bf16(dec->d_stage, (bf16*)dec->tok, elems, st); break;
+        case P_POS: rc = launch_f32_to_bf16(dec->d_stage, (bf16*)dec->pos, elems, st); break;
+        case P_QKV_W: rc = launch_transpose_f32_to_bf16_mapped(dec->d_stage, L->wqkv, d, d, p.slot * d, d, d, st); break;
+        case P_O_W: rc = launch_transpose_f32_to_bf16(dec->d_stage, (bf16*)L->wo, d, d, st); break;
+        case P_FF_IN_W: rc = launch_transpose_f32_to_bf16(dec->d_stage, (bf16*)L->w_in, d, f, st); break;
+        case P_FF_OUT_W: rc = launch_transpose_f32_to_bf16(dec->d_stage, (bf16*)L->w_out, f, d, st); break;
+        case P_GATE_W:
+            rc = dec->fused_gu ? launch_transpose_f32_to_bf16_mapped(dec->d_stage, L->wgu, d, f, 0, 16, 32, st)
+                               : launch_transpose_f32_to_bf16(dec->d_stage, (bf16*)L->w_gate, d, f, st);
+            break;
+        case P_UP_W:
+            rc = dec->fused_gu ? launch_transpose_f32_to_bf16_mapped(dec->d_stage, L->wgu, d, f, 16, 16, 32, st)
+                               : launch_transpose_f32_to_bf16(dec->d_stage, (bf16*)L->w_up, d, f, st);
+            break;
+        default: return fail(dec, TNSR_B200_ERR_INVALID_ARGUMENT, "unknown parameter kind");
+    }
+    if (rc) { dec->error = thread_error(); return rc; }
+    CU(dec, cudaStreamSynchronize(st));
+    return TNSR_B200_OK;
+}
+
+int tnsr_b200_decoder_reset(tnsr_b200_decoder* dec) {
+    if (!dec) return fail(nullptr, TNSR_B200_ERR_INVALID_ARGUMENT, "null decoder");
+    CU(dec, cudaSetDevice(dec->cfg.device));
+    const size_t cache_bytes = (size_t)dec->cfg.batch * dec->cfg.capacity * dec->cfg.embed_dim * kv_elt(dec);
+    for (Layer& L : dec->layers) {
+        CU(dec, cudaMemsetAsync(L.kcache, 0, cache_bytes, dec->stream));
+        CU(dec, cudaMemsetAsync(L.vcache, 0, cache_bytes, dec->stream));
+    }
+    CU(dec, cudaMemsetAsync(dec->d_status, 0, 16, dec->stream));
+    CU(dec, cudaStreamSynchronize(dec->stream));
+    dec->failed = false;
+    return TNSR_B200_OK;
+}
+
+static int check_step_args(tnsr_b200_decoder* dec, uint32_t chunk, uint32_t position) {
+    if (dec->failed) return fail(dec, TNSR_B200_ERR_FAILED_STATE, "decoder execution failed; reset the cache before reuse");
+    if (chunk == 0) return fail(dec, TNSR_B200_ERR_INVALID_ARGUMENT, "tokens must be a nonempty rectangular [batch, sequence] chunk");
+    if (position > dec->cfg.capacity || chunk > dec->cfg.capacity - position)
+        return fail(dec, TNSR_B200_ERR_CAPACITY, "decoder context capacity exceeded");
+    if ((uint64_t)dec->cfg.batch * chunk > 0x7fffffffull) return fail(dec, TNSR_B200_ERR_UNSUPPORTED, "chunk too large");
+    return TNSR_B200_OK;
+}
+
+static int device_status_to_code(tnsr_b200_decoder* dec, int status) {
+    switch (status) {
+        case DEV_OK: return TNSR_B200_OK;
+        case DEV_TOKEN_RANGE: return fail(dec, TNSR_B200_ERR_TOKEN_RANGE, "decoder token is outside the vocabulary");
+        case DEV_TIMEOUT: dec->failed = true; return fail(dec, TNSR_B200_ERR_TIMEOUT, "a device-side wait timed out");
+        default: dec->failed = true; return fail(dec, TNSR_B200_ERR_CUDA, "device reported an invalid session length");
+    }
+}
+
+int tnsr_b200_decoder_decode(tnsr_b200_decoder* dec, const uint32_t* tokens, uint32_t chunk, uint32_t position,
+                             float* logits_out, uint32_t* argmax_out) {
+    if (!dec) return fail(nullptr, TNSR_B200_ERR_INVALID_ARGUMENT, "null decoder");
+    int rc = check_step_args(dec, chunk, position);
+    if (rc) return rc;
+    const tnsr_b200_config& c = dec->cfg;
+    if (!tokens) return fail(dec, TNSR_B200_ERR_INVALID_ARGUMENT, "null token pointer");
+    if (c.logits_mode == TNSR_B200_LOGITS_NONE && logits_out)
+        return fail(dec, TNSR_B200_ERR_INVALID_ARGUMENT, "logits_out must be NULL when logits_mode is NONE");
+    const uint32_t rows = c.batch * chunk;
+    for (uint32_t i = 0; i < rows; ++i)
+        if (tokens[i] >= c.vocab_size) return fail(dec, TNSR_B200_ERR_TOKEN_RANGE, "decoder token is outside the vocabulary");
+    CU(dec, cudaSetDevice(c.device));
+    const uint32_t logit_rows = c.logits_mode == TNSR_B200_LOGITS_ALL ? rows : c.batch;
+    if ((rc = ensure_rows(dec, rows, logit_rows))) return rc;
+    dec->failed = true;  // poisoned until the step has completed (src/nn/kv_cache.rs:331)
+    std::memcpy(dec->h_tokens, tokens, (size_t)rows * 4);
+    CU(dec, cudaMemcpyAsync(dec->d_tokens, dec->h_tokens, (size_t)rows * 4, cudaMemcpyHostToDevice, dec->stream));
+    if ((rc = run_step(dec, dec->d_tokens, chunk, position, argmax_out ? dec->d_argmax : nullptr))) return rc;
+    if (logits_out)
+        CU(dec, cudaMemcpyAsync(logits_out, dec->logits, (size_t)logit_rows * c.vocab_size * 4, cudaMemcpyDeviceToHost, dec->stream));
+    if (argmax_out)
+        CU(dec, cudaMemcpyAsync(dec->h_argmax, dec->d_argmax, (size_t)c.batch * 4, cudaMemcpyDeviceToHost, dec->stream));
+    CU(dec, cudaMemcpyAsync(dec->h_status, dec->d_status, 4, cudaMemcpyDeviceToHost, dec->stream));
+    CU(dec, cudaStreamSynchronize(dec->stream));
+    if (*dec->h_status != DEV_OK) {
+        int status = *dec->h_status;
+        cudaMemsetAsync(dec->d_status, 0, 16, dec->stream);
+        return device_status_to_code(dec, status);
+    }
+    if (argmax_out) std::memcpy(argmax_out, dec->h_argmax, (size_t)c.batch * 4);
+    dec->failed = false;
+    return TNSR_B200_OK;
+}
+
+int tnsr_b200_decoder_decode_device(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, uint32_t position,
+                                    uint32_t* d_argmax_out) {
+    if (!dec) return fail(nullptr, TNSR_B200_ERR_INVALID_ARGUMENT, "null decoder");
+    int rc = check_step_args(dec, chunk, position);
+    if (rc) return rc;
+    if (!d_tokens) return fail(dec, TNSR_B200_ERR_INVALID_ARGUMENT, "null token pointer");
+    const tnsr_b200_config& c = dec->cfg;
+    CU(dec, cudaSetDevice(c.device));
+    const uint32_t rows = c.batch * chunk;
+    const uint32_t logit_rows = c.logits_mode == TNSR_B200_LOGITS_ALL ? rows : c.batch;
+    if ((rc = ensure_rows(dec, rows, logit_rows))) return rc;
+    return run_step(dec, d_tokens, chunk, position, d_argmax_out);
+}
+
+int tnsr_b200_decoder_synchronize(tnsr_b200_decoder* dec) {
+    if (!dec) return fail(nullptr, TNSR_B200_ERR_INVALID_ARGUMENT, "null decoder");
+    CU(dec, cudaSetDevice(dec->cfg.device));
+    CU(dec, cudaMemcpyAsync(dec->h_status, dec->d_status, 4, cudaMemcpyDeviceToHost, dec->stream));
+    CU(dec, cudaStreamSynchronize(dec->stream));
+    if (*dec->h_status != DEV_OK) {
+        int status = *dec->h_status;
+        cudaMemsetAsync(dec->d_status, 0, 16, dec->stream);
+        return device_status_to_code(dec, status);
+    }
+    return TNSR_B200_OK;
+}
+
+void* tnsr_b200_decoder_stream(tnsr_b200_decoder* dec) { return dec ? (void*)dec->stream : nullptr; }
+
+int tnsr_b200_decoder_read_cache(tnsr_b200_decoder* dec, uint32_t index, float* host_out) {
+    if (!dec || !host_out) return fail(dec, TNSR_B200_ERR_INVALID_ARGUMENT, "null argument");
+    if (index >= 2 * dec->cfg.num_layers) return fail(dec, TNSR_B200_ERR_INVALID_ARGUMENT, "cache index out of range");
+    CU(dec, cudaSetDevice(dec->cfg.device));
+    const uint64_t elems = (uint64_t)dec->cfg.batch * dec->cfg.capacity * dec->cfg.embed_dim;
+    Layer& L = dec->layers[index / 2];
+    const void* src = (index & 1) ? L.vcache : L.kcache;
+    if (!dec->kv_bf16) {
+        CU(dec, cudaMemcpyAsync(host_out, src, elems * 4, cudaMemcpyDeviceToHost, dec->stream));
+        CU(dec, cudaStreamSynchronize(dec->stream));
+        return TNSR_B200_OK;
+    }
+    float* tmp = nullptr;
+    int rc = dev_alloc(dec, (void**)&tmp, elems * 4, false);
+    if (rc) return rc;
+    rc = launch_bf16_to_f32((const bf16*)src, tmp, elems, dec->stream);
+    if (rc == TNSR_B200_OK) {
+        cudaError_t e = cudaMemcpyAsync(host_out, tmp, elems * 4, cudaMemcpyDeviceToHost, dec->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(dec->stream);
+        if (e != cudaSuccess) rc = cuda_fail(dec, e, "read_cache copy");
+    } else {
+        dec->error = thread_error();
+    }
+    cudaStreamSynchronize(dec->stream);
+    dev_free(dec, tmp);
+    return rc;
+}
+
+int tnsr_b200_decoder_write_cache(tnsr_b200_decoder* dec, uint32_t index, const float* host_in) {
+    if (!dec || !host_in) return fail(dec, TNSR_B200_ERR_INVALID_ARGUMENT, "null argument");
+    if (index >= 2 * dec->cfg.num_layers) return fail(dec, TNSR_B200_ERR_INVALID_ARGUMENT, "cache index out of range");
+    CU(dec, cudaSetDevice(dec->cfg.device));
+    const uint64_t elems = (uint64_t)dec->cfg.batch * dec->cfg.capacity * dec->cfg.embed_dim;
+    Layer& L = dec->layers[index / 2];
+    void* dst = (index & 1) ? L.vcache : L.kcache;
+    if (!dec->kv_bf16) {
+        CU(dec, cudaMemcpyAsync(dst, host_in, elems * 4, cudaMemcpyHostToDevice, dec->stream));
+        CU(dec, cudaStreamSynchronize(dec->stream));
+        return TNSR_B200_OK;
+    }
+    float* tmp = nullptr;
+    int rc = dev_alloc(dec, (void**)&tmp, elems * 4, false);
+    if (rc) return rc;
+    cudaError_t e = cudaMemcpyAsync(tmp, host_in, elems * 4, cudaMemcpyHostToDevice, dec->stream);
+    if (e != cudaSuccess) rc = cuda_fail(dec, e, "write_cache copy");
+    if (rc == TNSR_B200_OK) {
+        rc = launch_f32_to_bf16(tmp, (bf16*)dst, elems, dec->stream);
+        if (rc) dec->error = thread_error();
+    }
+    cudaStreamSynchronize(dec->stream);
+    dev_free(dec, tmp);
+    return rc;
+}
+
+}  // extern "C"

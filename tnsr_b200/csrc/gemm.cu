@@ -1,0 +1,670 @@
+// bf16 GEMM with f32 accumulation: out = epilogue(a[m,k] . bt[n,k]^T).
+//
+// Two engines share one epilogue:
+//  * gemm_tc_kernel   -- the Blackwell path: TMA (cp.async.bulk.tensor, 128-byte
+//    swizzle, one copy per CTA, no cluster forms) feeds a shared-memory ring,
+//    one thread issues tcgen05.mma (M=128, N=BN, K=16 per instruction) into
+//    double-buffered TMEM accumulators, four epilogue warps drain them with
+//    tcgen05.ld while the next tile's main loop runs.  Persistent over tiles.
+//  * gemm_simple_kernel -- CUDA-core kernel for shapes TMA cannot address
+//    (k not a multiple of 8, unaligned pointers) and as the cross-check of the
+//    tensor-core engine.
+//
+// This replaces the reference's tiled matmul path (wmma/mma.sync 64x64x32 tiles
+// with cp.async double buffering and fused epilogues: src/tile/matmul_schedule.rs:
+// 487-646, src/ptx/graph/matmul.rs:4-129, src/tile/graph.rs:712-1107).
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace tb {
+
+int g_gemm_engine = 0;
+
+struct EpiParams {
+    GemmEpilogue ep;
+    GemmQkvTargets qkv;
+    void* out;
+    uint32_t ldc;
+    uint32_t m, n;  // n = columns of the accumulator (packed width for SWIGLU)
+};
+
+// ---- epilogue: scalar forms ---------------------------------------------------
+__device__ __forceinline__ size_t map_out_row(const GemmEpilogue& ep, uint32_t row) {
+    if (!ep.rows_per_session) return row;
+    uint32_t off = ep.d_row_offset ? *ep.d_row_offset : ep.row_offset;
+    return (size_t)(row / ep.rows_per_session) * ep.out_session_rows + off + row % ep.rows_per_session;
+}
+
+__device__ __forceinline__ void store_plain(const EpiParams& P, uint32_t row, uint32_t col, float acc) {
+    float v = acc;
+    if (P.ep.bias) v += P.ep.bias[col];
+    v = apply_activation(v, P.ep.activation);
+    size_t orow = map_out_row(P.ep, row);
+    if (P.ep.out_dtype == TNSR_B200_BF16) {
+        reinterpret_cast<bf16*>(P.out)[orow * P.ldc + col] = __float2bfloat16_rn(v);
+    } else {
+        if (P.ep.residual) v += P.ep.residual[(size_t)row * P.ep.ldr + col];
+        reinterpret_cast<float*>(P.out)[orow * P.ldc + col] = v;
+    }
+}
+
+__device__ __forceinline__ void store_qkv(const EpiParams& P, uint32_t row, uint32_t col, float acc) {
+    float v = acc;
+    if (P.ep.bias) v += P.ep.bias[col];
+    const uint32_t d = P.qkv.d, which = col / d, c = col % d;
+    if (which == 0) {
+        P.qkv.q[(size_t)row * d + c] = __float2bfloat16_rn(v);
+    } else {
+        uint32_t pos = P.qkv.d_position ? *P.qkv.d_position : P.qkv.position;
+        size_t crow = (size_t)(row / P.qkv.chunk) * P.qkv.capacity + pos + row % P.qkv.chunk;
+        (which == 1 ? P.qkv.k_cache : P.qkv.v_cache)[crow * d + c] = __float2bfloat16_rn(v);
+    }
+}
+
+// g, u: accumulators of packed columns pc and pc + 16; output column oc.
+__device__ __forceinline__ void store_swiglu(const EpiParams& P, uint32_t row, uint32_t pc, uint32_t oc,
+                                             float g, float u) {
+    if (P.ep.bias) {
+        g += P.ep.bias[pc];
+        u += P.ep.bias[pc + 16];
+    }
+    reinterpret_cast<bf16*>(P.out)[(size_t)row * P.ldc + oc] = __float2bfloat16_rn(fast_silu(g) * u);
+}
+
+// ===========================================================================
+// CUDA-core engine: 64x64 tile, 16x16 threads, 4x4 outputs per thread.
+// ===========================================================================
+constexpr int SB = 64, SK = 16;
+
+template <int MODE>
+__global__ void __launch_bounds__(256)
+gemm_simple_kernel(const bf16* __restrict__ a, uint32_t lda, const bf16* __restrict__ bt, EpiParams P, uint32_t k) {
+    __shared__ float as[SK][SB + 4];
+    __shared__ float bs[SK][SB + 4];
+    __shared__ float cs[SB][SB + 1];
+    const uint32_t tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
+    const uint32_t m0 = blockIdx.y * SB, n0 = blockIdx.x * SB;
+    float acc[4][4] = {};
+    for (uint32_t k0 = 0; k0 < k; k0 += SK) {
+        // 64 rows x 16 k per operand = 1024 elements, 4 per thread
+        {
+            uint32_t r = tid / 4, kk = (tid % 4) * 4;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint32_t gk = k0 + kk + i;
+                float va = 0.0f, vb = 0.0f;
+                if (gk < k) {
+                    if (m0 + r < P.m) va = __bfloat162float(a[(size_t)(m0 + r) * lda + gk]);
+                    if (n0 + r < P.n) vb = __bfloat162float(bt[(size_t)(n0 + r) * k + gk]);
+                }
+                as[kk + i][r] = va;
+                bs[kk + i][r] = vb;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int p = 0; p < SK; ++p) {
+            float av[4], bv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { av[i] = as[p][ty * 4 + i]; bv[i] = bs[p][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) cs[ty * 4 + i][tx * 4 + j] = acc[i][j];
+    __syncthreads();
+    if (MODE == GEMM_SWIGLU) {
+        // 64 packed columns = 2 blocks of (16 gate, 16 up) -> 32 output columns
+        for (uint32_t e = tid; e < SB * 32; e += 256) {
+            uint32_t r = e / 32, oc_local = e % 32;
+            uint32_t pc_local = (oc_local / 16) * 32 + oc_local % 16;
+            uint32_t row = m0 + r, pc = n0 + pc_local, oc = n0 / 2 + oc_local;
+            if (row < P.m && pc + 16 < P.n)
+                store_swiglu(P, row, pc, oc, cs[r][pc_local], cs[r][pc_local + 16]);
+        }
+    } else {
+        for (uint32_t e = tid; e < SB * SB; e += 256) {
+            uint32_t r = e / SB, c = e % SB, row = m0 + r, col = n0 + c;
+            if (row < P.m && col < P.n) {
+                if (MODE == GEMM_QKV) store_qkv(P, row, col, cs[r][c]);
+                else store_plain(P, row, col, cs[r][c]);
+            }
+        }
+    }
+}
+
+static int launch_simple(const bf16* a, uint32_t lda, const bf16* bt, const EpiParams& P, uint32_t k, GemmMode mode,
+                         cudaStream_t stream) {
+    dim3 grid(ceil_div(P.n, SB), ceil_div(P.m, SB));
+    if (grid.y > 65535u) {
+        set_thread_error("gemm: too many rows for the CUDA-core engine");
+        return TNSR_B200_ERR_UNSUPPORTED;
+    }
+    switch (mode) {
+        case GEMM_PLAIN: gemm_simple_kernel<GEMM_PLAIN><<<grid, 256, 0, stream>>>(a, lda, bt, P, k); break;
+        case GEMM_QKV: gemm_simple_kernel<GEMM_QKV><<<grid, 256, 0, stream>>>(a, lda, bt, P, k); break;
+        case GEMM_SWIGLU: gemm_simple_kernel<GEMM_SWIGLU><<<grid, 256, 0, stream>>>(a, lda, bt, P, k); break;
+    }
+    count_launch();
+    return check_launch("gemm_simple");
+}
+
+// ===========================================================================
+// tcgen05 engine
+// ===========================================================================
+constexpr int BM = 128;           // rows per tile = TMEM lanes
+constexpr int BK = 64;            // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;        // K per tcgen05.mma for 16-bit operands
+constexpr int TC_THREADS = 192;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // a wait that lasts 2 s gives up
+
+template <int BN>
+struct TcShape {
+    static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+    static constexpr uint32_t A_BYTES = BM * BK * 2;
+    static constexpr uint32_t B_BYTES = BN * BK * 2;
+    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators; power of two
+    static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: returns false (and raises the CTA-wide abort flag) if the
+// barrier does not flip within WAIT_LIMIT_NS or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = global_timer_ns();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - start > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int32_t x, int32_t y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on `bar` once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 32 lanes x 32 columns of 32-bit accumulators: thread i of the warp receives
+// row (lane base + i), columns [col, col + 32).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major operand tile stored as rows of
+// 128 bytes with the 128-byte swizzle TMA applied: 8-row groups are 1024 bytes
+// apart (stride byte offset); the leading byte offset is unused for swizzled
+// K-major tiles; descriptor version 1; swizzle mode 2 (128 B).
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+    uint64_t desc = 0;
+    desc |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+    desc |= (uint64_t)1 << 16;
+    desc |= (uint64_t)(1024 >> 4) << 32;
+    desc |= (uint64_t)1 << 46;
+    desc |= (uint64_t)2 << 61;
+    return desc;
+}
+// Instruction descriptor, kind::f16: f32 accumulator (bit 4), bf16 A (bit 7)
+// and B (bit 10), both K-major (bits 15, 16 clear), N/8 at bit 17, M/16 at bit 24.
+__host__ __device__ constexpr uint32_t make_idesc_bf16(uint32_t bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+struct TcParams {
+    EpiParams epi;
+    uint32_t k;
+    uint32_t tiles_m, tiles_n;
+    int* d_status;
+};
+
+// Grouped tile order: 8 row-tiles share each column-tile before moving on, so a
+// wave of CTAs re-reads few distinct operand tiles from L2.
+__device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n, uint32_t& tm, uint32_t& tn) {
+    constexpr uint32_t GROUP = 8;
+    const uint32_t per_group = GROUP * tiles_n;
+    const uint32_t group = tile / per_group, first = group * GROUP;
+    const uint32_t size = min(tiles_m - first, GROUP);
+    const uint32_t in_group = tile % per_group;
+    tm = first + in_group % size;
+    tn = in_group / size;
+}
+
+// ---- epilogue on 32 consecutive accumulator columns of one row -----------------
+template <int MODE>
+__device__ __forceinline__ void epilogue_chunk(const EpiParams& P, uint32_t row, uint32_t col0, const float* acc) {
+    if (row >= P.m || col0 >= P.n) return;
+    const bool full = col0 + 32 <= P.n;
+    if (MODE == GEMM_SWIGLU) {
+        // 16 gate + 16 up columns -> 16 outputs at column col0 / 2
+        const uint32_t oc0 = col0 / 2;
+        bf16* dst = reinterpret_cast<bf16*>(P.out) + (size_t)row * P.ldc + oc0;
+        if (full && (reinterpret_cast<uintptr_t>(dst) % 16 == 0)) {
+            uint32_t packed[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float g0 = acc[2 * i], g1 = acc[2 * i + 1], u0 = acc[16 + 2 * i], u1 = acc[17 + 2 * i];
+                if (P.ep.bias) {
+                    g0 += __ldg(P.ep.bias + col0 + 2 * i);
+                    g1 += __ldg(P.ep.bias + col0 + 2 * i + 1);
+                    u0 += __ldg(P.ep.bias + col0 + 16 + 2 * i);
+                    u1 += __ldg(P.ep.bias + col0 + 17 + 2 * i);
+                }
+                packed[i] = pack_bf16x2(fast_silu(g0) * u0, fast_silu(g1) * u1);
+            }
+            reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                if (col0 + 16 + i < P.n) store_swiglu(P, row, col0 + i, oc0 + i, acc[i], acc[16 + i]);
+        }
+        return;
+    }
+    if (MODE == GEMM_QKV) {
+        const uint32_t d = P.qkv.d;
+        if (full && d % 32 == 0) {
+            const uint32_t which = col0 / d, c = col0 % d;
+            bf16* dst;
+            if (which == 0) {
+                dst = P.qkv.q + (size_t)row * d + c;
+            } else {
+                uint32_t pos = P.qkv.d_position ? *P.qkv.d_position : P.qkv.position;
+                size_t crow = (size_t)(row / P.qkv.chunk) * P.qkv.capacity + pos + row % P.qkv.chunk;
+                dst = (which == 1 ? P.qkv.k_cache : P.qkv.v_cache) + crow * d + c;
+            }
+            if (reinterpret_cast<uintptr_t>(dst) % 16 == 0) {
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float a = acc[2 * i], b = acc[2 * i + 1];
+                    if (P.ep.bias) { a += __ldg(P.ep.bias + col0 + 2 * i); b += __ldg(P.ep.bias + col0 + 2 * i + 1); }
+                    packed[i] = pack_bf16x2(a, b);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    reinterpret_cast<uint4*>(dst)[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                return;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (col0 + i < P.n) store_qkv(P, row, col0 + i, acc[i]);
+        return;
+    }
+    // GEMM_PLAIN
+    const size_t orow = map_out_row(P.ep, row);
+    if (P.ep.out_dtype == TNSR_B200_BF16) {
+        bf16* dst = reinterpret_cast<bf16*>(P.out) + orow * P.ldc + col0;
+        if (full && (reinterpret_cast<uintptr_t>(dst) % 16 == 0)) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                float a = acc[2 * i], b = acc[2 * i + 1];
+                if (P.ep.bias) { a += __ldg(P.ep.bias + col0 + 2 * i); b += __ldg(P.ep.bias + col0 + 2 * i + 1); }
+                packed[i] = pack_bf16x2(apply_activation(a, P.ep.activation), apply_activation(b, P.ep.activation));
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                reinterpret_cast<uint4*>(dst)[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+            return;
+        }
+    } else {
+        float* dst = reinterpret_cast<float*>(P.out) + orow * P.ldc + col0;
+        const float* res = P.ep.residual ? P.ep.residual + (size_t)row * P.ep.ldr + col0 : nullptr;
+        if (full && (reinterpret_cast<uintptr_t>(dst) % 16 == 0) && (!res || reinterpret_cast<uintptr_t>(res) % 16 == 0)) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float4 v = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+                if (P.ep.bias) {
+                    v.x += __ldg(P.ep.bias + col0 + 4 * i);
+                    v.y += __ldg(P.ep.bias + col0 + 4 * i + 1);
+                    v.z += __ldg(P.ep.bias + col0 + 4 * i + 2);
+                    v.w += __ldg(P.ep.bias + col0 + 4 * i + 3);
+                }
+                v.x = apply_activation(v.x, P.ep.activation);
+                v.y = apply_activation(v.y, P.ep.activation);
+                v.z = apply_activation(v.z, P.ep.activation);
+                v.w = apply_activation(v.w, P.ep.activation);
+                if (res) {
+                    float4 r = reinterpret_cast<const float4*>(res)[i];
+                    v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
+                }
+                reinterpret_cast<float4*>(dst)[i] = v;
+            }
+            return;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+        if (col0 + i < P.n) store_plain(P, row, col0 + i, acc[i]);
+}
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams prm) {
+    using S = TcShape<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    // 128-byte-swizzled tiles want a 1024-byte aligned base
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::STAGES * S::STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + S::STAGES;
+    uint64_t* acc_full = empty_bar + S::STAGES;   // [2]
+    uint64_t* acc_empty = acc_full + 2;           // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t num_tiles = prm.tiles_m * prm.tiles_n;
+    const uint32_t num_kb = (prm.k + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S::STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(acc_full + s, 1); mbar_init(acc_empty + s, 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, S::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                uint32_t tm, tn;
+                tile_coords(tile, prm.tiles_m, prm.tiles_n, tm, tn);
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(empty_bar + stage, phase ^ 1, abort_flag)) { ok = false; break; }
+                    uint8_t* sa = smem + stage * S::STAGE_BYTES;
+                    mbar_expect_tx(full_bar + stage, S::STAGE_BYTES);
+                    tma_load_2d(sa, &map_a, (int32_t)(kb * BK), (int32_t)(tm * BM), full_bar + stage);
+                    tma_load_2d(sa + S::A_BYTES, &map_b, (int32_t)(kb * BK), (int32_t)(tn * BN), full_bar + stage);
+                    if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_bf16(BN);
+            uint32_t stage = 0, phase = 0, it = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
+                const uint32_t ab = it & 1, aphase = (it >> 1) & 1;
+                if (!mbar_wait(acc_empty + ab, aphase ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + ab * BN;
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full_bar + stage, phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + stage * S::STAGE_BYTES);
+                    const uint64_t adesc = make_kmajor_sw128_desc(sa);
+                    const uint64_t bdesc = make_kmajor_sw128_desc(sa + S::A_BYTES);
+#pragma unroll
+                    for (uint32_t kk = 0; kk < BK / UMMA_K; ++kk) {
+                        // advancing K by 16 elements = 32 bytes inside the swizzle row: +2 in the address field
+                        umma_bf16(d_tmem, adesc + kk * 2, bdesc + kk * 2, idesc, (kb | kk) != 0);
+                    }
+                    umma_commit(empty_bar + stage);  // stage reusable once these MMAs have read it
+                    if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) umma_commit(acc_full + ab);
+            }
+        }
+    } else {
+        // ---------------- epilogue warps (TMEM lane quarter = warp % 4) ----------------
+        const uint32_t quarter = warp & 3;
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
+            const uint32_t ab = it & 1, aphase = (it >> 1) & 1;
+            uint32_t tm, tn;
+            tile_coords(tile, prm.tiles_m, prm.tiles_n, tm, tn);
+            if (!mbar_wait(acc_full + ab, aphase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t row = tm * BM + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + ab * BN;
+#pragma unroll 1
+            for (uint32_t c = 0; c < BN; c += 32) {
+                float acc[32];
+                tmem_ld32(taddr + c, acc);
+                tmem_ld_wait();
+                epilogue_chunk<MODE>(prm.epi, row, tn * BN + c, acc);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty + ab);
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // give copies that are still in flight time to land before the CTA's shared memory is released
+        const uint64_t start = global_timer_ns();
+        while (global_timer_ns() - start < 200000ull) __nanosleep(1000);
+        if (threadIdx.x == 0 && prm.d_status) atomicCAS(prm.d_status, DEV_OK, DEV_TIMEOUT);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, S::TMEM_COLS);
+    }
+}
+
+// ---- host: tensor maps ---------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// [rows, cols] bf16 row-major with `ld` elements between rows; box = 64 columns x box_rows rows.
+static bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+static int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <int BN, int MODE>
+static int launch_tc_t(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& prm, cudaStream_t stream) {
+    using S = TcShape<BN>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM_BYTES) != cudaSuccess)
+            return check_launch("gemm_tc attribute");
+        configured = true;
+    }
+    uint32_t tiles = prm.tiles_m * prm.tiles_n;
+    uint32_t grid = tiles < (uint32_t)sm_count() ? tiles : (uint32_t)sm_count();
+    gemm_tc_kernel<BN, MODE><<<grid, TC_THREADS, S::SMEM_BYTES, stream>>>(ma, mb, prm);
+    count_launch();
+    return check_launch("gemm_tc");
+}
+
+template <int BN>
+static int launch_tc_mode(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& prm, GemmMode mode, cudaStream_t stream) {
+    switch (mode) {
+        case GEMM_PLAIN: return launch_tc_t<BN, GEMM_PLAIN>(ma, mb, prm, stream);
+        case GEMM_QKV: return launch_tc_t<BN, GEMM_QKV>(ma, mb, prm, stream);
+        case GEMM_SWIGLU: return launch_tc_t<BN, GEMM_SWIGLU>(ma, mb, prm, stream);
+    }
+    return TNSR_B200_ERR_INVALID_ARGUMENT;
+}
+
+static bool tc_eligible(const bf16* a, uint32_t lda, const bf16* bt, uint32_t k) {
+    return k % 8 == 0 && lda % 8 == 0 && (reinterpret_cast<uintptr_t>(a) % 16 == 0) &&
+           (reinterpret_cast<uintptr_t>(bt) % 16 == 0) && encode_fn() != nullptr;
+}
+
+int launch_gemm_bf16(const bf16* a, const bf16* bt, void* out, uint32_t ldc, uint32_t m, uint32_t n,
+                     uint32_t k, GemmMode mode, const GemmEpilogue& ep, const GemmQkvTargets* qkv,
+                     int* d_status, cudaStream_t stream) {
+    if (m == 0 || n == 0) return TNSR_B200_OK;
+    if (k == 0) return TNSR_B200_ERR_INVALID_ARGUMENT;
+    if (mode == GEMM_QKV && (!qkv || qkv->d == 0 || n != 3 * qkv->d || qkv->chunk == 0)) return TNSR_B200_ERR_INVALID_ARGUMENT;
+    if (mode == GEMM_SWIGLU && n % 32 != 0) {
+        set_thread_error("gemm: packed SwiGLU width must be a multiple of 32");
+        return TNSR_B200_ERR_UNSUPPORTED;
+    }
+    if (ep.residual && ep.out_dtype != TNSR_B200_F32) return TNSR_B200_ERR_INVALID_ARGUMENT;
+    EpiParams P;
+    P.ep = ep;
+    if (qkv) P.qkv = *qkv;
+    P.out = out;
+    P.ldc = ldc;
+    P.m = m;
+    P.n = n;
+    const uint32_t lda = k;
+    const bool can_tc = tc_eligible(a, lda, bt, k);
+    if (g_gemm_engine == 1 || !can_tc) {
+        if (g_gemm_engine == 2) {
+            set_thread_error("gemm: shape or alignment outside the tcgen05 engine (k % 8, 16-byte pointers)");
+            return TNSR_B200_ERR_UNSUPPORTED;
+        }
+        return launch_simple(a, lda, bt, P, k, mode, stream);
+    }
+    // tile width: the widest that still gives every SM a tile
+    const uint32_t tiles_m = ceil_div(m, BM);
+    uint32_t bn = 256;
+    while (bn > 64 && (uint64_t)tiles_m * ceil_div(n, bn) < (uint64_t)sm_count()) bn >>= 1;
+    TcParams prm;
+    prm.epi = P;
+    prm.k = k;
+    prm.tiles_m = tiles_m;
+    prm.tiles_n = ceil_div(n, bn);
+    prm.d_status = d_status;
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, a, m, k, lda, BM) || !make_map(&mb, bt, n, k, k, bn)) {
+        if (g_gemm_engine == 2) {
+            set_thread_error("gemm: tensor map encoding failed");
+            return TNSR_B200_ERR_CUDA;
+        }
+        return launch_simple(a, lda, bt, P, k, mode, stream);
+    }
+    switch (bn) {
+        case 256: return launch_tc_mode<256>(ma, mb, prm, mode, stream);
+        case 128: return launch_tc_mode<128>(ma, mb, prm, mode, stream);
+        default: return launch_tc_mode<64>(ma, mb, prm, mode, stream);
+    }
+}
+
+}  // namespace tb
