@@ -182,6 +182,16 @@ TNSR_B200_API int tnsr_b200_decoder_read_cache(tnsr_b200_decoder* dec, uint32_t 
 TNSR_B200_API int tnsr_b200_decoder_write_cache(tnsr_b200_decoder* dec, uint32_t index,
                                                 const float* host_in);
 
+/* Measurement aid (no reference counterpart; the reference times kernels from
+ * outside with CUDA events, src/ptx/linear/mod.rs:425-437).  While enabled, the
+ * session brackets every launch of its split-KV decode-attention kernel with a
+ * pair of CUDA events on its stream.  `attention_profile` waits for the stream,
+ * returns the summed device time in milliseconds and the number of launches
+ * since the last call, and clears the record. */
+TNSR_B200_API int tnsr_b200_decoder_profile_attention(tnsr_b200_decoder* dec, int enable);
+TNSR_B200_API int tnsr_b200_decoder_attention_profile(tnsr_b200_decoder* dec, double* total_ms,
+                                                      uint64_t* launches);
+
 /* ---- operators on caller-owned device memory ---------------------------- */
 /* The kernels of the session, exposed one by one for operator-level parity
  * tests and roofline measurement.  All pointers are device pointers. */

@@ -34,3 +34,11 @@ def oracle():
     from oracle import oracle as module
     module.build()
     return module
+
+
+@pytest.fixture(autouse=True)
+def _release_device_temporaries():
+    yield
+    mod = sys.modules.get("tests.gpu_util")
+    if mod is not None:
+        mod._KEEP.clear()

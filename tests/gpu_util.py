@@ -22,9 +22,18 @@ def ptr(t):
     return C.c_void_p(t.data_ptr()) if t is not None else None
 
 
+_KEEP = []  # device tensors made by dev() stay alive until the test ends (conftest clears this)
+
+
 def dev(a, dtype=None):
+    """Host array -> device tensor.  The tensor is kept alive for the rest of the
+    test: the C ABI only sees raw pointers, so a temporary must not be returned
+    to torch's caching allocator while a kernel still reads it."""
     t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
-    return t.to(dtype) if dtype is not None else t
+    if dtype is not None:
+        t = t.to(dtype)
+    _KEEP.append(t)
+    return t
 
 
 def ok(code):

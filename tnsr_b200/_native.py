@@ -52,6 +52,8 @@ SIGNATURES = {
     "tnsr_b200_decoder_decode_device": (_i, [_vp, _vp, _u32, _u32, _vp]),
     "tnsr_b200_decoder_synchronize": (_i, [_vp]),
     "tnsr_b200_decoder_stream": (_vp, [_vp]),
+    "tnsr_b200_decoder_profile_attention": (_i, [_vp, _i]),
+    "tnsr_b200_decoder_attention_profile": (_i, [_vp, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
     "tnsr_b200_decoder_read_cache": (_i, [_vp, _u32, _fp]),
     "tnsr_b200_decoder_write_cache": (_i, [_vp, _u32, _fp]),
     "tnsr_b200_embedding": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _i, _vp, _vp]),

@@ -19,6 +19,8 @@
 
 namespace tb {
 
+thread_local KernelTimer* t_attention_timer = nullptr;
+
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -131,30 +133,32 @@ struct DaLayout {
 
 static uint64_t align256(uint64_t x) { return (x + 255) & ~255ull; }
 
-static DaLayout da_layout(uint32_t batch, uint32_t capacity, uint32_t heads, uint32_t head_dim, uint64_t budget) {
+static DaLayout da_layout_for(uint32_t batch, uint64_t per_item, uint64_t items) {
     DaLayout L;
+    L.first = 256;
+    L.count = align256(L.first + 4ull * batch);
+    L.items = align256(L.count + 4ull * batch);
+    L.max_items = (uint32_t)(items > 0x7fffffffull ? 0x7fffffffull : items);
+    L.partial = align256(L.items + sizeof(DaItem) * (uint64_t)L.max_items);
+    L.bytes = L.partial + per_item * L.max_items;
+    return L;
+}
+
+// budget == 0: the preferred size.  Otherwise the largest item count that fits
+// in `budget` bytes (the caller checks that it still covers one item per session).
+static DaLayout da_layout(uint32_t batch, uint32_t capacity, uint32_t heads, uint32_t head_dim, uint64_t budget) {
     // Enough items for the smallest slab, but never more partial storage than ~256 MiB.
-    uint64_t per_item = (uint64_t)heads * (head_dim + 2) * 4;
+    const uint64_t per_item = (uint64_t)heads * (head_dim + 2) * 4;
     uint64_t want = (uint64_t)batch * ceil_div(capacity, DA_MIN_SLAB);
     uint64_t cap_items = (256ull << 20) / per_item;
     if (cap_items < batch) cap_items = batch;
     uint64_t items = want < cap_items ? want : cap_items;
-    L.first = 256;
-    L.count = align256(L.first + 4ull * batch);
-    L.items = align256(L.count + 4ull * batch);
-    if (budget) {
-        // shrink to what the caller gave us, keeping at least one item per session
-        uint64_t fixed = align256(L.items);
-        if (budget > fixed) {
-            uint64_t fit = (budget - fixed - 256) / (per_item + sizeof(DaItem));
-            if (fit < items) items = fit;
-        } else {
-            items = 0;
-        }
-    }
-    L.max_items = (uint32_t)(items > 0x7fffffffull ? 0x7fffffffull : items);
-    L.partial = align256(L.items + sizeof(DaItem) * (uint64_t)L.max_items);
-    L.bytes = L.partial + per_item * L.max_items;
+    DaLayout L = da_layout_for(batch, per_item, items);
+    if (budget == 0 || L.bytes <= budget) return L;
+    const uint64_t fixed = da_layout_for(batch, per_item, 0).bytes;
+    items = budget > fixed ? (budget - fixed) / (per_item + sizeof(DaItem)) : 0;
+    L = da_layout_for(batch, per_item, items);
+    while (L.bytes > budget && items > 0) L = da_layout_for(batch, per_item, --items);
     return L;
 }
 
@@ -170,7 +174,7 @@ bool decode_attention_supported(uint32_t heads, uint32_t head_dim) {
 }
 
 // ---- plan: choose the slab, build the item list --------------------------------
-// One block.  lengths == nullptr means every session has *d_position + extra keys.
+// One block.  lengths == nullptr means every session has (d_position ? *d_position : 0) + extra keys.
 __global__ void __launch_bounds__(1024)
 da_plan_kernel(const uint32_t* __restrict__ lengths, const uint32_t* __restrict__ d_position, uint32_t extra,
                uint32_t batch, uint32_t capacity, uint32_t target_items, uint32_t max_items,
@@ -180,7 +184,7 @@ da_plan_kernel(const uint32_t* __restrict__ lengths, const uint32_t* __restrict_
     __shared__ uint32_t s_slab;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     auto len_of = [&](uint32_t b) -> uint32_t {
-        uint32_t L = lengths ? lengths[b] : (*d_position + extra);
+        uint32_t L = lengths ? lengths[b] : ((d_position ? *d_position : 0u) + extra);
         if (L > capacity) {
             if (d_status) atomicCAS(d_status, DEV_OK, DEV_BAD_LENGTH);
             L = capacity;
@@ -526,7 +530,23 @@ template <int HD, int HPW>
 static int launch_da_t(const DaParams& P, uint32_t threads, size_t smem, uint32_t grid, cudaStream_t stream) {
     if (cudaFuncSetAttribute(decode_attention_kernel<HD, HPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return check_launch("decode_attention attribute");
+    KernelTimer* timer = t_attention_timer;
+    cudaEvent_t start = nullptr, stop = nullptr;
+    if (timer) {
+        if (timer->used + 2 > timer->events.size()) {
+            for (int i = 0; i < 2; ++i) {
+                cudaEvent_t e;
+                if (cudaEventCreate(&e) != cudaSuccess) return check_launch("decode_attention event");
+                timer->events.push_back(e);
+            }
+        }
+        start = timer->events[timer->used];
+        stop = timer->events[timer->used + 1];
+        timer->used += 2;
+        cudaEventRecord(start, stream);
+    }
     decode_attention_kernel<HD, HPW><<<grid, threads, smem, stream>>>(P);
+    if (timer) cudaEventRecord(stop, stream);
     count_launch();
     return check_launch("decode_attention");
 }

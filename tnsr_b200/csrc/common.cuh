@@ -7,6 +7,7 @@
 
 #include <atomic>
 #include <string>
+#include <vector>
 
 #include "../../include/tnsr_b200.h"
 
@@ -23,14 +24,26 @@ const char* thread_error();
 inline void count_launch(uint64_t n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 // Status of the last launch on the current thread's device, as a tnsr_b200 code.
+// With TNSR_B200_DEBUG_SYNC=1 in the environment every launch is followed by a
+// device synchronisation, so an asynchronous fault is attributed to its kernel.
+bool debug_sync_enabled();
 inline int check_launch(const char* what) {
     cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess && debug_sync_enabled()) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) {
         set_thread_error(std::string(what) + ": " + cudaGetErrorString(e));
         return TNSR_B200_ERR_CUDA;
     }
     return TNSR_B200_OK;
 }
+
+// Optional per-thread sink: when set, the decode-attention launcher records an
+// event pair around its main kernel.
+struct KernelTimer {
+    std::vector<cudaEvent_t> events;  // start/stop pairs
+    size_t used = 0;                  // events consumed so far
+};
+extern thread_local KernelTimer* t_attention_timer;
 
 inline uint32_t ceil_div(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
 inline uint64_t ceil_div64(uint64_t a, uint64_t b) { return (a + b - 1) / b; }

@@ -4,6 +4,7 @@
 // buffers sized for the largest chunk seen so far, and runs one decode step as a
 // fixed sequence of kernels -- there is no graph to compile and no program
 // cache to evict.
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -14,6 +15,13 @@ std::atomic<uint64_t> g_launches{0};
 static thread_local std::string t_error;
 void set_thread_error(const std::string& msg) { t_error = msg; }
 const char* thread_error() { return t_error.c_str(); }
+bool debug_sync_enabled() {
+    static const bool on = [] {
+        const char* v = std::getenv("TNSR_B200_DEBUG_SYNC");
+        return v && v[0] == '1';
+    }();
+    return on;
+}
 }  // namespace tb
 
 using namespace tb;
@@ -89,6 +97,8 @@ struct tnsr_b200_decoder {
     float* d_stage = nullptr;  // upload staging (device, f32)
     size_t d_stage_bytes = 0;
     std::vector<float> host_bqkv, host_bgu;
+    bool profile_attention = false;
+    KernelTimer attention_timer;
 };
 
 namespace {
@@ -404,8 +414,10 @@ int run_step(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, u
     const tnsr_b200_config& c = dec->cfg;
     const uint32_t rows = c.batch * chunk;
     const uint32_t logit_rows = c.logits_mode == TNSR_B200_LOGITS_ALL ? rows : c.batch;
+    t_attention_timer = dec->profile_attention ? &dec->attention_timer : nullptr;
     int rc = dec->bf16_path ? step_bf16(dec, d_tokens, chunk, position, logit_rows)
                             : step_strict(dec, d_tokens, chunk, position, logit_rows);
+    t_attention_timer = nullptr;
     if (rc) return rc;
     if (d_argmax_out) {
         // last position of every session
@@ -549,6 +561,7 @@ void tnsr_b200_decoder_destroy(tnsr_b200_decoder* dec) {
     if (dec->h_argmax) cudaFreeHost(dec->h_argmax);
     if (dec->h_status) cudaFreeHost(dec->h_status);
     if (dec->h_stage) cudaFreeHost(dec->h_stage);
+    for (cudaEvent_t e : dec->attention_timer.events) cudaEventDestroy(e);
     if (dec->stream) cudaStreamDestroy(dec->stream);
     cudaGetLastError();
     delete dec;
@@ -749,6 +762,29 @@ int tnsr_b200_decoder_synchronize(tnsr_b200_decoder* dec) {
         cudaMemsetAsync(dec->d_status, 0, 16, dec->stream);
         return device_status_to_code(dec, status);
     }
+    return TNSR_B200_OK;
+}
+
+int tnsr_b200_decoder_profile_attention(tnsr_b200_decoder* dec, int enable) {
+    if (!dec) return fail(nullptr, TNSR_B200_ERR_INVALID_ARGUMENT, "null decoder");
+    dec->profile_attention = enable != 0;
+    return TNSR_B200_OK;
+}
+
+int tnsr_b200_decoder_attention_profile(tnsr_b200_decoder* dec, double* total_ms, uint64_t* launches) {
+    if (!dec || !total_ms || !launches) return fail(dec, TNSR_B200_ERR_INVALID_ARGUMENT, "null argument");
+    CU(dec, cudaSetDevice(dec->cfg.device));
+    CU(dec, cudaStreamSynchronize(dec->stream));
+    double sum = 0.0;
+    KernelTimer& t = dec->attention_timer;
+    for (size_t i = 0; i + 1 < t.used; i += 2) {
+        float ms = 0.0f;
+        CU(dec, cudaEventElapsedTime(&ms, t.events[i], t.events[i + 1]));
+        sum += ms;
+    }
+    *total_ms = sum;
+    *launches = t.used / 2;
+    t.used = 0;
     return TNSR_B200_OK;
 }
 

@@ -88,6 +88,15 @@ class B200Session:
     def stream(self) -> int:
         return int(lib().tnsr_b200_decoder_stream(self.handle) or 0)
 
+    def profile_attention(self, enable: bool) -> None:
+        self._check(lib().tnsr_b200_decoder_profile_attention(self.handle, int(enable)))
+
+    def attention_profile(self):
+        """(summed device milliseconds, launches) of the decode-attention kernel since the last call."""
+        ms, n = C.c_double(), C.c_uint64()
+        self._check(lib().tnsr_b200_decoder_attention_profile(self.handle, C.byref(ms), C.byref(n)))
+        return ms.value, int(n.value)
+
     def read_cache(self, index: int) -> np.ndarray:
         out = np.empty((self.batch, self.capacity, self.embed_dim), dtype=np.float32)
         self._check(lib().tnsr_b200_decoder_read_cache(self.handle, index, out.ctypes.data_as(C.POINTER(C.c_float))))
