@@ -1,0 +1,406 @@
+"""Benchmark of the cached-GPT decode hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --gpus N --steps K --warmup W   # CPU arm
+
+Workload ("c4"): the serving configuration -- 12 layers, d_model 768, 12 heads x
+64, SwiGLU 2048, vocab 32000, bf16 weights N(0, 0.02) seed 5; 256 independent
+sessions sharded 256/N over the GPUs, each a 512-token prefill of uniform random
+ids followed by greedy decode steps.  A benchmark "step" is one decode step: one
+new token for every session of the rank.  The timed region is K steps starting
+at position 512 (the default K = 256 is the configuration's decode length), with
+token ids living on the device; `value` is total tokens/s over all ranks, timed
+with CUDA events on the session's stream, max over ranks.  `e2e` repeats the K
+steps through the host API (`tnsr_b200_decoder_decode`): ids go up from host
+memory and greedy ids come back every step.
+
+The CPU arm times this repository's restatement of the reference's CPU executor
+(oracle/) on the host cores: the reference is Rust and cannot be built here.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+TOTAL_SESSIONS = 256
+PREFILL = 512
+DECODE_STEPS = 256
+FALLBACK_HBM_GBS = 6650.0
+
+# Per-launch DRAM traffic of decode_attention_kernel relative to its algorithmic
+# bytes, from the ncu capture summarised in profiles/decode_attention_c4_small.md
+# (dram__bytes_read.sum + dram__bytes_write.sum of a smaller launch; traffic
+# grows in proportion to the live keys, so it is scaled by that ratio).
+NCU_TRAFFIC_RATIO = None
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=DECODE_STEPS)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--sessions", type=int, default=TOTAL_SESSIONS, help="total sessions over all GPUs")
+    ap.add_argument("--prefill", type=int, default=PREFILL)
+    ap.add_argument("--layers", type=int, default=12)
+    ap.add_argument("--vocab", type=int, default=32000)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def serving_config(args):
+    from tnsr_b200.nn import GptConfig
+    return GptConfig(vocab_size=args.vocab, max_sequence_length=2048, embed_dim=768, num_heads=12,
+                     feed_forward_dim=2048, num_layers=args.layers, layer_norm_epsilon=1e-5,
+                     activation="swiglu", weight_dtype="bf16")
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            data = json.load(f)
+        return float(data["hbm_gbs"]), "measured", data
+    return FALLBACK_HBM_GBS, "fallback", {}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------
+# CPU arm: the checker's decode step on the host cores
+# ---------------------------------------------------------------------------
+def cpu_decode_rate(args, steps, warmup, threads=None, budget_s=None):
+    """tokens/s of the CPU restatement on `threads` host threads (one session per
+    thread per step, all advancing together as the reference's batch does).
+    The sessions start at position `prefill` on zeroed K/V rows: the arithmetic
+    cost of a decode step does not depend on the cached values."""
+    from oracle import oracle
+    from tests.workloads import normal_model_arrays
+    cfg = serving_config(args)
+    threads = threads or oracle.max_threads()
+    oracle.set_threads(threads)
+    sessions = threads
+    arrays = normal_model_arrays(cfg, seed=5, std=0.02)
+    model = oracle.OracleModel(cfg.vocab_size, cfg.max_sequence_length, cfg.embed_dim, cfg.num_heads,
+                               cfg.feed_forward_dim, cfg.num_layers, cfg.layer_norm_epsilon, "swiglu")
+    model.set_params(arrays)
+    del arrays
+    capacity = min(cfg.max_sequence_length, args.prefill + steps + warmup + 1)
+    dec = oracle.lib().oracle_decoder_create(model.handle, sessions, capacity)
+    oracle.lib().oracle_decoder_set_len(dec, args.prefill)
+    rng = np.random.default_rng(7)
+    ids = rng.integers(0, cfg.vocab_size, size=sessions).astype(np.uint32)
+    logits = np.empty((sessions, cfg.vocab_size), dtype=np.float32)
+    pl = logits.ctypes.data_as(C.POINTER(C.c_float))
+
+    def one_step():
+        nonlocal ids
+        rc = oracle.lib().oracle_decoder_decode(dec, ids.ctypes.data_as(C.POINTER(C.c_uint32)), 1, pl)
+        assert rc == 0, rc
+        ids = np.asarray([oracle.argmax_last(logits[s]) for s in range(sessions)], dtype=np.uint32)
+
+    for _ in range(warmup):
+        one_step()
+    done = 0
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one_step()
+        done += 1
+        if budget_s is not None and time.perf_counter() - t0 > budget_s:
+            break
+    elapsed = time.perf_counter() - t0
+    oracle.lib().oracle_decoder_destroy(dec)
+    oracle.set_threads(1)
+    return {"tokens_per_s": sessions * done / elapsed, "threads": threads, "sessions": sessions, "steps": done,
+            "elapsed_s": elapsed, "ms_per_step": elapsed / done * 1e3}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    r = cpu_decode_rate(args, args.steps, args.warmup)
+    sample = (f"{r['sessions']} sessions (one per host thread) x {r['steps']} decode steps from position {args.prefill}; "
+              "CPU restatement of tnsr's SimpleExecutor path (oracle/), f32")
+    line = {
+        "impl": "reference", "metric": "decode_tokens_per_s", "value": r["tokens_per_s"], "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": r["steps"], "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, args.gpus),
+        "cpu_baseline": {"value": r["tokens_per_s"], "unit": "tokens/s", "cores": r["threads"], "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": r["tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, n_gpus):
+    return {
+        "workload": "c4: GPT 12x768 (12 heads x 64, SwiGLU 2048, vocab 32000, ctx 2048), "
+                    f"{args.sessions} sessions x ({args.prefill}-token prefill + greedy decode), 1 token/session/step",
+        "sessions_total": args.sessions, "sessions_per_gpu": args.sessions // n_gpus, "prefill": args.prefill,
+        "layers": args.layers, "vocab": args.vocab, "parallelism": f"sessions sharded over {n_gpus} GPU(s), no collective",
+        "l2": "inputs larger than L2: each step streams the live K/V rows (GBs) and 222 MB of weights",
+    }
+
+
+# ---------------------------------------------------------------------------
+# this library
+# ---------------------------------------------------------------------------
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+    from tests.workloads import normal_model_arrays
+    from tnsr_b200 import _native
+    from tnsr_b200.session import B200Session
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus > 1 and world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    cfg = serving_config(args)
+    sessions = args.sessions // world
+    K, W = args.steps, args.warmup
+    capacity = min(cfg.max_sequence_length, args.prefill + max(K, W) + 1)
+    lib = _native.lib()
+
+    def make_session():
+        s = B200Session(cfg, sessions, capacity, device=local_rank, logits_mode="none")
+        for i, a in enumerate(arrays):
+            s.refresh(i, a)
+        return s
+
+    arrays = normal_model_arrays(cfg, seed=5, std=0.02)
+    sess = make_session()
+    del arrays
+    stream = torch.cuda.ExternalStream(sess.stream(), device=torch.device("cuda", local_rank))
+
+    rng = np.random.default_rng(1000 + rank)
+    prompt = rng.integers(0, cfg.vocab_size, size=(sessions, args.prefill)).astype(np.uint32)
+
+    # ---- prefill (untimed for the metric; reported on the side) ----
+    def prefill():
+        sess.reset()
+        d_prompt = torch.from_numpy(prompt.view(np.int32)).cuda()
+        first = torch.empty(sessions, dtype=torch.int32, device="cuda")
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        sess.decode_device(d_prompt.data_ptr(), args.prefill, 0, first.data_ptr())
+        e1.record(stream)
+        sess.synchronize()
+        return first, e0.elapsed_time(e1)
+
+    first, _ = prefill()              # warm-up pass (allocations, first-use costs)
+    first, prefill_ms = prefill()
+    first_host = first.cpu().numpy().astype(np.uint32)
+
+    def fresh_ids():
+        cur = first.clone()
+        torch.cuda.synchronize()  # the copy ran on torch's stream; the session has its own
+        return cur
+
+    def device_loop(n, cur):
+        """n greedy steps from position `prefill`; ids stay in `cur` on the device."""
+        for step in range(n):
+            sess.decode_device(cur.data_ptr(), 1, args.prefill + step, cur.data_ptr())
+        return cur
+
+    # ---- warm-up, then the timed region ----
+    device_loop(W, fresh_ids())
+    sess.synchronize()
+    cur = fresh_ids()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    barrier()
+    launches0 = lib.tnsr_b200_kernel_launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    last = device_loop(K, cur)
+    e1.record(stream)
+    sess.synchronize()
+    launches = lib.tnsr_b200_kernel_launches() - launches0
+    barrier()
+    clocks = sampler.stop()
+    elapsed_ms = e0.elapsed_time(e1)
+    tokens_after_timed = last.cpu().numpy().astype(np.uint32)
+
+    # ---- instrumented replay of the same K steps: device time of the attention kernel ----
+    sess.profile_attention(True)
+    sess.attention_profile()
+    device_loop(K, fresh_ids())
+    attn_ms, attn_launches = sess.attention_profile()
+    sess.profile_attention(False)
+
+    # ---- end to end through the host API ----
+    e2e = None
+    if not args.no_e2e:
+        cur = first_host.copy()
+        for step in range(min(W, K)):
+            _, cur = sess.decode_full(cur.reshape(sessions, 1), args.prefill + step)
+        cur = first_host.copy()
+        barrier()
+        t0 = time.perf_counter()
+        for step in range(K):
+            _, cur = sess.decode_full(cur.reshape(sessions, 1), args.prefill + step)
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+        barrier()
+        e2e = {"seconds": e2e_s, "same_tokens_as_device_loop": bool(np.array_equal(cur, tokens_after_timed))}
+
+    # ---- reduce over ranks ----
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    elapsed_ms = max_over_ranks(elapsed_ms)
+    prefill_ms = max_over_ranks(prefill_ms)
+    total_launches = int(sum_over_ranks(float(launches)))
+    e2e_s = max_over_ranks(e2e["seconds"]) if e2e else None
+    total_sessions = sessions * world
+
+    if rank == 0:
+        d, layers = cfg.embed_dim, cfg.num_layers
+        peak, peak_kind, peaks = measured_peaks()
+        # algorithmic bytes of one attention launch at decode step t: every session's live K and V rows
+        # (prefill + t + 1 keys x d x 2 B x 2 tensors) plus q and out rows
+        live = args.prefill + (K - 1) / 2.0 + 1.0
+        bytes_per_launch = sessions * (live * d * 2 * 2 + 2 * d * 2)
+        attn_avg_ms = attn_ms / max(attn_launches, 1)
+        achieved = bytes_per_launch / (attn_avg_ms * 1e-3) / 1e9 if attn_launches else None
+        roofline = {
+            "kernel": "decode_attention_kernel<64,1> (split-KV live-prefix scan)", "bound": "hbm",
+            "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak if achieved else None,
+            "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
+            "traffic": bytes_per_launch * NCU_TRAFFIC_RATIO if NCU_TRAFFIC_RATIO else None,
+            "algorithmic_bytes_per_launch": bytes_per_launch, "avg_launch_ms": attn_avg_ms, "launches": attn_launches,
+            "share_of_step": attn_ms / (elapsed_ms if world == 1 else elapsed_ms) if attn_launches else None,
+            "how": "CUDA events around every launch of the kernel on the session's stream, in a replay of the same K steps",
+        }
+        value = total_sessions * K / (elapsed_ms * 1e-3)
+        flops_per_token = 2.0 * (layers * (4 * d * d + 3 * d * cfg.feed_forward_dim)) + 2.0 * d * cfg.vocab_size
+        prefill_tokens = total_sessions * args.prefill
+        line = {
+            "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": elapsed_ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": workload_config(args, world),
+            "roofline": roofline,
+            "gpu_launches": total_launches,
+            "clocks": clocks,
+            "prefill": {"tokens_per_s": prefill_tokens / (prefill_ms * 1e-3), "ms": prefill_ms,
+                        "gemm_tflops": prefill_tokens * (flops_per_token - 2.0 * d * cfg.vocab_size) / (prefill_ms * 1e-3) / 1e12,
+                        "note": "whole prefill step incl. attention and LayerNorm; GEMM flops / wall time"},
+        }
+        if e2e:
+            line["e2e"] = {"value": total_sessions * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 4 * sessions,
+                           "d2h_bytes_per_step": 4 * sessions + 4, "ms_per_step": e2e_s / K * 1e3,
+                           "api": "tnsr_b200_decoder_decode, logits_mode NONE: ids up, greedy ids down, every step",
+                           "same_tokens_as_device_loop": e2e["same_tokens_as_device_loop"]}
+        if world == 1 and not args.no_cpu_baseline:
+            sess.close()
+            r = cpu_decode_rate(args, steps=64, warmup=1, budget_s=20.0)
+            line["cpu_baseline"] = {
+                "value": r["tokens_per_s"], "unit": "tokens/s", "cores": r["threads"], "kind": "port",
+                "sample": f"{r['sessions']} sessions x {r['steps']} decode steps from position {args.prefill} "
+                          f"({r['elapsed_s']:.1f} s); CPU restatement of tnsr's SimpleExecutor (oracle/), f32",
+            }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()
