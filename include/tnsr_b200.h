@@ -273,6 +273,28 @@ TNSR_B200_API int tnsr_b200_decode_attention(const void* q, const void* k_cache,
                                              uint32_t capacity, uint32_t heads, uint32_t head_dim,
                                              void* stream);
 
+/* The same decode attention for callers that cannot allocate device memory at
+ * call time and so have no workspace to pass: processes that budget the whole
+ * GPU at start-up, or latency-bound loops where cudaMalloc (a device-wide
+ * synchronisation that may fail under fragmentation) is not allowed.  It has no
+ * counterpart in the reference.  The scratch is a fixed array of
+ * TNSR_B200_STATIC_SCRATCH_BYTES inside the library, present on every GPU that
+ * loads it until the process exits; the call allocates and frees nothing.
+ * Limits: the batch must fit (at least 2048 + batch * (24 + heads *
+ * (head_dim + 2) * 4) bytes), otherwise TNSR_B200_ERR_UNSUPPORTED; larger
+ * batches simply get coarser key slabs than with a roomy workspace.  All calls
+ * share the array, so calls that overlap on the GPU (different streams or host
+ * threads) race: keep them on one stream.  The first call on each device looks
+ * up the array's device address once; make that first call before any stream
+ * capture.  d_status (optional device int) receives 0 or a device-side error
+ * code when the stream reaches the end of the call.  Arguments otherwise as
+ * tnsr_b200_decode_attention. */
+#define TNSR_B200_STATIC_SCRATCH_BYTES (32ull << 20)
+TNSR_B200_API int tnsr_b200_decode_attention_static(const void* q, const void* k_cache, const void* v_cache,
+                                                    const uint32_t* lengths, void* out, uint32_t batch,
+                                                    uint32_t capacity, uint32_t heads, uint32_t head_dim,
+                                                    int* d_status, void* stream);
+
 /* Causal attention of `chunk` new queries per session over `position + chunk`
  * cached keys (the new rows are already in the cache), the job of the tiled
  * prefill (src/nn/kv_cache/prefill.rs:170-607).  q, out: [batch, chunk, width]

@@ -66,6 +66,7 @@ SIGNATURES = {
     "tnsr_b200_pack_gate_up": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _vp]),
     "tnsr_b200_decode_attention_workspace": (_u64, [_u32, _u32, _u32, _u32]),
     "tnsr_b200_decode_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _u64, _u32, _u32, _u32, _u32, _vp]),
+    "tnsr_b200_decode_attention_static": (_i, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _vp]),
     "tnsr_b200_prefill_attention": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _vp]),
     "tnsr_b200_argmax": (_i, [_vp, _vp, _u32, _u32, _vp]),
 }
