@@ -43,7 +43,7 @@ FALLBACK_HBM_GBS = 6650.0
 # bytes, from the ncu capture summarised in profiles/decode_attention_c4_small.md
 # (dram__bytes_read.sum + dram__bytes_write.sum of a smaller launch; traffic
 # grows in proportion to the live keys, so it is scaled by that ratio).
-NCU_TRAFFIC_RATIO = None
+NCU_TRAFFIC_RATIO = 1.033
 
 
 def parse_args():
