@@ -4,7 +4,8 @@
 //    prefix only, split over the key axis so that every SM streams a contiguous
 //    slab of K and V rows (all heads) through a shared-memory ring filled by
 //    bulk async copies (cp.async.bulk, mbarrier completion); f32 online softmax;
-//    partials (max, sum, numerator) merged by a second small kernel.  This is
+//    partials (max, sum, numerator) are merged inside the same kernel by whichever
+//    warp stores the last partial of a (session, head) pair.  This is
 //    the job of the reference's AttentionScan / MergeScan pair
 //    (src/nn/kv_cache/attention.rs:31-239, :242-393; fixed 16/32 partitions,
 //    src/nn/kv_cache/cuda.rs:31-32,110-116) with two differences: the split is
@@ -124,20 +125,22 @@ struct DaItem {
 //   header  : uint32 n_items, slab
 //   first   : uint32 [batch]      first item of each session
 //   count   : uint32 [batch]      items of each session
+//   done    : uint32 [batch * heads]  partials stored so far per (session, head); zero between launches
 //   items   : DaItem [max_items]
 //   partial : float  [max_items][heads][head_dim + 2]   (numerator, then max, then sum)
 struct DaLayout {
-    uint64_t first, count, items, partial, bytes;
+    uint64_t first, count, done, items, partial, bytes;
     uint32_t max_items;
 };
 
 static uint64_t align256(uint64_t x) { return (x + 255) & ~255ull; }
 
-static DaLayout da_layout_for(uint32_t batch, uint64_t per_item, uint64_t items) {
+static DaLayout da_layout_for(uint32_t batch, uint32_t heads, uint64_t per_item, uint64_t items) {
     DaLayout L;
     L.first = 256;
     L.count = align256(L.first + 4ull * batch);
-    L.items = align256(L.count + 4ull * batch);
+    L.done = align256(L.count + 4ull * batch);
+    L.items = align256(L.done + 4ull * batch * heads);
     L.max_items = (uint32_t)(items > 0x7fffffffull ? 0x7fffffffull : items);
     L.partial = align256(L.items + sizeof(DaItem) * (uint64_t)L.max_items);
     L.bytes = L.partial + per_item * L.max_items;
@@ -153,12 +156,12 @@ static DaLayout da_layout(uint32_t batch, uint32_t capacity, uint32_t heads, uin
     uint64_t cap_items = (256ull << 20) / per_item;
     if (cap_items < batch) cap_items = batch;
     uint64_t items = want < cap_items ? want : cap_items;
-    DaLayout L = da_layout_for(batch, per_item, items);
+    DaLayout L = da_layout_for(batch, heads, per_item, items);
     if (budget == 0 || L.bytes <= budget) return L;
-    const uint64_t fixed = da_layout_for(batch, per_item, 0).bytes;
+    const uint64_t fixed = da_layout_for(batch, heads, per_item, 0).bytes;
     items = budget > fixed ? (budget - fixed) / (per_item + sizeof(DaItem)) : 0;
-    L = da_layout_for(batch, per_item, items);
-    while (L.bytes > budget && items > 0) L = da_layout_for(batch, per_item, --items);
+    L = da_layout_for(batch, heads, per_item, items);
+    while (L.bytes > budget && items > 0) L = da_layout_for(batch, heads, per_item, --items);
     return L;
 }
 
@@ -177,11 +180,11 @@ bool decode_attention_supported(uint32_t heads, uint32_t head_dim) {
 // One block.  lengths == nullptr means every session has (d_position ? *d_position : 0) + extra keys.
 __global__ void __launch_bounds__(1024)
 da_plan_kernel(const uint32_t* __restrict__ lengths, const uint32_t* __restrict__ d_position, uint32_t extra,
-               uint32_t batch, uint32_t capacity, uint32_t target_items, uint32_t max_items,
+               uint32_t batch, uint32_t heads, uint32_t capacity, uint32_t target_items, uint32_t max_items,
                uint32_t* __restrict__ header, uint32_t* __restrict__ first, uint32_t* __restrict__ count,
-               DaItem* __restrict__ items, int* __restrict__ d_status) {
+               uint32_t* __restrict__ done, DaItem* __restrict__ items, int* __restrict__ d_status) {
     __shared__ unsigned long long red[32];
-    __shared__ uint32_t s_slab;
+    __shared__ uint32_t s_slab, s_carry, s_warp_tot[32];
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     auto len_of = [&](uint32_t b) -> uint32_t {
         uint32_t L = lengths ? lengths[b] : ((d_position ? *d_position : 0u) + extra);
@@ -215,18 +218,35 @@ da_plan_kernel(const uint32_t* __restrict__ lengths, const uint32_t* __restrict_
         if (n <= max_items || slab >= (1u << 30)) break;
         slab <<= 1;
     }
-    if (tid == 0) s_slab = slab;
+    if (tid == 0) { s_slab = slab; s_carry = 0; }
     __syncthreads();
     slab = s_slab;
-    if (tid == 0) {
-        uint32_t run = 0;
-        for (uint32_t b = 0; b < batch; ++b) {
-            uint32_t c = (len_of(b) + slab - 1) / slab;
-            first[b] = run;
-            count[b] = c;
-            run += c;
+    // the merge counters must be zero when the attention kernel starts
+    for (uint32_t i = tid; i < batch * heads; i += blockDim.x) done[i] = 0;
+    // exclusive prefix sum of the per-session item counts, one block-wide scan per 1024 sessions
+    for (uint32_t base = 0; base < batch; base += blockDim.x) {
+        const uint32_t b = base + tid;
+        const uint32_t c = b < batch ? (len_of(b) + slab - 1) / slab : 0;
+        uint32_t incl = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= (uint32_t)o) incl += v;
         }
-        header[0] = run;
+        if (lane == 31) s_warp_tot[warp] = incl;
+        __syncthreads();
+        uint32_t before = s_carry;
+        for (uint32_t w = 0; w < warp; ++w) before += s_warp_tot[w];
+        if (b < batch) {
+            first[b] = before + incl - c;
+            count[b] = c;
+        }
+        __syncthreads();
+        if (tid == blockDim.x - 1) s_carry = before + incl;
+        __syncthreads();
+    }
+    if (tid == 0) {
+        header[0] = s_carry;
         header[1] = slab;
     }
     __syncthreads();
@@ -303,9 +323,13 @@ struct DaParams {
     const bf16* kc;
     const bf16* vc;
     const uint32_t* header;
+    const uint32_t* first;
+    const uint32_t* count;
+    uint32_t* done;
     const DaItem* items;
     float* partial;
-    uint32_t capacity, heads;
+    bf16* out;
+    uint32_t batch, capacity, heads;
     uint32_t stages;
     float scale_log2;
     int* d_status;
@@ -472,6 +496,17 @@ decode_attention_kernel(DaParams P) {
 #pragma unroll
                             for (int e = 0; e < 8; ++e) a[e] += __shfl_xor_sync(0xffffffffu, a[e], o);
                         }
+                        const uint32_t n_parts = P.count[mt.session];
+                        if (n_parts == 1) {
+                            // the only slab of this session: normalise and write the output row directly
+                            if (grp == 0) {
+                                const float inv = 1.0f / ll;
+                                bf16* o = P.out + (size_t)mt.session * d + (size_t)h * HD + sub * 8;
+                                *reinterpret_cast<uint4*>(o) = make_uint4(pack_bf16x2(a[0] * inv, a[1] * inv), pack_bf16x2(a[2] * inv, a[3] * inv),
+                                                                          pack_bf16x2(a[4] * inv, a[5] * inv), pack_bf16x2(a[6] * inv, a[7] * inv));
+                            }
+                            continue;
+                        }
                         if (grp == 0) {
                             float* dst = P.partial + ((size_t)mt.item * P.heads + h) * (HD + 2);
                             // (HD + 2) floats per head keeps 8-byte alignment only: store as float2
@@ -479,6 +514,39 @@ decode_attention_kernel(DaParams P) {
                             for (int e = 0; e < 4; ++e)
                                 *reinterpret_cast<float2*>(dst + sub * 8 + 2 * e) = make_float2(a[2 * e], a[2 * e + 1]);
                             if (sub == 0) *reinterpret_cast<float2*>(dst + HD) = make_float2(mm, ll);
+                            __threadfence();
+                        }
+                        __syncwarp();
+                        // whoever stores the last partial of (session, head) merges them
+                        uint32_t seen = 0;
+                        if (lane == 0) {
+                            __threadfence();
+                            seen = atomicAdd(P.done + (size_t)mt.session * P.heads + h, 1u);
+                        }
+                        seen = __shfl_sync(0xffffffffu, seen, 0);
+                        if (seen + 1 == n_parts) {
+                            __threadfence();
+                            constexpr int DPL = HD / 32;  // output dims per lane
+                            const float* base = P.partial + ((size_t)P.first[mt.session] * P.heads + h) * (HD + 2);
+                            const size_t step = (size_t)P.heads * (HD + 2);
+                            float mx = -INFINITY;
+                            for (uint32_t i = 0; i < n_parts; ++i) mx = fmaxf(mx, __ldcg(base + i * step + HD));
+                            const float ms = (mx == -INFINITY) ? 0.0f : mx;
+                            float lt = 0.0f, o[DPL];
+#pragma unroll
+                            for (int e = 0; e < DPL; ++e) o[e] = 0.0f;
+                            for (uint32_t i = 0; i < n_parts; ++i) {
+                                const float* pp = base + i * step;
+                                const float w = ex2(__ldcg(pp + HD) - ms);
+                                lt = fmaf(__ldcg(pp + HD + 1), w, lt);
+#pragma unroll
+                                for (int e = 0; e < DPL; ++e) o[e] = fmaf(__ldcg(pp + lane * DPL + e), w, o[e]);
+                            }
+                            const float inv = 1.0f / lt;
+                            bf16* orow = P.out + (size_t)mt.session * d + (size_t)h * HD + lane * DPL;
+#pragma unroll
+                            for (int e = 0; e < DPL; ++e) orow[e] = __float2bfloat16_rn(o[e] * inv);
+                            if (lane == 0) P.done[(size_t)mt.session * P.heads + h] = 0;
                         }
                     }
                 }
@@ -487,6 +555,12 @@ decode_attention_kernel(DaParams P) {
                 if (++stage == P.stages) { stage = 0; phase ^= 1; }
                 if (last) break;
             }
+        }
+        // sessions without any live key own no item: their output row is zero
+        for (uint32_t b = blockIdx.x * consumers + warp; b < P.batch; b += gridDim.x * consumers) {
+            if (P.count[b] != 0) continue;
+            for (uint32_t c = lane * 8; c < d; c += 32 * 8)
+                *reinterpret_cast<uint4*>(P.out + (size_t)b * d + c) = make_uint4(0u, 0u, 0u, 0u);
         }
     }
     __syncthreads();
@@ -498,38 +572,16 @@ decode_attention_kernel(DaParams P) {
     }
 }
 
-// ---- merge: one block per session, one thread per 4 output dims -----------------
-__global__ void __launch_bounds__(1024)
-da_merge_kernel(const float* __restrict__ partial, const uint32_t* __restrict__ first, const uint32_t* __restrict__ count,
-                bf16* __restrict__ out, uint32_t heads, uint32_t hd) {
-    const uint32_t b = blockIdx.x, d = heads * hd;
-    const uint32_t f = first[b], n = count[b];
-    for (uint32_t c4 = threadIdx.x * 4; c4 < d; c4 += blockDim.x * 4) {
-        const uint32_t h = c4 / hd, c = c4 % hd;
-        float mx = -INFINITY;
-        for (uint32_t i = 0; i < n; ++i) mx = fmaxf(mx, partial[((size_t)(f + i) * heads + h) * (hd + 2) + hd]);
-        const float m_safe = (mx == -INFINITY) ? 0.0f : mx;
-        float l = 0.0f, a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
-        for (uint32_t i = 0; i < n; ++i) {
-            const float* p = partial + ((size_t)(f + i) * heads + h) * (hd + 2);
-            const float w = ex2(p[hd] - m_safe);
-            l = fmaf(p[hd + 1], w, l);
-            const float2 x = *reinterpret_cast<const float2*>(p + c), y = *reinterpret_cast<const float2*>(p + c + 2);
-            a0 = fmaf(x.x, w, a0); a1 = fmaf(x.y, w, a1); a2 = fmaf(y.x, w, a2); a3 = fmaf(y.y, w, a3);
-        }
-        uint2 o = make_uint2(0u, 0u);
-        if (n > 0) {
-            const float inv = 1.0f / l;
-            o = make_uint2(pack_bf16x2(a0 * inv, a1 * inv), pack_bf16x2(a2 * inv, a3 * inv));
-        }
-        *reinterpret_cast<uint2*>(out + (size_t)b * d + c4) = o;
-    }
-}
-
 template <int HD, int HPW>
 static int launch_da_t(const DaParams& P, uint32_t threads, size_t smem, uint32_t grid, cudaStream_t stream) {
-    if (cudaFuncSetAttribute(decode_attention_kernel<HD, HPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return check_launch("decode_attention attribute");
+    static size_t configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || configured[dev] < smem) {
+        if (cudaFuncSetAttribute(decode_attention_kernel<HD, HPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return check_launch("decode_attention attribute");
+        if (dev >= 0 && dev < 64) configured[dev] = smem;
+    }
     KernelTimer* timer = t_attention_timer;
     cudaEvent_t start = nullptr, stop = nullptr;
     if (timer) {
@@ -586,12 +638,13 @@ int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v
     uint32_t* header = reinterpret_cast<uint32_t*>(ws);
     uint32_t* first = reinterpret_cast<uint32_t*>(ws + L.first);
     uint32_t* count = reinterpret_cast<uint32_t*>(ws + L.count);
+    uint32_t* done = reinterpret_cast<uint32_t*>(ws + L.done);
     DaItem* items = reinterpret_cast<DaItem*>(ws + L.items);
     float* partial = reinterpret_cast<float*>(ws + L.partial);
     const uint32_t grid = (uint32_t)da_sm_count();
     if (plan) {
-        da_plan_kernel<<<1, 1024, 0, stream>>>(d_lengths, d_position, extra, batch, capacity, 8 * grid, L.max_items, header,
-                                               first, count, items, d_status);
+        da_plan_kernel<<<1, 1024, 0, stream>>>(d_lengths, d_position, extra, batch, heads, capacity, 8 * grid, L.max_items,
+                                               header, first, count, done, items, d_status);
         count_launch();
         int rc = check_launch("decode_attention plan");
         if (rc) return rc;
@@ -605,8 +658,9 @@ int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v
     const uint32_t consumers = ceil_div(heads, hpw);
     DaParams P;
     P.q = q; P.kc = k_cache; P.vc = v_cache;
-    P.header = header; P.items = items; P.partial = partial;
-    P.capacity = capacity; P.heads = heads; P.stages = stages;
+    P.header = header; P.first = first; P.count = count; P.done = done; P.items = items; P.partial = partial;
+    P.out = out;
+    P.batch = batch; P.capacity = capacity; P.heads = heads; P.stages = stages;
     P.scale_log2 = (1.0f / sqrtf((float)head_dim)) * 1.4426950408889634f;
     P.d_status = d_status;
     const uint32_t threads = (consumers + 1) * 32;
@@ -620,13 +674,7 @@ int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v
            : head_dim == 64 ? launch_da_t<64, 2>(P, threads, smem, grid, stream)
                             : launch_da_t<128, 2>(P, threads, smem, grid, stream);
     }
-    if (rc) return rc;
-    uint32_t mthreads = d / 4;
-    if (mthreads > 1024) mthreads = 1024;
-    mthreads = (mthreads + 31) / 32 * 32;
-    da_merge_kernel<<<batch, mthreads, 0, stream>>>(partial, first, count, out, heads, head_dim);
-    count_launch();
-    return check_launch("decode_attention merge");
+    return rc;
 }
 
 int launch_decode_attention(const bf16* q, const bf16* k_cache, const bf16* v_cache, const uint32_t* d_lengths,

@@ -90,7 +90,8 @@ int launch_gemm_strict(const float* a, const float* b, void* out, uint32_t ldc, 
 enum GemmMode : int {
     GEMM_PLAIN = 0,   // out[m, n] (f32 or bf16) = act(acc + bias) (+ residual)
     GEMM_QKV = 1,     // n = 3*d: columns [0,d) -> q (bf16), [d,2d) -> K cache rows, [2d,3d) -> V cache rows
-    GEMM_SWIGLU = 2   // n = 2*f packed in blocks of 16: out[m, f] bf16 = silu(gate) * up
+    GEMM_SWIGLU = 2,  // n = 2*f packed in blocks of 16: out[m, f] bf16 = silu(gate) * up
+    GEMM_ARGMAX = 3   // no matrix leaves the kernel: per (row, column tile) the greedy candidate (key, index)
 };
 struct GemmQkvTargets {
     bf16* q = nullptr;        // [m, d]
@@ -104,6 +105,11 @@ int launch_gemm_bf16(const bf16* a, const bf16* bt, void* out, uint32_t ldc, uin
                      uint32_t k, GemmMode mode, const GemmEpilogue& ep, const GemmQkvTargets* qkv,
                      int* d_status, cudaStream_t stream);
 extern int g_gemm_engine;  // 0 auto, 1 CUDA-core only, 2 tcgen05 only
+// Greedy ids straight from the LM-head GEMM: ids[r] = last index of the maximum of row r of a . bt^T
+// under IEEE totalOrder.  `candidates` is scratch for rows * ceil(n / 32) uint2 values.
+uint64_t lm_head_argmax_scratch_bytes(uint32_t rows, uint32_t n);
+int launch_lm_head_argmax(const bf16* a, const bf16* bt, uint32_t m, uint32_t n, uint32_t k, void* candidates,
+                          uint32_t* ids, int* d_status, cudaStream_t stream);
 
 int launch_embedding(const void* tok, const void* pos, const uint32_t* ids, float* out, uint32_t rows,
                      uint32_t chunk, uint32_t position0, const uint32_t* d_position, uint32_t vocab,
@@ -167,6 +173,11 @@ int launch_prefill_attention(const bf16* q, const bf16* k_cache, const bf16* v_c
 // ---- device helpers ----------------------------------------------------------
 #ifdef __CUDACC__
 
+// Sign-folded bit pattern: integer order of the keys is IEEE totalOrder of the floats.
+__device__ __forceinline__ int total_order_key(float x) {
+    int bits = __float_as_int(x);
+    return bits ^ (int)(((unsigned)(bits >> 31)) >> 1);
+}
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t hi16) { return __uint_as_float(hi16 << 16); }
 // Two packed bf16 (low half = element 0) -> two f32.
 __device__ __forceinline__ float2 bf16x2_to_f32(uint32_t v) {

@@ -99,6 +99,18 @@ struct tnsr_b200_decoder {
     std::vector<float> host_bqkv, host_bgu;
     bool profile_attention = false;
     KernelTimer attention_timer;
+    void* lm_candidates = nullptr;  // per (session, vocabulary tile) greedy candidates of the fused LM head
+    // single-token steps are replayed from a captured CUDA graph; the position lives in d_pos
+    uint32_t* d_pos = nullptr;
+    struct StepGraph {
+        const uint32_t* tokens;
+        uint32_t* argmax;
+        cudaGraphExec_t exec;
+        uint64_t kernels;
+    };
+    std::vector<StepGraph> graphs;
+    bool use_graphs = true;
+    bool stepped_once = false;  // a plain (uncaptured) single-token step has run: buffers and attributes are set
 };
 
 namespace {
@@ -132,6 +144,11 @@ int cuda_fail(tnsr_b200_decoder* dec, cudaError_t e, const char* what) {
             return rc__;                                                \
         }                                                               \
     } while (0)
+
+void drop_graphs(tnsr_b200_decoder* dec) {
+    for (auto& g : dec->graphs) cudaGraphExecDestroy(g.exec);
+    dec->graphs.clear();
+}
 
 int dev_alloc(tnsr_b200_decoder* dec, void** out, size_t bytes, bool zero) {
     if (bytes == 0) bytes = 16;
@@ -252,6 +269,7 @@ int ensure_rows(tnsr_b200_decoder* dec, uint32_t rows, uint32_t logit_rows) {
     const uint64_t d = c.embed_dim, f = c.feed_forward_dim;
     const size_t a = dec->bf16_path ? 2 : 4;
     int rc;
+    if (rows > dec->rows_cap || logit_rows > dec->logit_rows_cap || rows > dec->tokens_cap) drop_graphs(dec);
     if (rows > dec->rows_cap) {
         CU(dec, cudaStreamSynchronize(dec->stream));
         dev_free(dec, dec->h); dev_free(dec, dec->n); dev_free(dec, dec->q); dev_free(dec, dec->att);
@@ -344,12 +362,16 @@ int step_strict(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk
 }
 
 // ---- one step on the bf16 tensor-core path -----------------------------------
-int step_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, uint32_t position, uint32_t logit_rows) {
+// `d_position` (optional): the position as a device scalar, so that a captured graph of the step can be replayed
+// while the position advances.  `fused_ids` (optional): greedy ids come straight out of the LM-head GEMM and no
+// logits are written (only when the logits mode is NONE).
+int step_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, uint32_t position,
+              const uint32_t* d_position, uint32_t logit_rows, uint32_t* fused_ids) {
     const tnsr_b200_config& c = dec->cfg;
     const uint32_t d = c.embed_dim, f = c.feed_forward_dim, H = c.num_heads, hd = d / H, B = c.batch, rows = B * chunk;
     cudaStream_t st = dec->stream;
     bf16* n = (bf16*)dec->n; bf16* q = (bf16*)dec->q; bf16* att = (bf16*)dec->att; bf16* ff = (bf16*)dec->ff;
-    RUN(dec, launch_embedding(dec->tok, dec->pos, d_tokens, dec->h, rows, chunk, position, nullptr, c.vocab_size, d,
+    RUN(dec, launch_embedding(dec->tok, dec->pos, d_tokens, dec->h, rows, chunk, position, d_position, c.vocab_size, d,
                               TNSR_B200_BF16, dec->d_status, st));
     const bool fast_decode = chunk == 1 && dec->attn_ws && decode_attention_supported(H, hd);
     bool planned = false;
@@ -359,19 +381,19 @@ int step_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, 
         eq.bias = L.bqkv;
         GemmQkvTargets tg;
         tg.q = q; tg.k_cache = (bf16*)L.kcache; tg.v_cache = (bf16*)L.vcache;
-        tg.d = d; tg.chunk = chunk; tg.capacity = c.capacity; tg.position = position;
+        tg.d = d; tg.chunk = chunk; tg.capacity = c.capacity; tg.position = position; tg.d_position = d_position;
         RUN(dec, launch_gemm_bf16(n, L.wqkv, nullptr, 0, rows, 3 * d, d, GEMM_QKV, eq, &tg, dec->d_status, st));
         if (fast_decode) {
             // every session holds position + 1 keys; the item list is the same for all layers of this step
-            RUN(dec, launch_decode_attention_ex(q, (const bf16*)L.kcache, (const bf16*)L.vcache, nullptr, nullptr, position + 1,
-                                                att, dec->attn_ws, dec->attn_ws_bytes, B, c.capacity, H, hd, !planned,
-                                                dec->d_status, st));
+            RUN(dec, launch_decode_attention_ex(q, (const bf16*)L.kcache, (const bf16*)L.vcache, nullptr, d_position,
+                                                d_position ? 1 : position + 1, att, dec->attn_ws, dec->attn_ws_bytes, B,
+                                                c.capacity, H, hd, !planned, dec->d_status, st));
             planned = true;
         } else if (chunk > 1 && prefill_attention_supported(hd)) {
-            RUN(dec, launch_prefill_attention(q, (const bf16*)L.kcache, (const bf16*)L.vcache, att, B, chunk, position, nullptr,
+            RUN(dec, launch_prefill_attention(q, (const bf16*)L.kcache, (const bf16*)L.vcache, att, B, chunk, position, d_position,
                                               c.capacity, H, hd, st));
         } else {
-            RUN(dec, launch_attention_generic(q, (const bf16*)L.kcache, (const bf16*)L.vcache, att, B, chunk, position, nullptr,
+            RUN(dec, launch_attention_generic(q, (const bf16*)L.kcache, (const bf16*)L.vcache, att, B, chunk, position, d_position,
                                               c.capacity, H, hd, st));
         }
         GemmEpilogue eo;
@@ -403,23 +425,30 @@ int step_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, 
         src = dec->hl;
     }
     RUN(dec, launch_layernorm(src, dec->fnw, dec->fnb, n, logit_rows, d, c.layer_norm_epsilon, TNSR_B200_BF16, false, st));
-    GemmEpilogue el; el.out_dtype = TNSR_B200_F32;
     // the tied head: the token table [vocab, d] already is the K-major operand
+    if (fused_ids) {
+        RUN(dec, launch_lm_head_argmax(n, (const bf16*)dec->tok, logit_rows, c.vocab_size, d, dec->lm_candidates, fused_ids,
+                                       dec->d_status, st));
+        return TNSR_B200_OK;
+    }
+    GemmEpilogue el; el.out_dtype = TNSR_B200_F32;
     RUN(dec, launch_gemm_bf16(n, (const bf16*)dec->tok, dec->logits, c.vocab_size, logit_rows, c.vocab_size, d, GEMM_PLAIN, el,
                               nullptr, dec->d_status, st));
     return TNSR_B200_OK;
 }
 
-int run_step(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, uint32_t position, uint32_t* d_argmax_out) {
+int run_step_direct(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, uint32_t position,
+                    const uint32_t* d_position, uint32_t* d_argmax_out) {
     const tnsr_b200_config& c = dec->cfg;
     const uint32_t rows = c.batch * chunk;
     const uint32_t logit_rows = c.logits_mode == TNSR_B200_LOGITS_ALL ? rows : c.batch;
+    const bool fuse_ids = dec->bf16_path && c.logits_mode == TNSR_B200_LOGITS_NONE && d_argmax_out && dec->lm_candidates;
     t_attention_timer = dec->profile_attention ? &dec->attention_timer : nullptr;
-    int rc = dec->bf16_path ? step_bf16(dec, d_tokens, chunk, position, logit_rows)
+    int rc = dec->bf16_path ? step_bf16(dec, d_tokens, chunk, position, d_position, logit_rows, fuse_ids ? d_argmax_out : nullptr)
                             : step_strict(dec, d_tokens, chunk, position, logit_rows);
     t_attention_timer = nullptr;
     if (rc) return rc;
-    if (d_argmax_out) {
+    if (d_argmax_out && !fuse_ids) {
         // last position of every session
         const float* base = dec->logits;
         uint32_t stride = c.vocab_size;
@@ -429,6 +458,52 @@ int run_step(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, u
         }
         RUN(dec, launch_argmax(base, d_argmax_out, c.batch, c.vocab_size, stride, dec->stream));
     }
+    return TNSR_B200_OK;
+}
+
+// One step.  Single-token steps of the bf16 path are captured once per (ids pointer, output pointer) pair
+// and replayed: the kernels read the position from dec->d_pos, which a one-thread kernel sets before each replay.
+int run_step(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, uint32_t position, uint32_t* d_argmax_out) {
+    const bool graphable = dec->use_graphs && dec->bf16_path && chunk == 1 && !dec->profile_attention && dec->stepped_once &&
+                           !debug_sync_enabled();
+    if (!graphable) {
+        int rc = run_step_direct(dec, d_tokens, chunk, position, nullptr, d_argmax_out);
+        if (rc == TNSR_B200_OK && chunk == 1) dec->stepped_once = true;
+        return rc;
+    }
+    tnsr_b200_decoder::StepGraph* found = nullptr;
+    for (auto& g : dec->graphs)
+        if (g.tokens == d_tokens && g.argmax == d_argmax_out) { found = &g; break; }
+    if (!found) {
+        if (dec->graphs.size() >= 8) drop_graphs(dec);
+        const uint64_t before = g_launches.load();
+        cudaGraph_t graph = nullptr;
+        CU(dec, cudaStreamBeginCapture(dec->stream, cudaStreamCaptureModeThreadLocal));
+        int rc = run_step_direct(dec, d_tokens, 1, 0, dec->d_pos, d_argmax_out);
+        cudaError_t e = cudaStreamEndCapture(dec->stream, &graph);
+        const uint64_t kernels = g_launches.load() - before;
+        g_launches.fetch_sub(kernels);  // nothing ran yet; replays are counted below
+        if (rc != TNSR_B200_OK || e != cudaSuccess || !graph) {
+            if (graph) cudaGraphDestroy(graph);
+            cudaGetLastError();
+            dec->use_graphs = false;  // fall back to direct launches for the rest of this session
+            if (rc != TNSR_B200_OK) return rc;
+            return run_step_direct(dec, d_tokens, chunk, position, nullptr, d_argmax_out);
+        }
+        cudaGraphExec_t exec = nullptr;
+        e = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            dec->use_graphs = false;
+            return run_step_direct(dec, d_tokens, chunk, position, nullptr, d_argmax_out);
+        }
+        dec->graphs.push_back({d_tokens, d_argmax_out, exec, kernels});
+        found = &dec->graphs.back();
+    }
+    RUN(dec, launch_fill_u32(dec->d_pos, position, 1, dec->stream));
+    CU(dec, cudaGraphLaunch(found->exec, dec->stream));
+    count_launch(found->kernels);
     return TNSR_B200_OK;
 }
 
@@ -533,6 +608,14 @@ int tnsr_b200_decoder_create(const tnsr_b200_config* config, tnsr_b200_decoder**
     if ((rc = dev_alloc(dec, (void**)&dec->hl, (size_t)config->batch * d * 4, false))) return bail(rc);
     if ((rc = dev_alloc(dec, (void**)&dec->d_argmax, (size_t)config->batch * 4, true))) return bail(rc);
     if ((rc = dev_alloc(dec, (void**)&dec->d_status, 16, true))) return bail(rc);
+    if ((rc = dev_alloc(dec, (void**)&dec->d_pos, 16, true))) return bail(rc);
+    if (dec->bf16_path && config->logits_mode == TNSR_B200_LOGITS_NONE)
+        if ((rc = dev_alloc(dec, &dec->lm_candidates, lm_head_argmax_scratch_bytes(config->batch, config->vocab_size), false)))
+            return bail(rc);
+    {
+        const char* v = std::getenv("TNSR_B200_NO_GRAPH");
+        if (v && v[0] == '1') dec->use_graphs = false;
+    }
     if (cudaMallocHost((void**)&dec->h_argmax, (size_t)config->batch * 4) != cudaSuccess ||
         cudaMallocHost((void**)&dec->h_status, 16) != cudaSuccess)
         return bail(cuda_fail(dec, cudaGetLastError(), "cudaMallocHost"));
@@ -561,6 +644,7 @@ void tnsr_b200_decoder_destroy(tnsr_b200_decoder* dec) {
     if (dec->h_argmax) cudaFreeHost(dec->h_argmax);
     if (dec->h_status) cudaFreeHost(dec->h_status);
     if (dec->h_stage) cudaFreeHost(dec->h_stage);
+    drop_graphs(dec);
     for (cudaEvent_t e : dec->attention_timer.events) cudaEventDestroy(e);
     if (dec->stream) cudaStreamDestroy(dec->stream);
     cudaGetLastError();

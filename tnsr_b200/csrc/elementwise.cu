@@ -232,15 +232,10 @@ int launch_gather_last_rows(const float* x, float* out, uint32_t sessions, uint3
 // IEEE totalOrder (src/nn/kv_cache.rs:148-153).  Keys are the sign-folded bit
 // patterns, compared as signed integers; ties prefer the larger index.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ int total_order_key(float x) {
-    int bits = __float_as_int(x);
-    return bits ^ (int)(((unsigned)(bits >> 31)) >> 1);
-}
-
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 argmax_kernel(const float* __restrict__ logits, uint32_t* __restrict__ out, uint32_t vocab, uint32_t row_stride) {
-    __shared__ int keys[8];
-    __shared__ uint32_t idxs[8];
+    __shared__ int keys[32];
+    __shared__ uint32_t idxs[32];
     const float* row = logits + (size_t)blockIdx.x * row_stride;
     int best = INT_MIN;
     uint32_t best_i = 0;
@@ -264,7 +259,7 @@ argmax_kernel(const float* __restrict__ logits, uint32_t* __restrict__ out, uint
         int bk = INT_MIN;
         uint32_t bi = 0;
         bool any = false;
-        for (int wi = 0; wi < 8; ++wi) {
+        for (int wi = 0; wi < (int)(blockDim.x >> 5); ++wi) {
             // a warp with no element reports INT_MIN at index 0; a real INT_MIN key can only
             // lose or tie against it, and ties resolve towards the larger index
             if (!any || keys[wi] > bk || (keys[wi] == bk && idxs[wi] > bi)) { bk = keys[wi]; bi = idxs[wi]; any = true; }
@@ -276,7 +271,7 @@ argmax_kernel(const float* __restrict__ logits, uint32_t* __restrict__ out, uint
 int launch_argmax(const float* logits, uint32_t* out, uint32_t rows, uint32_t vocab, uint32_t row_stride,
                   cudaStream_t stream) {
     if (rows == 0) return TNSR_B200_OK;
-    argmax_kernel<<<rows, 256, 0, stream>>>(logits, out, vocab, row_stride);
+    argmax_kernel<<<rows, vocab >= 8192 ? 1024 : 256, 0, stream>>>(logits, out, vocab, row_stride);
     count_launch();
     return check_launch("argmax");
 }

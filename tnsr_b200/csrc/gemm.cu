@@ -123,7 +123,19 @@ gemm_simple_kernel(const bf16* __restrict__ a, uint32_t lda, const bf16* __restr
 #pragma unroll
         for (int j = 0; j < 4; ++j) cs[ty * 4 + i][tx * 4 + j] = acc[i][j];
     __syncthreads();
-    if (MODE == GEMM_SWIGLU) {
+    if (MODE == GEMM_ARGMAX) {
+        // one candidate per (row, 64-column tile): thread r scans its row of the tile in column order
+        if (tid < SB && m0 + tid < P.m) {
+            int best = 0;
+            uint32_t best_i = 0;
+            bool have = false;
+            for (uint32_t c = 0; c < SB && n0 + c < P.n; ++c) {
+                const int key = total_order_key(cs[tid][c]);
+                if (!have || key >= best) { best = key; best_i = n0 + c; have = true; }
+            }
+            reinterpret_cast<uint2*>(P.out)[(size_t)(m0 + tid) * P.ldc + blockIdx.x] = make_uint2((uint32_t)best, best_i);
+        }
+    } else if (MODE == GEMM_SWIGLU) {
         // 64 packed columns = 2 blocks of (16 gate, 16 up) -> 32 output columns
         for (uint32_t e = tid; e < SB * 32; e += 256) {
             uint32_t r = e / 32, oc_local = e % 32;
@@ -154,6 +166,7 @@ static int launch_simple(const bf16* a, uint32_t lda, const bf16* bt, const EpiP
         case GEMM_PLAIN: gemm_simple_kernel<GEMM_PLAIN><<<grid, 256, 0, stream>>>(a, lda, bt, P, k); break;
         case GEMM_QKV: gemm_simple_kernel<GEMM_QKV><<<grid, 256, 0, stream>>>(a, lda, bt, P, k); break;
         case GEMM_SWIGLU: gemm_simple_kernel<GEMM_SWIGLU><<<grid, 256, 0, stream>>>(a, lda, bt, P, k); break;
+        case GEMM_ARGMAX: gemm_simple_kernel<GEMM_ARGMAX><<<grid, 256, 0, stream>>>(a, lda, bt, P, k); break;
     }
     count_launch();
     return check_launch("gemm_simple");
@@ -170,7 +183,7 @@ constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // a wait that lasts 2 s give
 
 template <int BN>
 struct TcShape {
-    static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+    static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);  // 196 KB (160 KB at BN 32)
     static constexpr uint32_t A_BYTES = BM * BK * 2;
     static constexpr uint32_t B_BYTES = BN * BK * 2;
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -512,13 +525,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after();
             const uint32_t row = tm * BM + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + ab * BN;
+            int best = 0;
+            uint32_t best_i = 0;
+            bool have = false;
 #pragma unroll 1
             for (uint32_t c = 0; c < BN; c += 32) {
                 float acc[32];
                 tmem_ld32(taddr + c, acc);
                 tmem_ld_wait();
-                epilogue_chunk<MODE>(prm.epi, row, tn * BN + c, acc);
+                if (MODE == GEMM_ARGMAX) {
+                    const uint32_t col0 = tn * BN + c;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = total_order_key(acc[i]);
+                        if (col0 + i < prm.epi.n && (!have || key >= best)) { best = key; best_i = col0 + i; have = true; }
+                    }
+                } else {
+                    epilogue_chunk<MODE>(prm.epi, row, tn * BN + c, acc);
+                }
             }
+            if (MODE == GEMM_ARGMAX && row < prm.epi.m)
+                reinterpret_cast<uint2*>(prm.epi.out)[(size_t)row * prm.epi.ldc + tn] = make_uint2((uint32_t)best, best_i);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty + ab);
@@ -587,11 +614,13 @@ static int sm_count() {
 template <int BN, int MODE>
 static int launch_tc_t(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& prm, cudaStream_t stream) {
     using S = TcShape<BN>;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
         if (cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM_BYTES) != cudaSuccess)
             return check_launch("gemm_tc attribute");
-        configured = true;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     uint32_t tiles = prm.tiles_m * prm.tiles_n;
     uint32_t grid = tiles < (uint32_t)sm_count() ? tiles : (uint32_t)sm_count();
@@ -606,6 +635,7 @@ static int launch_tc_mode(const CUtensorMap& ma, const CUtensorMap& mb, const Tc
         case GEMM_PLAIN: return launch_tc_t<BN, GEMM_PLAIN>(ma, mb, prm, stream);
         case GEMM_QKV: return launch_tc_t<BN, GEMM_QKV>(ma, mb, prm, stream);
         case GEMM_SWIGLU: return launch_tc_t<BN, GEMM_SWIGLU>(ma, mb, prm, stream);
+        case GEMM_ARGMAX: return launch_tc_t<BN, GEMM_ARGMAX>(ma, mb, prm, stream);
     }
     return TNSR_B200_ERR_INVALID_ARGUMENT;
 }
@@ -615,9 +645,11 @@ static bool tc_eligible(const bf16* a, uint32_t lda, const bf16* bt, uint32_t k)
            (reinterpret_cast<uintptr_t>(bt) % 16 == 0) && encode_fn() != nullptr;
 }
 
-int launch_gemm_bf16(const bf16* a, const bf16* bt, void* out, uint32_t ldc, uint32_t m, uint32_t n,
-                     uint32_t k, GemmMode mode, const GemmEpilogue& ep, const GemmQkvTargets* qkv,
-                     int* d_status, cudaStream_t stream) {
+// Shared body of the public launchers.  `tiles_n_out` (optional) receives the number of column
+// tiles the chosen engine used, which GEMM_ARGMAX callers need to read the candidates back.
+static int launch_gemm_impl(const bf16* a, const bf16* bt, void* out, uint32_t ldc, uint32_t m, uint32_t n, uint32_t k,
+                            GemmMode mode, const GemmEpilogue& ep, const GemmQkvTargets* qkv, int* d_status,
+                            uint32_t* tiles_n_out, cudaStream_t stream) {
     if (m == 0 || n == 0) return TNSR_B200_OK;
     if (k == 0) return TNSR_B200_ERR_INVALID_ARGUMENT;
     if (mode == GEMM_QKV && (!qkv || qkv->d == 0 || n != 3 * qkv->d || qkv->chunk == 0)) return TNSR_B200_ERR_INVALID_ARGUMENT;
@@ -635,19 +667,23 @@ int launch_gemm_bf16(const bf16* a, const bf16* bt, void* out, uint32_t ldc, uin
     P.n = n;
     const uint32_t lda = k;
     const bool can_tc = tc_eligible(a, lda, bt, k);
+    auto simple = [&]() {
+        if (mode == GEMM_ARGMAX) P.ldc = ceil_div(n, SB);
+        if (tiles_n_out) *tiles_n_out = ceil_div(n, SB);
+        return launch_simple(a, lda, bt, P, k, mode, stream);
+    };
     if (g_gemm_engine == 1 || !can_tc) {
         if (g_gemm_engine == 2) {
             set_thread_error("gemm: shape or alignment outside the tcgen05 engine (k % 8, 16-byte pointers)");
             return TNSR_B200_ERR_UNSUPPORTED;
         }
-        return launch_simple(a, lda, bt, P, k, mode, stream);
+        return simple();
     }
-    // tile width: the widest that still gives every SM a tile
+    // tile width: the widest that still gives every SM a tile (32 at the narrowest)
     const uint32_t tiles_m = ceil_div(m, BM);
     uint32_t bn = 256;
-    while (bn > 64 && (uint64_t)tiles_m * ceil_div(n, bn) < (uint64_t)sm_count()) bn >>= 1;
+    while (bn > 32 && (uint64_t)tiles_m * ceil_div(n, bn) < (uint64_t)sm_count()) bn >>= 1;
     TcParams prm;
-    prm.epi = P;
     prm.k = k;
     prm.tiles_m = tiles_m;
     prm.tiles_n = ceil_div(n, bn);
@@ -658,13 +694,65 @@ int launch_gemm_bf16(const bf16* a, const bf16* bt, void* out, uint32_t ldc, uin
             set_thread_error("gemm: tensor map encoding failed");
             return TNSR_B200_ERR_CUDA;
         }
-        return launch_simple(a, lda, bt, P, k, mode, stream);
+        return simple();
     }
+    if (mode == GEMM_ARGMAX) P.ldc = prm.tiles_n;
+    if (tiles_n_out) *tiles_n_out = prm.tiles_n;
+    prm.epi = P;
     switch (bn) {
         case 256: return launch_tc_mode<256>(ma, mb, prm, mode, stream);
         case 128: return launch_tc_mode<128>(ma, mb, prm, mode, stream);
-        default: return launch_tc_mode<64>(ma, mb, prm, mode, stream);
+        case 64: return launch_tc_mode<64>(ma, mb, prm, mode, stream);
+        default: return launch_tc_mode<32>(ma, mb, prm, mode, stream);
     }
+}
+
+int launch_gemm_bf16(const bf16* a, const bf16* bt, void* out, uint32_t ldc, uint32_t m, uint32_t n,
+                     uint32_t k, GemmMode mode, const GemmEpilogue& ep, const GemmQkvTargets* qkv,
+                     int* d_status, cudaStream_t stream) {
+    if (mode == GEMM_ARGMAX) return TNSR_B200_ERR_INVALID_ARGUMENT;  // use launch_lm_head_argmax
+    return launch_gemm_impl(a, bt, out, ldc, m, n, k, mode, ep, qkv, d_status, nullptr, stream);
+}
+
+// ---- greedy ids from the LM head without materialising logits --------------------
+// One warp per row folds the per-tile candidates; ties between tiles go to the larger index,
+// which is the later tile, so the result is the last index of the row maximum.
+__global__ void __launch_bounds__(128)
+argmax_finish_kernel(const uint2* __restrict__ cand, uint32_t* __restrict__ ids, uint32_t rows, uint32_t tiles) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t row = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    int best = 0;
+    uint32_t best_i = 0;
+    bool have = false;
+    for (uint32_t t = lane; t < tiles; t += 32) {
+        const uint2 c = cand[(size_t)row * tiles + t];
+        const int key = (int)c.x;
+        if (!have || key > best || (key == best && c.y > best_i)) { best = key; best_i = c.y; have = true; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const int ok = __shfl_xor_sync(0xffffffffu, best, o);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        const int oh = __shfl_xor_sync(0xffffffffu, (int)have, o);
+        if (oh && (!have || ok > best || (ok == best && oi > best_i))) { best = ok; best_i = oi; have = true; }
+    }
+    if (lane == 0) ids[row] = best_i;
+}
+
+uint64_t lm_head_argmax_scratch_bytes(uint32_t rows, uint32_t n) { return (uint64_t)rows * ceil_div(n, 32) * sizeof(uint2); }
+
+int launch_lm_head_argmax(const bf16* a, const bf16* bt, uint32_t m, uint32_t n, uint32_t k, void* candidates,
+                          uint32_t* ids, int* d_status, cudaStream_t stream) {
+    if (m == 0) return TNSR_B200_OK;
+    if (n == 0 || !candidates || !ids) return TNSR_B200_ERR_INVALID_ARGUMENT;
+    GemmEpilogue ep;
+    uint32_t tiles = 0;
+    int rc = launch_gemm_impl(a, bt, candidates, 0, m, n, k, GEMM_ARGMAX, ep, nullptr, d_status, &tiles, stream);
+    if (rc) return rc;
+    argmax_finish_kernel<<<ceil_div(m, 4), 128, 0, stream>>>(reinterpret_cast<const uint2*>(candidates), ids, m, tiles);
+    count_launch();
+    return check_launch("argmax_finish");
 }
 
 }  // namespace tb
