@@ -263,7 +263,8 @@ TNSR_B200_API int tnsr_b200_pack_gate_up(const void* w_gate, const void* w_up, c
  * bf16; k_cache, v_cache: [batch, capacity, heads*head_dim] bf16; lengths[b]
  * = live keys of session b including its newest row (1..capacity; 0 gives a
  * zero output row).  workspace: device scratch of at least
- * tnsr_b200_decode_attention_workspace(...) bytes.  Scores are scaled by
+ * tnsr_b200_decode_attention_workspace(...) bytes; bytes 64..67 of it hold a
+ * status word (0 = ok) once the stream has passed the call.  Scores are scaled by
  * 1/sqrt(head_dim); softmax statistics and accumulation are f32. */
 TNSR_B200_API uint64_t tnsr_b200_decode_attention_workspace(uint32_t batch, uint32_t capacity,
                                                             uint32_t heads, uint32_t head_dim);
@@ -280,9 +281,9 @@ TNSR_B200_API int tnsr_b200_decode_attention(const void* q, const void* k_cache,
  * counterpart in the reference.  The scratch is a fixed array of
  * TNSR_B200_STATIC_SCRATCH_BYTES inside the library, present on every GPU that
  * loads it until the process exits; the call allocates and frees nothing.
- * Limits: the batch must fit (at least 2048 + batch * (24 + heads *
- * (head_dim + 2) * 4) bytes), otherwise TNSR_B200_ERR_UNSUPPORTED; larger
- * batches simply get coarser key slabs than with a roomy workspace.  All calls
+ * Limit: tnsr_b200_decode_attention_workspace(batch, capacity, heads,
+ * head_dim) must not exceed the array (it grows with batch * heads * head_dim,
+ * not with capacity), otherwise TNSR_B200_ERR_UNSUPPORTED.  All calls
  * share the array, so calls that overlap on the GPU (different streams or host
  * threads) race: keep them on one stream.  The first call on each device looks
  * up the array's device address once; make that first call before any stream

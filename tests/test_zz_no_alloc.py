@@ -73,8 +73,9 @@ def test_static_scratch_entry_point_matches_the_workspace_one_twice_in_a_row():
 def test_static_scratch_entry_point_rejects_what_does_not_fit():
     from tnsr_b200 import _native
     heads, hd = 16, 64
-    per_session = 24 + heads * (hd + 2) * 4
-    too_many = (STATIC_BYTES - 2048) // per_session + 1
+    too_many = 1
+    while lib().tnsr_b200_decode_attention_workspace(too_many, 64, heads, hd) <= STATIC_BYTES:
+        too_many *= 2
     dummy = torch.zeros(16, dtype=torch.uint8, device="cuda")
     code = lib().tnsr_b200_decode_attention_static(ptr(dummy), ptr(dummy), ptr(dummy), ptr(dummy), ptr(dummy), too_many, 64,
                                                    heads, hd, None, stream())

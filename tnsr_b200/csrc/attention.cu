@@ -21,6 +21,7 @@
 namespace tb {
 
 thread_local KernelTimer* t_attention_timer = nullptr;
+thread_local bool t_pdl = false;
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -44,6 +45,8 @@ attention_generic_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc
                          bf16* __restrict__ out, uint32_t total_queries, uint32_t chunk, uint32_t position,
                          const uint32_t* __restrict__ d_position, uint32_t capacity, uint32_t heads, uint32_t hd,
                          float scale_log2) {
+    pdl_wait();
+    pdl_trigger();
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t idx = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (idx >= total_queries) return;
@@ -102,8 +105,8 @@ int launch_attention_generic(const bf16* q, const bf16* k_cache, const bf16* v_c
     uint64_t total = (uint64_t)sessions * heads * chunk;
     if (total > 0x7fffffffull) return TNSR_B200_ERR_UNSUPPORTED;
     const float scale_log2 = (1.0f / sqrtf((float)head_dim)) * 1.4426950408889634f;
-    attention_generic_kernel<<<(unsigned)ceil_div64(total, 4), 128, 0, stream>>>(
-        q, k_cache, v_cache, out, (uint32_t)total, chunk, position, d_position, capacity, heads, head_dim, scale_log2);
+    launch_kernel(attention_generic_kernel, dim3((unsigned)ceil_div64(total, 4)), dim3(128), 0, stream, q, k_cache, v_cache, out,
+                  (uint32_t)total, chunk, position, d_position, capacity, heads, head_dim, scale_log2);
     count_launch();
     return check_launch("attention_generic");
 }
@@ -115,58 +118,54 @@ constexpr uint32_t DA_KS = 16;             // keys per ring stage
 constexpr uint32_t DA_MAX_STAGES = 8;
 constexpr uint32_t DA_SMEM_BUDGET = 200 * 1024;
 constexpr uint64_t DA_WAIT_LIMIT_NS = 2000000000ull;
-constexpr uint32_t DA_MIN_SLAB = 32;       // smallest key slab per work item
+constexpr uint32_t DA_MAX_CTAS = 256;      // upper bound on the grid (one CTA per SM)
 
+// A work item: keys [key0, key0 + nkeys) of one session, all heads.  `slot` is the index of its
+// partial result, or DA_DIRECT when the item covers the whole session and writes the output row itself.
+constexpr uint32_t DA_DIRECT = 0xffffffffu;
 struct DaItem {
-    uint32_t session, key0, nkeys, pad;
+    uint32_t session, key0, nkeys, slot;
 };
 
+// Work is split by position in the concatenation of all sessions' live keys, counted in stages of
+// DA_KS keys: CTA c owns stages [c * quota, (c + 1) * quota).  Every CTA therefore streams the same
+// amount of K/V (+-1 stage) whatever the per-session lengths are, a session is cut only where a CTA
+// boundary falls inside it, and there are at most batch + grid items.
+//
 // Workspace layout (all offsets 256-byte aligned):
-//   header  : uint32 n_items, slab
-//   first   : uint32 [batch]      first item of each session
-//   count   : uint32 [batch]      items of each session
-//   done    : uint32 [batch * heads]  partials stored so far per (session, head); zero between launches
-//   items   : DaItem [max_items]
-//   partial : float  [max_items][heads][head_dim + 2]   (numerator, then max, then sum)
+//   header    : uint32 total_stages, quota, n_items
+//   first     : uint32 [batch]          first partial slot of each session
+//   count     : uint32 [batch]          number of pieces of each session (0 for an empty session)
+//   done      : uint32 [batch * heads]  partials stored so far per (session, head); zero between launches
+//   sstart    : uint32 [batch + 1]      first global stage of each session
+//   cta_begin : uint32 [DA_MAX_CTAS + 1] first item of each CTA
+//   items     : DaItem [batch + DA_MAX_CTAS]
+//   partial   : float  [batch + DA_MAX_CTAS][heads][head_dim + 2]   (numerator, then max, then sum)
 struct DaLayout {
-    uint64_t first, count, done, items, partial, bytes;
+    uint64_t first, count, done, sstart, cta_begin, items, partial, bytes;
     uint32_t max_items;
 };
 
 static uint64_t align256(uint64_t x) { return (x + 255) & ~255ull; }
 
-static DaLayout da_layout_for(uint32_t batch, uint32_t heads, uint64_t per_item, uint64_t items) {
+static DaLayout da_layout(uint32_t batch, uint32_t heads, uint32_t head_dim) {
     DaLayout L;
+    const uint64_t per_item = (uint64_t)heads * (head_dim + 2) * 4;
+    L.max_items = batch + DA_MAX_CTAS;
     L.first = 256;
     L.count = align256(L.first + 4ull * batch);
     L.done = align256(L.count + 4ull * batch);
-    L.items = align256(L.done + 4ull * batch * heads);
-    L.max_items = (uint32_t)(items > 0x7fffffffull ? 0x7fffffffull : items);
+    L.sstart = align256(L.done + 4ull * batch * heads);
+    L.cta_begin = align256(L.sstart + 4ull * (batch + 1));
+    L.items = align256(L.cta_begin + 4ull * (DA_MAX_CTAS + 1));
     L.partial = align256(L.items + sizeof(DaItem) * (uint64_t)L.max_items);
     L.bytes = L.partial + per_item * L.max_items;
     return L;
 }
 
-// budget == 0: the preferred size.  Otherwise the largest item count that fits
-// in `budget` bytes (the caller checks that it still covers one item per session).
-static DaLayout da_layout(uint32_t batch, uint32_t capacity, uint32_t heads, uint32_t head_dim, uint64_t budget) {
-    // Enough items for the smallest slab, but never more partial storage than ~256 MiB.
-    const uint64_t per_item = (uint64_t)heads * (head_dim + 2) * 4;
-    uint64_t want = (uint64_t)batch * ceil_div(capacity, DA_MIN_SLAB);
-    uint64_t cap_items = (256ull << 20) / per_item;
-    if (cap_items < batch) cap_items = batch;
-    uint64_t items = want < cap_items ? want : cap_items;
-    DaLayout L = da_layout_for(batch, heads, per_item, items);
-    if (budget == 0 || L.bytes <= budget) return L;
-    const uint64_t fixed = da_layout_for(batch, heads, per_item, 0).bytes;
-    items = budget > fixed ? (budget - fixed) / (per_item + sizeof(DaItem)) : 0;
-    L = da_layout_for(batch, heads, per_item, items);
-    while (L.bytes > budget && items > 0) L = da_layout_for(batch, heads, per_item, --items);
-    return L;
-}
-
 uint64_t decode_attention_workspace_bytes(uint32_t batch, uint32_t capacity, uint32_t heads, uint32_t head_dim) {
-    return da_layout(batch, capacity, heads, head_dim, 0).bytes;
+    (void)capacity;  // the scratch depends on the number of sessions, not on how long they may grow
+    return da_layout(batch, heads, head_dim).bytes;
 }
 
 bool decode_attention_supported(uint32_t heads, uint32_t head_dim) {
@@ -176,15 +175,17 @@ bool decode_attention_supported(uint32_t heads, uint32_t head_dim) {
     return stage * 2 <= DA_SMEM_BUDGET;  // at least a double buffer
 }
 
-// ---- plan: choose the slab, build the item list --------------------------------
-// One block.  lengths == nullptr means every session has (d_position ? *d_position : 0) + extra keys.
+// ---- plan: one block ---------------------------------------------------------------
+// lengths == nullptr means every session has (d_position ? *d_position : 0) + extra keys.
 __global__ void __launch_bounds__(1024)
 da_plan_kernel(const uint32_t* __restrict__ lengths, const uint32_t* __restrict__ d_position, uint32_t extra,
-               uint32_t batch, uint32_t heads, uint32_t capacity, uint32_t target_items, uint32_t max_items,
-               uint32_t* __restrict__ header, uint32_t* __restrict__ first, uint32_t* __restrict__ count,
-               uint32_t* __restrict__ done, DaItem* __restrict__ items, int* __restrict__ d_status) {
-    __shared__ unsigned long long red[32];
-    __shared__ uint32_t s_slab, s_carry, s_warp_tot[32];
+               uint32_t batch, uint32_t heads, uint32_t capacity, uint32_t grid, uint32_t* __restrict__ header,
+               uint32_t* __restrict__ first, uint32_t* __restrict__ count, uint32_t* __restrict__ done,
+               uint32_t* __restrict__ sstart, uint32_t* __restrict__ cta_begin, DaItem* __restrict__ items,
+               int* __restrict__ d_status) {
+    __shared__ uint32_t s_carry, s_warp_tot[32], s_quota, s_total;
+    pdl_wait();
+    pdl_trigger();
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     auto len_of = [&](uint32_t b) -> uint32_t {
         uint32_t L = lengths ? lengths[b] : ((d_position ? *d_position : 0u) + extra);
@@ -194,72 +195,84 @@ da_plan_kernel(const uint32_t* __restrict__ lengths, const uint32_t* __restrict_
         }
         return L;
     };
-    auto block_sum = [&](unsigned long long v) -> unsigned long long {
+    // block-wide exclusive scan of f(b) over the sessions, 1024 at a time; returns the total
+    auto scan = [&](auto f, uint32_t* out_excl) -> uint32_t {
+        if (tid == 0) s_carry = 0;
+        __syncthreads();
+        for (uint32_t base = 0; base < batch; base += blockDim.x) {
+            const uint32_t b = base + tid;
+            const uint32_t v = b < batch ? f(b) : 0;
+            uint32_t incl = v;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        __syncthreads();
-        if (lane == 0) red[warp] = v;
-        __syncthreads();
-        unsigned long long t = 0;
-        for (uint32_t w = 0; w < (blockDim.x >> 5); ++w) t += red[w];
-        return t;
+            for (int o = 1; o < 32; o <<= 1) {
+                uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= (uint32_t)o) incl += t;
+            }
+            if (lane == 31) s_warp_tot[warp] = incl;
+            __syncthreads();
+            uint32_t before = s_carry;
+            for (uint32_t w = 0; w < warp; ++w) before += s_warp_tot[w];
+            if (b < batch) out_excl[b] = before + incl - v;
+            __syncthreads();
+            if (tid == blockDim.x - 1) s_carry = before + incl;
+            __syncthreads();
+        }
+        return s_carry;
     };
-    unsigned long long mine = 0;
-    for (uint32_t b = tid; b < batch; b += blockDim.x) mine += len_of(b);
-    const unsigned long long total = block_sum(mine);
-    // largest slab (a power of two from 256 down to DA_MIN_SLAB) that still yields target_items
-    uint32_t slab = 256;
-    while (slab > DA_MIN_SLAB && total / slab < target_items) slab >>= 1;
-    // ... but never more items than the workspace holds
-    for (;;) {
-        unsigned long long n = 0;
-        for (uint32_t b = tid; b < batch; b += blockDim.x) n += (len_of(b) + slab - 1) / slab;
-        n = block_sum(n);
-        if (n <= max_items || slab >= (1u << 30)) break;
-        slab <<= 1;
-    }
-    if (tid == 0) { s_slab = slab; s_carry = 0; }
-    __syncthreads();
-    slab = s_slab;
     // the merge counters must be zero when the attention kernel starts
     for (uint32_t i = tid; i < batch * heads; i += blockDim.x) done[i] = 0;
-    // exclusive prefix sum of the per-session item counts, one block-wide scan per 1024 sessions
-    for (uint32_t base = 0; base < batch; base += blockDim.x) {
-        const uint32_t b = base + tid;
-        const uint32_t c = b < batch ? (len_of(b) + slab - 1) / slab : 0;
-        uint32_t incl = c;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= (uint32_t)o) incl += v;
-        }
-        if (lane == 31) s_warp_tot[warp] = incl;
-        __syncthreads();
-        uint32_t before = s_carry;
-        for (uint32_t w = 0; w < warp; ++w) before += s_warp_tot[w];
-        if (b < batch) {
-            first[b] = before + incl - c;
-            count[b] = c;
-        }
-        __syncthreads();
-        if (tid == blockDim.x - 1) s_carry = before + incl;
-        __syncthreads();
-    }
+    // 1. global stage offsets of the sessions
+    const uint32_t total = scan([&](uint32_t b) { return (len_of(b) + DA_KS - 1) / DA_KS; }, sstart);
     if (tid == 0) {
-        header[0] = s_carry;
-        header[1] = slab;
+        sstart[batch] = total;
+        const uint32_t ctas = total < grid ? (total ? total : 1) : grid;
+        s_quota = (total + ctas - 1) / ctas;
+        if (s_quota == 0) s_quota = 1;
+        s_total = total;
     }
     __syncthreads();
+    const uint32_t quota = s_quota;
+    // 2. pieces per session = CTAs its stage range touches; slots by exclusive scan
+    auto pieces = [&](uint32_t b) -> uint32_t {
+        const uint32_t s0 = sstart[b], n = (len_of(b) + DA_KS - 1) / DA_KS;
+        return n ? (s0 + n - 1) / quota - s0 / quota + 1 : 0;
+    };
+    const uint32_t n_items = scan(pieces, first);
+    // 3. items, one thread per session
     for (uint32_t b = tid; b < batch; b += blockDim.x) {
-        const uint32_t L = len_of(b), f = first[b], c = count[b];
-        for (uint32_t i = 0; i < c; ++i) {
+        const uint32_t L = len_of(b), s0 = sstart[b], n = (L + DA_KS - 1) / DA_KS;
+        const uint32_t c = pieces(b), f = first[b];
+        count[b] = c;
+        const uint32_t cta0 = s0 / quota;
+        for (uint32_t j = 0; j < c; ++j) {
+            const uint32_t lo = max(s0, (cta0 + j) * quota), hi = min(s0 + n, (cta0 + j + 1) * quota);
             DaItem it;
             it.session = b;
-            it.key0 = i * slab;
-            it.nkeys = min(slab, L - i * slab);
-            it.pad = 0;
-            items[f + i] = it;
+            it.key0 = (lo - s0) * DA_KS;
+            it.nkeys = min(L, (hi - s0) * DA_KS) - it.key0;
+            it.slot = c == 1 ? DA_DIRECT : f + j;
+            items[f + j] = it;
         }
+    }
+    __syncthreads();
+    // 4. first item of every CTA: the piece that contains global stage c * quota
+    for (uint32_t c = tid; c <= grid; c += blockDim.x) {
+        const uint32_t g = c * quota;
+        uint32_t begin = n_items;
+        if (g < s_total) {
+            uint32_t lo = 0, hi = batch;  // last session with sstart <= g and at least one stage
+            while (hi - lo > 1) {
+                const uint32_t mid = (lo + hi) / 2;
+                if (sstart[mid] <= g) lo = mid; else hi = mid;
+            }
+            begin = first[lo] + (g / quota - sstart[lo] / quota);
+        }
+        cta_begin[c] = begin;
+    }
+    if (tid == 0) {
+        header[0] = s_total;
+        header[1] = quota;
+        header[2] = n_items;
     }
 }
 
@@ -312,7 +325,7 @@ __device__ __forceinline__ void da_bulk_load(void* dst, const void* src, uint32_
 }
 
 struct DaStageMeta {
-    uint32_t item;    // index into items / partial
+    uint32_t slot;    // partial slot of the item, or DA_DIRECT
     uint32_t nk;      // valid keys in this stage (1..DA_KS)
     uint32_t flags;   // bit 0: first stage of the item, bit 1: last stage
     uint32_t session;
@@ -322,10 +335,10 @@ struct DaParams {
     const bf16* q;
     const bf16* kc;
     const bf16* vc;
-    const uint32_t* header;
     const uint32_t* first;
     const uint32_t* count;
     uint32_t* done;
+    const uint32_t* cta_begin;
     const DaItem* items;
     float* partial;
     bf16* out;
@@ -360,15 +373,17 @@ decode_attention_kernel(DaParams P) {
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    pdl_wait();
+    pdl_trigger();
     __syncthreads();
-    const uint32_t n_items = P.header[0];
+    const uint32_t item_begin = P.cta_begin[blockIdx.x], item_end = P.cta_begin[blockIdx.x + 1];
 
     if (warp == consumers) {
         // ---------------- producer ----------------
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (uint32_t item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+            for (uint32_t item = item_begin; ok && item < item_end; ++item) {
                 const DaItem it = P.items[item];
                 const size_t base = ((size_t)it.session * P.capacity + it.key0) * d;
                 const uint32_t n_stages = (it.nkeys + DA_KS - 1) / DA_KS;
@@ -377,7 +392,7 @@ decode_attention_kernel(DaParams P) {
                     const uint32_t nk = min(DA_KS, it.nkeys - s * DA_KS);
                     uint8_t* sk = ring + (size_t)stage * stage_bytes;
                     DaStageMeta mt;
-                    mt.item = item;
+                    mt.slot = it.slot;
                     mt.nk = nk;
                     mt.flags = (s == 0 ? 1u : 0u) | (s + 1 == n_stages ? 2u : 0u);
                     mt.session = it.session;
@@ -398,7 +413,7 @@ decode_attention_kernel(DaParams P) {
         float qf[HPW][8], acc[HPW][8], m[HPW], l[HPW];
         uint32_t stage = 0, phase = 0;
         bool ok = true;
-        for (uint32_t item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+        for (uint32_t item = item_begin; ok && item < item_end; ++item) {
             for (;;) {
                 if (!da_mbar_wait(full_bar + stage, phase, abort_flag)) { ok = false; break; }
                 const DaStageMeta mt = meta[stage];
@@ -474,86 +489,83 @@ decode_attention_kernel(DaParams P) {
                     }
                     l[hh] = lsum;
                 }
-                const bool last = (mt.flags & 2u) != 0;
-                if (last) {
-                    // fold the KPW side-by-side key groups together and store the partial
-#pragma unroll
-                    for (int hh = 0; hh < HPW; ++hh) {
-                        const uint32_t h = warp + hh * consumers;
-                        if (h >= P.heads) continue;
-                        float mm = m[hh];
-#pragma unroll
-                        for (uint32_t o = LPK; o < 32; o <<= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
-                        const float m_safe = (mm == -INFINITY) ? 0.0f : mm;
-                        const float f = ex2(m[hh] - m_safe);
-                        float ll = l[hh] * f;
-                        float a[8];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) a[e] = acc[hh][e] * f;
-#pragma unroll
-                        for (uint32_t o = LPK; o < 32; o <<= 1) {
-                            ll += __shfl_xor_sync(0xffffffffu, ll, o);
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) a[e] += __shfl_xor_sync(0xffffffffu, a[e], o);
-                        }
-                        const uint32_t n_parts = P.count[mt.session];
-                        if (n_parts == 1) {
-                            // the only slab of this session: normalise and write the output row directly
-                            if (grp == 0) {
-                                const float inv = 1.0f / ll;
-                                bf16* o = P.out + (size_t)mt.session * d + (size_t)h * HD + sub * 8;
-                                *reinterpret_cast<uint4*>(o) = make_uint4(pack_bf16x2(a[0] * inv, a[1] * inv), pack_bf16x2(a[2] * inv, a[3] * inv),
-                                                                          pack_bf16x2(a[4] * inv, a[5] * inv), pack_bf16x2(a[6] * inv, a[7] * inv));
-                            }
-                            continue;
-                        }
-                        if (grp == 0) {
-                            float* dst = P.partial + ((size_t)mt.item * P.heads + h) * (HD + 2);
-                            // (HD + 2) floats per head keeps 8-byte alignment only: store as float2
-#pragma unroll
-                            for (int e = 0; e < 4; ++e)
-                                *reinterpret_cast<float2*>(dst + sub * 8 + 2 * e) = make_float2(a[2 * e], a[2 * e + 1]);
-                            if (sub == 0) *reinterpret_cast<float2*>(dst + HD) = make_float2(mm, ll);
-                            __threadfence();
-                        }
-                        __syncwarp();
-                        // whoever stores the last partial of (session, head) merges them
-                        uint32_t seen = 0;
-                        if (lane == 0) {
-                            __threadfence();
-                            seen = atomicAdd(P.done + (size_t)mt.session * P.heads + h, 1u);
-                        }
-                        seen = __shfl_sync(0xffffffffu, seen, 0);
-                        if (seen + 1 == n_parts) {
-                            __threadfence();
-                            constexpr int DPL = HD / 32;  // output dims per lane
-                            const float* base = P.partial + ((size_t)P.first[mt.session] * P.heads + h) * (HD + 2);
-                            const size_t step = (size_t)P.heads * (HD + 2);
-                            float mx = -INFINITY;
-                            for (uint32_t i = 0; i < n_parts; ++i) mx = fmaxf(mx, __ldcg(base + i * step + HD));
-                            const float ms = (mx == -INFINITY) ? 0.0f : mx;
-                            float lt = 0.0f, o[DPL];
-#pragma unroll
-                            for (int e = 0; e < DPL; ++e) o[e] = 0.0f;
-                            for (uint32_t i = 0; i < n_parts; ++i) {
-                                const float* pp = base + i * step;
-                                const float w = ex2(__ldcg(pp + HD) - ms);
-                                lt = fmaf(__ldcg(pp + HD + 1), w, lt);
-#pragma unroll
-                                for (int e = 0; e < DPL; ++e) o[e] = fmaf(__ldcg(pp + lane * DPL + e), w, o[e]);
-                            }
-                            const float inv = 1.0f / lt;
-                            bf16* orow = P.out + (size_t)mt.session * d + (size_t)h * HD + lane * DPL;
-#pragma unroll
-                            for (int e = 0; e < DPL; ++e) orow[e] = __float2bfloat16_rn(o[e] * inv);
-                            if (lane == 0) P.done[(size_t)mt.session * P.heads + h] = 0;
-                        }
-                    }
-                }
+                // the stage's shared memory is no longer needed: hand it back before any finishing work
                 __syncwarp();
                 if (lane == 0) da_mbar_arrive(empty_bar + stage);
                 if (++stage == P.stages) { stage = 0; phase ^= 1; }
-                if (last) break;
+                const bool last = (mt.flags & 2u) != 0;
+                if (!last) continue;
+                // ---- end of the item: fold the KPW side-by-side key groups, then store or merge ----
+#pragma unroll
+                for (int hh = 0; hh < HPW; ++hh) {
+                    const uint32_t h = warp + hh * consumers;
+                    if (h >= P.heads) continue;
+                    float mm = m[hh];
+#pragma unroll
+                    for (uint32_t o = LPK; o < 32; o <<= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+                    const float m_safe = (mm == -INFINITY) ? 0.0f : mm;
+                    const float f = ex2(m[hh] - m_safe);
+                    float ll = l[hh] * f;
+                    float a[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) a[e] = acc[hh][e] * f;
+#pragma unroll
+                    for (uint32_t o = LPK; o < 32; o <<= 1) {
+                        ll += __shfl_xor_sync(0xffffffffu, ll, o);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) a[e] += __shfl_xor_sync(0xffffffffu, a[e], o);
+                    }
+                    if (mt.slot == DA_DIRECT) {
+                        // the item is the whole session: normalise and write the output row
+                        if (grp == 0) {
+                            const float inv = 1.0f / ll;
+                            bf16* o = P.out + (size_t)mt.session * d + (size_t)h * HD + sub * 8;
+                            *reinterpret_cast<uint4*>(o) = make_uint4(pack_bf16x2(a[0] * inv, a[1] * inv), pack_bf16x2(a[2] * inv, a[3] * inv),
+                                                                      pack_bf16x2(a[4] * inv, a[5] * inv), pack_bf16x2(a[6] * inv, a[7] * inv));
+                        }
+                        continue;
+                    }
+                    if (grp == 0) {
+                        float* dst = P.partial + ((size_t)mt.slot * P.heads + h) * (HD + 2);
+                        // (HD + 2) floats per head keeps 8-byte alignment only: store as float2
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            *reinterpret_cast<float2*>(dst + sub * 8 + 2 * e) = make_float2(a[2 * e], a[2 * e + 1]);
+                        if (sub == 0) *reinterpret_cast<float2*>(dst + HD) = make_float2(mm, ll);
+                        __threadfence();
+                    }
+                    __syncwarp();
+                    // whoever stores the last partial of (session, head) merges them
+                    const uint32_t n_parts = P.count[mt.session];
+                    uint32_t seen = 0;
+                    if (lane == 0) seen = atomicAdd(P.done + (size_t)mt.session * P.heads + h, 1u);
+                    seen = __shfl_sync(0xffffffffu, seen, 0);
+                    if (seen + 1 == n_parts) {
+                        __threadfence();
+                        constexpr int DPL = HD / 32;  // output dims per lane
+                        const float* base = P.partial + ((size_t)P.first[mt.session] * P.heads + h) * (HD + 2);
+                        const size_t step = (size_t)P.heads * (HD + 2);
+                        float mx = -INFINITY;
+                        for (uint32_t i = 0; i < n_parts; ++i) mx = fmaxf(mx, __ldcg(base + i * step + HD));
+                        const float ms = (mx == -INFINITY) ? 0.0f : mx;
+                        float lt = 0.0f, o[DPL];
+#pragma unroll
+                        for (int e = 0; e < DPL; ++e) o[e] = 0.0f;
+                        for (uint32_t i = 0; i < n_parts; ++i) {
+                            const float* pp = base + i * step;
+                            const float w = ex2(__ldcg(pp + HD) - ms);
+                            lt = fmaf(__ldcg(pp + HD + 1), w, lt);
+#pragma unroll
+                            for (int e = 0; e < DPL; ++e) o[e] = fmaf(__ldcg(pp + lane * DPL + e), w, o[e]);
+                        }
+                        const float inv = 1.0f / lt;
+                        bf16* orow = P.out + (size_t)mt.session * d + (size_t)h * HD + lane * DPL;
+#pragma unroll
+                        for (int e = 0; e < DPL; ++e) orow[e] = __float2bfloat16_rn(o[e] * inv);
+                        if (lane == 0) P.done[(size_t)mt.session * P.heads + h] = 0;
+                    }
+                }
+                break;
             }
         }
         // sessions without any live key own no item: their output row is zero
@@ -597,7 +609,7 @@ static int launch_da_t(const DaParams& P, uint32_t threads, size_t smem, uint32_
         timer->used += 2;
         cudaEventRecord(start, stream);
     }
-    decode_attention_kernel<HD, HPW><<<grid, threads, smem, stream>>>(P);
+    launch_kernel(decode_attention_kernel<HD, HPW>, dim3(grid), dim3(threads), smem, stream, P);
     if (timer) cudaEventRecord(stop, stream);
     count_launch();
     return check_launch("decode_attention");
@@ -614,7 +626,7 @@ static int da_sm_count() {
     return n;
 }
 
-// lengths may be nullptr: then every session holds *d_position + extra keys.
+// lengths may be nullptr: then every session holds (d_position ? *d_position : 0) + extra keys.
 int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v_cache, const uint32_t* d_lengths,
                                const uint32_t* d_position, uint32_t extra, bf16* out, void* workspace,
                                uint64_t workspace_bytes, uint32_t batch, uint32_t capacity, uint32_t heads,
@@ -629,8 +641,8 @@ int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v
         set_thread_error("decode attention: pointers must be 16-byte aligned");
         return TNSR_B200_ERR_INVALID_ARGUMENT;
     }
-    const DaLayout L = da_layout(batch, capacity, heads, head_dim, workspace_bytes);
-    if (L.max_items < batch || L.bytes > workspace_bytes) {
+    const DaLayout L = da_layout(batch, heads, head_dim);
+    if (L.bytes > workspace_bytes) {
         set_thread_error("decode attention: workspace too small");
         return TNSR_B200_ERR_INVALID_ARGUMENT;
     }
@@ -639,12 +651,15 @@ int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v
     uint32_t* first = reinterpret_cast<uint32_t*>(ws + L.first);
     uint32_t* count = reinterpret_cast<uint32_t*>(ws + L.count);
     uint32_t* done = reinterpret_cast<uint32_t*>(ws + L.done);
+    uint32_t* sstart = reinterpret_cast<uint32_t*>(ws + L.sstart);
+    uint32_t* cta_begin = reinterpret_cast<uint32_t*>(ws + L.cta_begin);
     DaItem* items = reinterpret_cast<DaItem*>(ws + L.items);
     float* partial = reinterpret_cast<float*>(ws + L.partial);
-    const uint32_t grid = (uint32_t)da_sm_count();
+    uint32_t grid = (uint32_t)da_sm_count();
+    if (grid > DA_MAX_CTAS) grid = DA_MAX_CTAS;
     if (plan) {
-        da_plan_kernel<<<1, 1024, 0, stream>>>(d_lengths, d_position, extra, batch, heads, capacity, 8 * grid, L.max_items,
-                                               header, first, count, done, items, d_status);
+        launch_kernel(da_plan_kernel, dim3(1), dim3(1024), 0, stream, d_lengths, d_position, extra, batch, heads, capacity, grid,
+                      header, first, count, done, sstart, cta_begin, items, d_status);
         count_launch();
         int rc = check_launch("decode_attention plan");
         if (rc) return rc;
@@ -658,23 +673,20 @@ int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v
     const uint32_t consumers = ceil_div(heads, hpw);
     DaParams P;
     P.q = q; P.kc = k_cache; P.vc = v_cache;
-    P.header = header; P.first = first; P.count = count; P.done = done; P.items = items; P.partial = partial;
+    P.first = first; P.count = count; P.done = done; P.cta_begin = cta_begin; P.items = items; P.partial = partial;
     P.out = out;
     P.batch = batch; P.capacity = capacity; P.heads = heads; P.stages = stages;
     P.scale_log2 = (1.0f / sqrtf((float)head_dim)) * 1.4426950408889634f;
     P.d_status = d_status;
     const uint32_t threads = (consumers + 1) * 32;
-    int rc;
     if (hpw == 1) {
-        rc = head_dim == 32 ? launch_da_t<32, 1>(P, threads, smem, grid, stream)
-           : head_dim == 64 ? launch_da_t<64, 1>(P, threads, smem, grid, stream)
-                            : launch_da_t<128, 1>(P, threads, smem, grid, stream);
-    } else {
-        rc = head_dim == 32 ? launch_da_t<32, 2>(P, threads, smem, grid, stream)
-           : head_dim == 64 ? launch_da_t<64, 2>(P, threads, smem, grid, stream)
-                            : launch_da_t<128, 2>(P, threads, smem, grid, stream);
+        return head_dim == 32 ? launch_da_t<32, 1>(P, threads, smem, grid, stream)
+             : head_dim == 64 ? launch_da_t<64, 1>(P, threads, smem, grid, stream)
+                              : launch_da_t<128, 1>(P, threads, smem, grid, stream);
     }
-    return rc;
+    return head_dim == 32 ? launch_da_t<32, 2>(P, threads, smem, grid, stream)
+         : head_dim == 64 ? launch_da_t<64, 2>(P, threads, smem, grid, stream)
+                          : launch_da_t<128, 2>(P, threads, smem, grid, stream);
 }
 
 int launch_decode_attention(const bf16* q, const bf16* k_cache, const bf16* v_cache, const uint32_t* d_lengths,

@@ -45,6 +45,27 @@ struct KernelTimer {
 };
 extern thread_local KernelTimer* t_attention_timer;
 
+// Programmatic dependent launch: while t_pdl is set (the session sets it around single-token steps) kernels are
+// launched with programmatic stream serialization, i.e. a kernel may be scheduled while its predecessor in the
+// stream is still draining.  Every kernel launched this way starts with pdl_wait(), which blocks until the
+// predecessor has completed and its writes are visible, so only launch latency overlaps, never data.
+extern thread_local bool t_pdl;
+
+template <typename... KArgs, typename... Args>
+inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = t_pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline uint32_t ceil_div(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
 inline uint64_t ceil_div64(uint64_t a, uint64_t b) { return (a + b - 1) / b; }
 
@@ -178,6 +199,11 @@ __device__ __forceinline__ int total_order_key(float x) {
     int bits = __float_as_int(x);
     return bits ^ (int)(((unsigned)(bits >> 31)) >> 1);
 }
+// First statement of every kernel that may be launched with programmatic stream serialization.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel in the stream be scheduled (it still waits for this one's completion in its own pdl_wait).
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t hi16) { return __uint_as_float(hi16 << 16); }
 // Two packed bf16 (low half = element 0) -> two f32.
 __device__ __forceinline__ float2 bf16x2_to_f32(uint32_t v) {

@@ -21,7 +21,7 @@
 //    device current) and that address is what the kernels receive.  The first
 //    call on a device performs this look-up; make that first call before any
 //    stream capture begins.
-//  * Shapes whose smallest possible workspace exceeds the array are rejected with
+//  * Shapes whose workspace (tnsr_b200_decode_attention_workspace) exceeds the array are rejected with
 //    TNSR_B200_ERR_UNSUPPORTED and a message that states both sizes.
 //  * Every call reuses the same bytes and finds the previous call's contents in
 //    them.  The words that must start at zero (item count, slab size, the
@@ -72,12 +72,6 @@ int scratch_for_current_device(void** out) {
     return TNSR_B200_OK;
 }
 
-// Smallest workspace the kernels can run in: one work item per session.
-uint64_t minimum_scratch(uint32_t batch, uint32_t heads, uint32_t head_dim) {
-    const uint64_t per_item = 16 + (uint64_t)heads * (head_dim + 2) * 4;
-    return 2048 + 8ull * batch + per_item * batch;
-}
-
 }  // namespace
 
 extern "C" int tnsr_b200_decode_attention_static(const void* q, const void* k_cache, const void* v_cache,
@@ -91,9 +85,9 @@ extern "C" int tnsr_b200_decode_attention_static(const void* q, const void* k_ca
         set_thread_error("decode_attention_static: head_dim must be 32, 64 or 128 and heads <= 32");
         return TNSR_B200_ERR_UNSUPPORTED;
     }
-    const uint64_t need = minimum_scratch(batch, heads, head_dim);
+    const uint64_t need = decode_attention_workspace_bytes(batch, capacity, heads, head_dim);
     if (need > kStaticScratchBytes) {
-        set_thread_error("decode_attention_static: this batch needs at least " + std::to_string(need) +
+        set_thread_error("decode_attention_static: this batch needs " + std::to_string(need) +
                          " bytes of scratch but the built-in array holds " + std::to_string(kStaticScratchBytes) +
                          "; use tnsr_b200_decode_attention with a caller-provided workspace");
         return TNSR_B200_ERR_UNSUPPORTED;

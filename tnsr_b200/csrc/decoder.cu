@@ -110,6 +110,7 @@ struct tnsr_b200_decoder {
     };
     std::vector<StepGraph> graphs;
     bool use_graphs = true;
+    bool use_pdl = true;
     bool stepped_once = false;  // a plain (uncaptured) single-token step has run: buffers and attributes are set
 };
 
@@ -444,10 +445,11 @@ int run_step_direct(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t c
     const uint32_t logit_rows = c.logits_mode == TNSR_B200_LOGITS_ALL ? rows : c.batch;
     const bool fuse_ids = dec->bf16_path && c.logits_mode == TNSR_B200_LOGITS_NONE && d_argmax_out && dec->lm_candidates;
     t_attention_timer = dec->profile_attention ? &dec->attention_timer : nullptr;
+    t_pdl = dec->use_pdl && dec->bf16_path && chunk == 1;
     int rc = dec->bf16_path ? step_bf16(dec, d_tokens, chunk, position, d_position, logit_rows, fuse_ids ? d_argmax_out : nullptr)
                             : step_strict(dec, d_tokens, chunk, position, logit_rows);
     t_attention_timer = nullptr;
-    if (rc) return rc;
+    if (rc) { t_pdl = false; return rc; }
     if (d_argmax_out && !fuse_ids) {
         // last position of every session
         const float* base = dec->logits;
@@ -456,8 +458,14 @@ int run_step_direct(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t c
             base = dec->logits + (size_t)(chunk - 1) * c.vocab_size;
             stride = chunk * c.vocab_size;
         }
-        RUN(dec, launch_argmax(base, d_argmax_out, c.batch, c.vocab_size, stride, dec->stream));
+        int arc = launch_argmax(base, d_argmax_out, c.batch, c.vocab_size, stride, dec->stream);
+        if (arc) {
+            t_pdl = false;
+            dec->error = thread_error();
+            return arc;
+        }
     }
+    t_pdl = false;
     return TNSR_B200_OK;
 }
 
@@ -615,6 +623,8 @@ int tnsr_b200_decoder_create(const tnsr_b200_config* config, tnsr_b200_decoder**
     {
         const char* v = std::getenv("TNSR_B200_NO_GRAPH");
         if (v && v[0] == '1') dec->use_graphs = false;
+        v = std::getenv("TNSR_B200_NO_PDL");
+        if (v && v[0] == '1') dec->use_pdl = false;
     }
     if (cudaMallocHost((void**)&dec->h_argmax, (size_t)config->batch * 4) != cudaSuccess ||
         cudaMallocHost((void**)&dec->h_status, 16) != cudaSuccess)

@@ -37,6 +37,8 @@ embedding_kernel(const T* __restrict__ tok, const T* __restrict__ pos, const uin
                  float* __restrict__ out, uint32_t chunk, uint32_t position0,
                  const uint32_t* __restrict__ d_position, uint32_t vocab, uint32_t width,
                  int* __restrict__ d_status) {
+    pdl_wait();
+    pdl_trigger();
     const uint32_t r = blockIdx.x;
     const uint32_t position = (d_position ? *d_position : position0) + r % chunk;
     uint32_t id = ids[r];
@@ -66,11 +68,11 @@ int launch_embedding(const void* tok, const void* pos, const uint32_t* ids, floa
     if (rows == 0) return TNSR_B200_OK;
     if (chunk == 0) return TNSR_B200_ERR_INVALID_ARGUMENT;
     if (dtype == TNSR_B200_BF16)
-        embedding_kernel<bf16><<<rows, 128, 0, stream>>>((const bf16*)tok, (const bf16*)pos, ids, out, chunk,
-                                                         position0, d_position, vocab, width, d_status);
+        launch_kernel(embedding_kernel<bf16>, dim3(rows), dim3(128), 0, stream, (const bf16*)tok, (const bf16*)pos, ids, out,
+                      chunk, position0, d_position, vocab, width, d_status);
     else
-        embedding_kernel<float><<<rows, 128, 0, stream>>>((const float*)tok, (const float*)pos, ids, out, chunk,
-                                                          position0, d_position, vocab, width, d_status);
+        launch_kernel(embedding_kernel<float>, dim3(rows), dim3(128), 0, stream, (const float*)tok, (const float*)pos, ids, out,
+                      chunk, position0, d_position, vocab, width, d_status);
     count_launch();
     return check_launch("embedding");
 }
@@ -93,6 +95,8 @@ template <bool OUT_BF16>
 __global__ void __launch_bounds__(128)
 layernorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
                       void* __restrict__ out, uint32_t rows, uint32_t width, float eps) {
+    pdl_wait();
+    pdl_trigger();
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -145,6 +149,8 @@ layernorm_block_kernel(const float* __restrict__ x, const float* __restrict__ w,
                        void* __restrict__ out, uint32_t width, float eps) {
     __shared__ float red[8];
     __shared__ float bc;
+    pdl_wait();
+    pdl_trigger();
     const float* xr = x + (size_t)blockIdx.x * width;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float sum = 0.0f;
@@ -198,14 +204,14 @@ int launch_layernorm(const float* x, const float* w, const float* b, void* out, 
     if (vec_ok) {
         dim3 grid(ceil_div(rows, 4));
         if (out_dtype == TNSR_B200_BF16)
-            layernorm_warp_kernel<true><<<grid, 128, 0, stream>>>(x, w, b, out, rows, width, eps);
+            launch_kernel(layernorm_warp_kernel<true>, grid, dim3(128), 0, stream, x, w, b, out, rows, width, eps);
         else
-            layernorm_warp_kernel<false><<<grid, 128, 0, stream>>>(x, w, b, out, rows, width, eps);
+            launch_kernel(layernorm_warp_kernel<false>, grid, dim3(128), 0, stream, x, w, b, out, rows, width, eps);
     } else {
         if (out_dtype == TNSR_B200_BF16)
-            layernorm_block_kernel<true><<<rows, 256, 0, stream>>>(x, w, b, out, width, eps);
+            launch_kernel(layernorm_block_kernel<true>, dim3(rows), dim3(256), 0, stream, x, w, b, out, width, eps);
         else
-            layernorm_block_kernel<false><<<rows, 256, 0, stream>>>(x, w, b, out, width, eps);
+            launch_kernel(layernorm_block_kernel<false>, dim3(rows), dim3(256), 0, stream, x, w, b, out, width, eps);
     }
     count_launch();
     return check_launch("layernorm");
@@ -214,6 +220,8 @@ int launch_layernorm(const float* x, const float* w, const float* b, void* out, 
 // ---------------------------------------------------------------------------
 __global__ void gather_last_rows_kernel(const float* __restrict__ x, float* __restrict__ out, uint32_t chunk,
                                         uint32_t width) {
+    pdl_wait();
+    pdl_trigger();
     const float* src = x + ((size_t)blockIdx.x * chunk + chunk - 1) * width;
     float* dst = out + (size_t)blockIdx.x * width;
     for (uint32_t c = threadIdx.x; c < width; c += blockDim.x) dst[c] = src[c];
@@ -222,7 +230,7 @@ __global__ void gather_last_rows_kernel(const float* __restrict__ x, float* __re
 int launch_gather_last_rows(const float* x, float* out, uint32_t sessions, uint32_t chunk, uint32_t width,
                             cudaStream_t stream) {
     if (sessions == 0) return TNSR_B200_OK;
-    gather_last_rows_kernel<<<sessions, 128, 0, stream>>>(x, out, chunk, width);
+    launch_kernel(gather_last_rows_kernel, dim3(sessions), dim3(128), 0, stream, x, out, chunk, width);
     count_launch();
     return check_launch("gather_last_rows");
 }
@@ -236,6 +244,8 @@ __global__ void __launch_bounds__(1024)
 argmax_kernel(const float* __restrict__ logits, uint32_t* __restrict__ out, uint32_t vocab, uint32_t row_stride) {
     __shared__ int keys[32];
     __shared__ uint32_t idxs[32];
+    pdl_wait();
+    pdl_trigger();
     const float* row = logits + (size_t)blockIdx.x * row_stride;
     int best = INT_MIN;
     uint32_t best_i = 0;
@@ -271,7 +281,7 @@ argmax_kernel(const float* __restrict__ logits, uint32_t* __restrict__ out, uint
 int launch_argmax(const float* logits, uint32_t* out, uint32_t rows, uint32_t vocab, uint32_t row_stride,
                   cudaStream_t stream) {
     if (rows == 0) return TNSR_B200_OK;
-    argmax_kernel<<<rows, vocab >= 8192 ? 1024 : 256, 0, stream>>>(logits, out, vocab, row_stride);
+    launch_kernel(argmax_kernel, dim3(rows), dim3(vocab >= 8192 ? 1024 : 256), 0, stream, logits, out, vocab, row_stride);
     count_launch();
     return check_launch("argmax");
 }
@@ -282,6 +292,8 @@ int launch_argmax(const float* logits, uint32_t* out, uint32_t rows, uint32_t vo
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 swiglu_kernel(const bf16* __restrict__ gate, const bf16* __restrict__ up, bf16* __restrict__ out, uint64_t elems) {
+    pdl_wait();
+    pdl_trigger();
     const uint64_t nvec = elems >> 3;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (uint64_t)gridDim.x * blockDim.x) {
         uint4 g = reinterpret_cast<const uint4*>(gate)[i], u = reinterpret_cast<const uint4*>(up)[i], y;
@@ -310,7 +322,7 @@ int launch_swiglu(const bf16* gate, const bf16* up, bf16* out, uint64_t elems, c
     }
     uint64_t want = ceil_div64(ceil_div64(elems, 8), 256);
     unsigned grid = (unsigned)(want < 148ull * 16 ? (want ? want : 1) : 148ull * 16);
-    swiglu_kernel<<<grid, 256, 0, stream>>>(gate, up, out, elems);
+    launch_kernel(swiglu_kernel, dim3(grid), dim3(256), 0, stream, gate, up, out, elems);
     count_launch();
     return check_launch("swiglu");
 }
@@ -430,6 +442,8 @@ int launch_pack_gate_up(const bf16* wg, const bf16* wu, const float* bg, const f
 }
 
 __global__ void fill_u32_kernel(uint32_t* p, uint32_t value, uint32_t n) {
+    pdl_wait();
+    pdl_trigger();
     uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) p[i] = value;
 }
@@ -437,7 +451,7 @@ __global__ void add_u32_kernel(uint32_t* p, uint32_t delta) { *p += delta; }
 
 int launch_fill_u32(uint32_t* p, uint32_t value, uint32_t n, cudaStream_t stream) {
     if (n == 0) return TNSR_B200_OK;
-    fill_u32_kernel<<<ceil_div(n, 256), 256, 0, stream>>>(p, value, n);
+    launch_kernel(fill_u32_kernel, dim3(ceil_div(n, 256)), dim3(256), 0, stream, p, value, n);
     count_launch();
     return check_launch("fill_u32");
 }

@@ -86,6 +86,8 @@ gemm_simple_kernel(const bf16* __restrict__ a, uint32_t lda, const bf16* __restr
     __shared__ float as[SK][SB + 4];
     __shared__ float bs[SK][SB + 4];
     __shared__ float cs[SB][SB + 1];
+    pdl_wait();
+    pdl_trigger();
     const uint32_t tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
     const uint32_t m0 = blockIdx.y * SB, n0 = blockIdx.x * SB;
     float acc[4][4] = {};
@@ -163,10 +165,10 @@ static int launch_simple(const bf16* a, uint32_t lda, const bf16* bt, const EpiP
         return TNSR_B200_ERR_UNSUPPORTED;
     }
     switch (mode) {
-        case GEMM_PLAIN: gemm_simple_kernel<GEMM_PLAIN><<<grid, 256, 0, stream>>>(a, lda, bt, P, k); break;
-        case GEMM_QKV: gemm_simple_kernel<GEMM_QKV><<<grid, 256, 0, stream>>>(a, lda, bt, P, k); break;
-        case GEMM_SWIGLU: gemm_simple_kernel<GEMM_SWIGLU><<<grid, 256, 0, stream>>>(a, lda, bt, P, k); break;
-        case GEMM_ARGMAX: gemm_simple_kernel<GEMM_ARGMAX><<<grid, 256, 0, stream>>>(a, lda, bt, P, k); break;
+        case GEMM_PLAIN: launch_kernel(gemm_simple_kernel<GEMM_PLAIN>, grid, dim3(256), 0, stream, a, lda, bt, P, k); break;
+        case GEMM_QKV: launch_kernel(gemm_simple_kernel<GEMM_QKV>, grid, dim3(256), 0, stream, a, lda, bt, P, k); break;
+        case GEMM_SWIGLU: launch_kernel(gemm_simple_kernel<GEMM_SWIGLU>, grid, dim3(256), 0, stream, a, lda, bt, P, k); break;
+        case GEMM_ARGMAX: launch_kernel(gemm_simple_kernel<GEMM_ARGMAX>, grid, dim3(256), 0, stream, a, lda, bt, P, k); break;
     }
     count_launch();
     return check_launch("gemm_simple");
@@ -457,6 +459,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // everything above touches only this CTA's shared memory; from here on the previous kernel must be done
+    pdl_wait();
+    pdl_trigger();
     if (warp == 1) {
         tmem_alloc(tmem_slot, S::TMEM_COLS);
         tmem_relinquish();
@@ -624,7 +629,7 @@ static int launch_tc_t(const CUtensorMap& ma, const CUtensorMap& mb, const TcPar
     }
     uint32_t tiles = prm.tiles_m * prm.tiles_n;
     uint32_t grid = tiles < (uint32_t)sm_count() ? tiles : (uint32_t)sm_count();
-    gemm_tc_kernel<BN, MODE><<<grid, TC_THREADS, S::SMEM_BYTES, stream>>>(ma, mb, prm);
+    launch_kernel(gemm_tc_kernel<BN, MODE>, dim3(grid), dim3(TC_THREADS), S::SMEM_BYTES, stream, ma, mb, prm);
     count_launch();
     return check_launch("gemm_tc");
 }
@@ -682,7 +687,8 @@ static int launch_gemm_impl(const bf16* a, const bf16* bt, void* out, uint32_t l
     // tile width: the widest that still gives every SM a tile (32 at the narrowest)
     const uint32_t tiles_m = ceil_div(m, BM);
     uint32_t bn = 256;
-    while (bn > 32 && (uint64_t)tiles_m * ceil_div(n, bn) < (uint64_t)sm_count()) bn >>= 1;
+    while (bn > 64 && (uint64_t)tiles_m * ceil_div(n, bn) < (uint64_t)sm_count()) bn >>= 1;
+    if (bn == 64 && 2ull * tiles_m * ceil_div(n, 64) <= (uint64_t)sm_count()) bn = 32;  // very few tiles: halve once more
     TcParams prm;
     prm.k = k;
     prm.tiles_m = tiles_m;
@@ -719,6 +725,8 @@ int launch_gemm_bf16(const bf16* a, const bf16* bt, void* out, uint32_t ldc, uin
 // which is the later tile, so the result is the last index of the row maximum.
 __global__ void __launch_bounds__(128)
 argmax_finish_kernel(const uint2* __restrict__ cand, uint32_t* __restrict__ ids, uint32_t rows, uint32_t tiles) {
+    pdl_wait();
+    pdl_trigger();
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t row = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -750,7 +758,7 @@ int launch_lm_head_argmax(const bf16* a, const bf16* bt, uint32_t m, uint32_t n,
     uint32_t tiles = 0;
     int rc = launch_gemm_impl(a, bt, candidates, 0, m, n, k, GEMM_ARGMAX, ep, nullptr, d_status, &tiles, stream);
     if (rc) return rc;
-    argmax_finish_kernel<<<ceil_div(m, 4), 128, 0, stream>>>(reinterpret_cast<const uint2*>(candidates), ids, m, tiles);
+    launch_kernel(argmax_finish_kernel, dim3(ceil_div(m, 4)), dim3(128), 0, stream, reinterpret_cast<const uint2*>(candidates), ids, m, tiles);
     count_launch();
     return check_launch("argmax_finish");
 }
