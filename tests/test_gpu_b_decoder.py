@@ -298,3 +298,16 @@ def test_graph_replay_of_single_token_steps_matches_direct_launches(monkeypatch)
     a, b = run(False), run(True)
     for x, y in zip(a, b):
         assert np.array_equal(x.view(np.uint32), y.view(np.uint32))
+
+
+def test_full_context_forward_and_uncached_generate_on_the_gpu():
+    """Gpt::forward / Gpt::generate (src/nn.rs:629-715) through the library vs the CPU checker."""
+    model = kv_model(9)
+    rows = kv_test_tokens(2, 9)
+    close(model.forward(Backend.Cuda, rows), cpu_forward(model, rows))
+    prompt = [365, 2, 3, 4]
+    assert model.generate(Backend.Cuda, prompt, 8) == cpu_generate(model, prompt, 8)
+    assert model.generate(Backend.Cuda, prompt, 8) == model.generate_cached(Backend.Cuda, prompt, 8)
+    from tnsr_b200.nn import TnsrError
+    with pytest.raises(TnsrError):
+        model.forward(Backend.Cuda, [list(range(10))])

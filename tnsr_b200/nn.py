@@ -209,6 +209,44 @@ class Gpt:
                              options: GptDecoderOptions, **extra) -> "GptDecoder":
         return GptDecoder(self, backend, batch_size, capacity, options, **extra)
 
+    # -- full-context paths (src/nn.rs:629-715) -------------------------------
+    def forward(self, backend, token_ids) -> np.ndarray:
+        """``Gpt::forward`` evaluated on the backend: logits ``[batch, sequence, vocabulary]``
+        of a whole ``[batch, sequence]`` id block (a fresh session decoding one chunk is the same graph:
+        src/nn/kv_cache/graph.rs with past = 0)."""
+        ids = np.asarray(token_ids)
+        if ids.ndim != 2:
+            raise TnsrError("GPT token IDs must have shape [batch, sequence]")
+        batch, sequence = ids.shape
+        if batch == 0:
+            raise TnsrError("GPT batch size must be non-zero")
+        if sequence == 0:
+            raise TnsrError("GPT sequence length must be non-zero")
+        if sequence > self._config.max_sequence_length:
+            raise TnsrError(f"GPT sequence length {sequence} exceeds configured maximum "
+                            f"{self._config.max_sequence_length}")
+        decoder = self.decoder_with_capacity(backend, batch, sequence)
+        logits = decoder.decode([int(t) for t in ids.reshape(-1)])
+        return logits.reshape(batch, sequence, self._config.vocab_size)
+
+    def generate(self, backend, prompt: Sequence[int], max_new_tokens: int) -> List[int]:
+        """``Gpt::generate``: greedy, re-running the whole retained context for every new token."""
+        if len(prompt) == 0:
+            raise TnsrError("GPT generation prompt must be non-empty")
+        if not all(0 <= t < self._config.vocab_size for t in prompt):
+            raise TnsrError("GPT generation prompt contains an out-of-range token")
+        tokens = [int(t) for t in prompt]
+        context = self._config.max_sequence_length
+        decoder = None
+        for _ in range(max_new_tokens):
+            window = tokens[max(0, len(tokens) - context):]
+            if decoder is None:
+                decoder = self.decoder(backend, 1)
+            decoder.reset()
+            logits = decoder.decode(window)
+            tokens.append(argmax_last(logits[logits.size - self._config.vocab_size:]))
+        return tokens
+
     # -- greedy generation (src/nn/kv_cache.rs:121-157) ----------------------
     def generate_cached(self, backend, prompt: Sequence[int], max_new_tokens: int) -> List[int]:
         if len(prompt) == 0:
