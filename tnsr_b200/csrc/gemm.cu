@@ -4,8 +4,9 @@
 //  * gemm_tc_kernel   -- the Blackwell path: TMA (cp.async.bulk.tensor, 128-byte
 //    swizzle, one copy per CTA, no cluster forms) feeds a shared-memory ring,
 //    one thread issues tcgen05.mma (M=128, N=BN, K=16 per instruction) into
-//    double-buffered TMEM accumulators, four epilogue warps drain them with
-//    tcgen05.ld while the next tile's main loop runs.  Persistent over tiles.
+//    double-buffered TMEM accumulators, eight epilogue warps drain them with
+//    tcgen05.ld, transpose each 32x32 block through shared memory and write
+//    coalesced rows while the next tile's main loop runs.  Persistent over tiles.
 //  * gemm_simple_kernel -- CUDA-core kernel for shapes TMA cannot address
 //    (k not a multiple of 8, unaligned pointers) and as the cross-check of the
 //    tensor-core engine.
@@ -180,7 +181,9 @@ static int launch_simple(const bf16* a, uint32_t lda, const bf16* bt, const EpiP
 constexpr int BM = 128;           // rows per tile = TMEM lanes
 constexpr int BK = 64;            // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;        // K per tcgen05.mma for 16-bit operands
-constexpr int TC_THREADS = 192;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr int TC_EPI_WARPS = 8;   // two warps per TMEM lane quarter, each taking every other 32-column chunk
+constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: epilogue
+constexpr uint32_t TC_STAGE_TILE_BYTES = 32 * 32 * 4;  // per-warp transpose buffer: 32 rows x 32 f32 columns
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // a wait that lasts 2 s gives up
 
 template <int BN>
@@ -190,7 +193,8 @@ struct TcShape {
     static constexpr uint32_t B_BYTES = BN * BK * 2;
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators; power of two
-    static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr uint32_t SMEM_BYTES =
+        STAGES * STAGE_BYTES + 1024 /* alignment slack */ + TC_EPI_WARPS * TC_STAGE_TILE_BYTES + 256 /* barriers */;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -324,114 +328,91 @@ __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uin
     tn = in_group / size;
 }
 
-// ---- epilogue on 32 consecutive accumulator columns of one row -----------------
+// ---- epilogue of one 32-row x 32-column accumulator block, one warp ------------------
+// tcgen05.ld hands every lane one ROW of the block (32 columns in registers).  Writing global
+// memory that way would touch 32 different cache lines per store instruction, so the block is
+// first transposed through a 4 KB shared-memory buffer private to the warp: lanes write their
+// row (16-byte stores, XOR-swizzled in units of 4 columns so neither phase has bank conflicts),
+// then lanes become COLUMNS and every global access is one contiguous segment per row.
+__device__ __forceinline__ uint32_t stage_index(uint32_t r, uint32_t c) {
+    return r * 32u + ((((c >> 2) ^ r) & 7u) << 2) + (c & 3u);
+}
+
 template <int MODE>
-__device__ __forceinline__ void epilogue_chunk(const EpiParams& P, uint32_t row, uint32_t col0, const float* acc) {
-    if (row >= P.m || col0 >= P.n) return;
-    const bool full = col0 + 32 <= P.n;
+__device__ __forceinline__ void epilogue_block(const EpiParams& P, float* stage, uint32_t row0, uint32_t col0,
+                                               const float* acc, uint32_t lane) {
+    if (row0 >= P.m || col0 >= P.n) return;  // warp-uniform
+#pragma unroll
+    for (int g = 0; g < 8; ++g)
+        *reinterpret_cast<float4*>(stage + stage_index(lane, 4 * g)) = make_float4(acc[4 * g], acc[4 * g + 1], acc[4 * g + 2], acc[4 * g + 3]);
+    __syncwarp();
+    const uint32_t rows = min(32u, P.m - row0);
     if (MODE == GEMM_SWIGLU) {
-        // 16 gate + 16 up columns -> 16 outputs at column col0 / 2
-        const uint32_t oc0 = col0 / 2;
-        bf16* dst = reinterpret_cast<bf16*>(P.out) + (size_t)row * P.ldc + oc0;
-        if (full && (reinterpret_cast<uintptr_t>(dst) % 16 == 0)) {
-            uint32_t packed[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                float g0 = acc[2 * i], g1 = acc[2 * i + 1], u0 = acc[16 + 2 * i], u1 = acc[17 + 2 * i];
-                if (P.ep.bias) {
-                    g0 += __ldg(P.ep.bias + col0 + 2 * i);
-                    g1 += __ldg(P.ep.bias + col0 + 2 * i + 1);
-                    u0 += __ldg(P.ep.bias + col0 + 16 + 2 * i);
-                    u1 += __ldg(P.ep.bias + col0 + 17 + 2 * i);
-                }
-                packed[i] = pack_bf16x2(fast_silu(g0) * u0, fast_silu(g1) * u1);
-            }
-            reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-        } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-                if (col0 + 16 + i < P.n) store_swiglu(P, row, col0 + i, oc0 + i, acc[i], acc[16 + i]);
+        // columns [0,16) are gate, [16,32) the matching up columns; two rows per step, 16 outputs each
+        const uint32_t oc = lane & 15, half = lane >> 4, ocol = col0 / 2 + oc;
+        const bool col_ok = col0 + 16 + oc < P.n;
+        float bg = 0.0f, bu = 0.0f;
+        if (P.ep.bias && col_ok) { bg = __ldg(P.ep.bias + col0 + oc); bu = __ldg(P.ep.bias + col0 + 16 + oc); }
+        bf16* out = reinterpret_cast<bf16*>(P.out);
+        for (uint32_t rr = half; rr < rows; rr += 2) {
+            const float g = stage[stage_index(rr, oc)] + bg, u = stage[stage_index(rr, 16 + oc)] + bu;
+            if (col_ok) out[(size_t)(row0 + rr) * P.ldc + ocol] = __float2bfloat16_rn(fast_silu(g) * u);
         }
-        return;
-    }
-    if (MODE == GEMM_QKV) {
+    } else if (MODE == GEMM_QKV) {
         const uint32_t d = P.qkv.d;
-        if (full && d % 32 == 0) {
-            const uint32_t which = col0 / d, c = col0 % d;
-            bf16* dst;
-            if (which == 0) {
-                dst = P.qkv.q + (size_t)row * d + c;
-            } else {
-                uint32_t pos = P.qkv.d_position ? *P.qkv.d_position : P.qkv.position;
-                size_t crow = (size_t)(row / P.qkv.chunk) * P.qkv.capacity + pos + row % P.qkv.chunk;
-                dst = (which == 1 ? P.qkv.k_cache : P.qkv.v_cache) + crow * d + c;
-            }
-            if (reinterpret_cast<uintptr_t>(dst) % 16 == 0) {
-                uint32_t packed[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    float a = acc[2 * i], b = acc[2 * i + 1];
-                    if (P.ep.bias) { a += __ldg(P.ep.bias + col0 + 2 * i); b += __ldg(P.ep.bias + col0 + 2 * i + 1); }
-                    packed[i] = pack_bf16x2(a, b);
+        const uint32_t pos = P.qkv.d_position ? *P.qkv.d_position : P.qkv.position;
+        if (d % 32 == 0 && col0 + 32 <= P.n) {
+            // the whole block belongs to one of q / K / V; two rows per step, a pair of columns per lane
+            const uint32_t which = col0 / d, cbase = col0 % d, cp = (lane & 15) * 2, half = lane >> 4;
+            float b0 = 0.0f, b1 = 0.0f;
+            if (P.ep.bias) { b0 = __ldg(P.ep.bias + col0 + cp); b1 = __ldg(P.ep.bias + col0 + cp + 1); }
+            for (uint32_t rr = half; rr < rows; rr += 2) {
+                const uint32_t row = row0 + rr;
+                const float2 v = *reinterpret_cast<const float2*>(stage + stage_index(rr, cp));
+                bf16* dst;
+                if (which == 0) {
+                    dst = P.qkv.q + (size_t)row * d;
+                } else {
+                    const size_t crow = (size_t)(row / P.qkv.chunk) * P.qkv.capacity + pos + row % P.qkv.chunk;
+                    dst = (which == 1 ? P.qkv.k_cache : P.qkv.v_cache) + crow * d;
                 }
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    reinterpret_cast<uint4*>(dst)[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-                return;
+                *reinterpret_cast<uint32_t*>(dst + cbase + cp) = pack_bf16x2(v.x + b0, v.y + b1);
             }
+        } else {
+            for (uint32_t rr = 0; rr < rows; ++rr)
+                if (col0 + lane < P.n) store_qkv(P, row0 + rr, col0 + lane, stage[stage_index(rr, lane)]);
         }
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-            if (col0 + i < P.n) store_qkv(P, row, col0 + i, acc[i]);
-        return;
-    }
-    // GEMM_PLAIN
-    const size_t orow = map_out_row(P.ep, row);
-    if (P.ep.out_dtype == TNSR_B200_BF16) {
-        bf16* dst = reinterpret_cast<bf16*>(P.out) + orow * P.ldc + col0;
-        if (full && (reinterpret_cast<uintptr_t>(dst) % 16 == 0)) {
-            uint32_t packed[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                float a = acc[2 * i], b = acc[2 * i + 1];
-                if (P.ep.bias) { a += __ldg(P.ep.bias + col0 + 2 * i); b += __ldg(P.ep.bias + col0 + 2 * i + 1); }
-                packed[i] = pack_bf16x2(apply_activation(a, P.ep.activation), apply_activation(b, P.ep.activation));
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-                reinterpret_cast<uint4*>(dst)[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-            return;
+    } else if (P.ep.out_dtype == TNSR_B200_BF16 && P.ldc % 2 == 0 && col0 + 32 <= P.n &&
+               (reinterpret_cast<uintptr_t>(P.out) & 3) == 0) {
+        const uint32_t cp = (lane & 15) * 2, half = lane >> 4;
+        float b0 = 0.0f, b1 = 0.0f;
+        if (P.ep.bias) { b0 = __ldg(P.ep.bias + col0 + cp); b1 = __ldg(P.ep.bias + col0 + cp + 1); }
+        bf16* out = reinterpret_cast<bf16*>(P.out);
+        for (uint32_t rr = half; rr < rows; rr += 2) {
+            const float2 v = *reinterpret_cast<const float2*>(stage + stage_index(rr, cp));
+            const size_t orow = map_out_row(P.ep, row0 + rr);
+            *reinterpret_cast<uint32_t*>(out + orow * P.ldc + col0 + cp) =
+                pack_bf16x2(apply_activation(v.x + b0, P.ep.activation), apply_activation(v.y + b1, P.ep.activation));
         }
     } else {
-        float* dst = reinterpret_cast<float*>(P.out) + orow * P.ldc + col0;
-        const float* res = P.ep.residual ? P.ep.residual + (size_t)row * P.ep.ldr + col0 : nullptr;
-        if (full && (reinterpret_cast<uintptr_t>(dst) % 16 == 0) && (!res || reinterpret_cast<uintptr_t>(res) % 16 == 0)) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                float4 v = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
-                if (P.ep.bias) {
-                    v.x += __ldg(P.ep.bias + col0 + 4 * i);
-                    v.y += __ldg(P.ep.bias + col0 + 4 * i + 1);
-                    v.z += __ldg(P.ep.bias + col0 + 4 * i + 2);
-                    v.w += __ldg(P.ep.bias + col0 + 4 * i + 3);
-                }
-                v.x = apply_activation(v.x, P.ep.activation);
-                v.y = apply_activation(v.y, P.ep.activation);
-                v.z = apply_activation(v.z, P.ep.activation);
-                v.w = apply_activation(v.w, P.ep.activation);
-                if (res) {
-                    float4 r = reinterpret_cast<const float4*>(res)[i];
-                    v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
-                }
-                reinterpret_cast<float4*>(dst)[i] = v;
+        // f32 output (optionally + residual), or any ragged / unaligned case: one column per lane
+        const uint32_t col = col0 + lane;
+        const bool col_ok = col < P.n;
+        const float bv = (P.ep.bias && col_ok) ? __ldg(P.ep.bias + col) : 0.0f;
+        for (uint32_t rr = 0; rr < rows; ++rr) {
+            if (!col_ok) continue;
+            const uint32_t row = row0 + rr;
+            float v = apply_activation(stage[stage_index(rr, lane)] + bv, P.ep.activation);
+            const size_t orow = map_out_row(P.ep, row);
+            if (P.ep.out_dtype == TNSR_B200_BF16) {
+                reinterpret_cast<bf16*>(P.out)[orow * P.ldc + col] = __float2bfloat16_rn(v);
+            } else {
+                if (P.ep.residual) v += P.ep.residual[(size_t)row * P.ep.ldr + col];
+                reinterpret_cast<float*>(P.out)[orow * P.ldc + col] = v;
             }
-            return;
         }
     }
-#pragma unroll
-    for (int i = 0; i < 32; ++i)
-        if (col0 + i < P.n) store_plain(P, row, col0 + i, acc[i]);
+    __syncwarp();  // the buffer is reused by the next block
 }
 
 template <int BN, int MODE>
@@ -442,7 +423,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // 128-byte-swizzled tiles want a 1024-byte aligned base
     const uint32_t raw_addr = smem_u32(smem_raw);
     uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::STAGES * S::STAGE_BYTES);
+    float* stage_tiles = reinterpret_cast<float*>(smem + S::STAGES * S::STAGE_BYTES);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::STAGES * S::STAGE_BYTES + TC_EPI_WARPS * TC_STAGE_TILE_BYTES);
     uint64_t* empty_bar = full_bar + S::STAGES;
     uint64_t* acc_full = empty_bar + S::STAGES;   // [2]
     uint64_t* acc_empty = acc_full + 2;           // [2]
@@ -455,7 +437,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S::STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(acc_full + s, 1); mbar_init(acc_empty + s, 4); }
+        for (int s = 0; s < 2; ++s) { mbar_init(acc_full + s, 1); mbar_init(acc_empty + s, TC_EPI_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -518,8 +500,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
     } else {
-        // ---------------- epilogue warps (TMEM lane quarter = warp % 4) ----------------
-        const uint32_t quarter = warp & 3;
+        // ---------------- epilogue warps ----------------
+        // TMEM lane quarter = warp % 4 (a warp may only read its own quarter); the two warps of a quarter
+        // take alternate 32-column chunks.
+        const uint32_t quarter = warp & 3, half = (warp - 2) >> 2;
+        float* stage = stage_tiles + (warp - 2) * (TC_STAGE_TILE_BYTES / 4);
         uint32_t it = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
@@ -528,29 +513,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tile_coords(tile, prm.tiles_m, prm.tiles_n, tm, tn);
             if (!mbar_wait(acc_full + ab, aphase, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t row = tm * BM + quarter * 32 + lane;
+            const uint32_t row0 = tm * BM + quarter * 32;
             const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + ab * BN;
-            int best = 0;
-            uint32_t best_i = 0;
-            bool have = false;
+            if (MODE == GEMM_ARGMAX) {
+                // no matrix leaves the kernel: every lane scans its own row; the first warp of the quarter does all chunks
+                if (half == 0) {
+                    int best = 0;
+                    uint32_t best_i = 0;
+                    bool have = false;
 #pragma unroll 1
-            for (uint32_t c = 0; c < BN; c += 32) {
-                float acc[32];
-                tmem_ld32(taddr + c, acc);
-                tmem_ld_wait();
-                if (MODE == GEMM_ARGMAX) {
-                    const uint32_t col0 = tn * BN + c;
+                    for (uint32_t c = 0; c < BN; c += 32) {
+                        float acc[32];
+                        tmem_ld32(taddr + c, acc);
+                        tmem_ld_wait();
+                        const uint32_t col0 = tn * BN + c;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int key = total_order_key(acc[i]);
-                        if (col0 + i < prm.epi.n && (!have || key >= best)) { best = key; best_i = col0 + i; have = true; }
+                        for (int i = 0; i < 32; ++i) {
+                            const int key = total_order_key(acc[i]);
+                            if (col0 + i < prm.epi.n && (!have || key >= best)) { best = key; best_i = col0 + i; have = true; }
+                        }
                     }
-                } else {
-                    epilogue_chunk<MODE>(prm.epi, row, tn * BN + c, acc);
+                    if (row0 + lane < prm.epi.m)
+                        reinterpret_cast<uint2*>(prm.epi.out)[(size_t)(row0 + lane) * prm.epi.ldc + tn] = make_uint2((uint32_t)best, best_i);
+                }
+            } else {
+#pragma unroll 1
+                for (uint32_t c = half * 32; c < BN; c += 64) {
+                    float acc[32];
+                    tmem_ld32(taddr + c, acc);
+                    tmem_ld_wait();
+                    epilogue_block<MODE>(prm.epi, stage, row0, tn * BN + c, acc, lane);
                 }
             }
-            if (MODE == GEMM_ARGMAX && row < prm.epi.m)
-                reinterpret_cast<uint2*>(prm.epi.out)[(size_t)row * prm.epi.ldc + tn] = make_uint2((uint32_t)best, best_i);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty + ab);

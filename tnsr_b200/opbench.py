@@ -1,8 +1,10 @@
 """Operator-level measurements of the kernels behind the C ABI.
 
     python -m tnsr_b200.opbench gemm        # configuration 1: square sweep + skinny decode shapes
+    python -m tnsr_b200.opbench serving_gemms  # configuration 4's projection shapes at prefill and decode size
     python -m tnsr_b200.opbench mlp         # configuration 2: fused SwiGLU MLP 4096 x 2048 -> 5632 -> 2048
     python -m tnsr_b200.opbench attention   # configuration 3: 64 sessions x 16 heads x 64, ragged lengths <= 4096
+    python -m tnsr_b200.opbench serving_attention  # configuration 4's decode attention: 256 x 12 x 64, 641 live keys
     python -m tnsr_b200.opbench elementwise # LayerNorm, SwiGLU, embedding, greedy pick
     python -m tnsr_b200.opbench all
 
@@ -108,6 +110,46 @@ def bench_gemm(samples):
             del a, b, o
 
 
+def bench_serving_gemms(samples):
+    """The four projection shapes of configuration 4 at prefill (131 072 rows) and decode (256 rows) size."""
+    hbm, tf, kind = peaks()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    for rows in (131072, 256):
+        for name, n, k, out_dtype, resid in (("qkv", 2304, 768, 1, False), ("attn_out", 768, 768, 0, True),
+                                             ("gate_up", 4096, 768, 1, False), ("ffn_down", 768, 2048, 0, True)):
+            a = (torch.randn((rows, k), device="cuda", generator=g)).to(torch.bfloat16)
+            b = (torch.randn((n, k), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+            r = torch.randn((rows, n), device="cuda", generator=g) if resid else None
+            o = torch.empty((rows, n), device="cuda", dtype=torch.bfloat16 if out_dtype else torch.float32)
+            flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if rows <= 1024 else None
+
+            def launch(_):
+                if flush is not None:
+                    flush.zero_()  # small operands would otherwise sit in L2 between launches
+                ok(lib().tnsr_b200_gemm_bf16(ptr(a), ptr(b), None, ptr(r), ptr(o), rows, n, k, -1, out_dtype, stream()))
+
+            if flush is None:
+                ms, _ = timed(launch, 1, samples)
+            else:
+                # time only the GEMM: events around it, the L2 flush outside
+                for _ in range(3):
+                    launch(0)
+                ts = []
+                for _ in range(samples):
+                    flush.zero_()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    ok(lib().tnsr_b200_gemm_bf16(ptr(a), ptr(b), None, ptr(r), ptr(o), rows, n, k, -1, out_dtype, stream()))
+                    e1.record()
+                    e1.synchronize()
+                    ts.append(e0.elapsed_time(e1))
+                ms = float(np.median(ts))
+            flops = 2.0 * rows * n * k
+            emit(op="serving_gemm", which=name, rows=rows, n=n, k=k, out="bf16" if out_dtype else "f32+residual", ms=ms,
+                 tflops=flops / ms / 1e9, frac_tensor=flops / ms / 1e9 / tf, peaks=kind)
+            del a, b, r, o, flush
+
+
 def bench_mlp(samples):
     hbm, tf, kind = peaks()
     rows, d, f = 4096, 2048, 5632
@@ -135,11 +177,17 @@ def bench_mlp(samples):
          peaks=kind)
 
 
-def bench_attention(samples):
+def bench_attention(samples, serving=False):
+    """Configuration 3 (ragged lengths), or with serving=True the decode attention of configuration 4:
+    256 sessions x 12 heads x 64 at 641 live keys (the mean over the 256 benchmark steps)."""
     hbm, _, kind = peaks()
-    batch, heads, hd, capacity = 64, 16, 64, 4096
+    if serving:
+        batch, heads, hd, capacity = 256, 12, 64, 769
+        lengths = np.full(batch, 641, dtype=np.uint32)
+    else:
+        batch, heads, hd, capacity = 64, 16, 64, 4096
+        lengths = np.random.default_rng(4).integers(1, capacity + 1, size=batch).astype(np.uint32)
     d = heads * hd
-    lengths = np.random.default_rng(4).integers(1, capacity + 1, size=batch).astype(np.uint32)
     g = torch.Generator(device="cuda").manual_seed(4)
     q = torch.randn((batch, d), device="cuda", generator=g).to(torch.bfloat16)
     kc = torch.randn((batch, capacity, d), device="cuda", generator=g).to(torch.bfloat16)
@@ -186,14 +234,15 @@ def bench_elementwise(samples):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "mlp", "attention", "elementwise", "all"])
+    ap.add_argument("what", choices=["gemm", "serving_gemms", "mlp", "attention", "serving_attention", "elementwise", "all"])
     ap.add_argument("--samples", type=int, default=20)
     args = ap.parse_args()
     if not torch.cuda.is_available():
         sys.exit("opbench needs a CUDA device")
-    todo = ["gemm", "mlp", "attention", "elementwise"] if args.what == "all" else [args.what]
+    todo = ["gemm", "serving_gemms", "mlp", "attention", "serving_attention", "elementwise"] if args.what == "all" else [args.what]
     for name in todo:
-        {"gemm": bench_gemm, "mlp": bench_mlp, "attention": bench_attention, "elementwise": bench_elementwise}[name](args.samples)
+        {"gemm": bench_gemm, "serving_gemms": bench_serving_gemms, "mlp": bench_mlp, "attention": bench_attention,
+         "serving_attention": lambda n: bench_attention(n, serving=True), "elementwise": bench_elementwise}[name](args.samples)
 
 
 if __name__ == "__main__":
