@@ -399,16 +399,26 @@ __device__ __forceinline__ void epilogue_block(const EpiParams& P, float* stage,
         const uint32_t col = col0 + lane;
         const bool col_ok = col < P.n;
         const float bv = (P.ep.bias && col_ok) ? __ldg(P.ep.bias + col) : 0.0f;
-        for (uint32_t rr = 0; rr < rows; ++rr) {
-            if (!col_ok) continue;
-            const uint32_t row = row0 + rr;
-            float v = apply_activation(stage[stage_index(rr, lane)] + bv, P.ep.activation);
-            const size_t orow = map_out_row(P.ep, row);
-            if (P.ep.out_dtype == TNSR_B200_BF16) {
-                reinterpret_cast<bf16*>(P.out)[orow * P.ldc + col] = __float2bfloat16_rn(v);
-            } else {
-                if (P.ep.residual) v += P.ep.residual[(size_t)row * P.ep.ldr + col];
-                reinterpret_cast<float*>(P.out)[orow * P.ldc + col] = v;
+        if (P.ep.out_dtype == TNSR_B200_F32) {
+            // The residual may be the output buffer itself (the residual stream is updated in place), so the
+            // compiler must not be left to order these loads against the stores: fetch all rows first.
+            float res[32];
+#pragma unroll
+            for (int rr = 0; rr < 32; ++rr)
+                res[rr] = (P.ep.residual && col_ok && (uint32_t)rr < rows) ? P.ep.residual[(size_t)(row0 + rr) * P.ep.ldr + col] : 0.0f;
+            float* out = reinterpret_cast<float*>(P.out);
+#pragma unroll
+            for (int rr = 0; rr < 32; ++rr) {
+                if (col_ok && (uint32_t)rr < rows) {
+                    const float v = apply_activation(stage[stage_index(rr, lane)] + bv, P.ep.activation) + res[rr];
+                    out[map_out_row(P.ep, row0 + rr) * P.ldc + col] = v;
+                }
+            }
+        } else {
+            for (uint32_t rr = 0; rr < rows; ++rr) {
+                if (!col_ok) continue;
+                const float v = apply_activation(stage[stage_index(rr, lane)] + bv, P.ep.activation);
+                reinterpret_cast<bf16*>(P.out)[map_out_row(P.ep, row0 + rr) * P.ldc + col] = __float2bfloat16_rn(v);
             }
         }
     }
