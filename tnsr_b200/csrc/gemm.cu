@@ -338,6 +338,14 @@ __device__ __forceinline__ uint32_t stage_index(uint32_t r, uint32_t c) {
     return r * 32u + ((((c >> 2) ^ r) & 7u) << 2) + (c & 3u);
 }
 
+__device__ __forceinline__ float4 stage_load4(const float* stage, uint32_t r, uint32_t c4) {
+    return *reinterpret_cast<const float4*>(stage + stage_index(r, c4));
+}
+__device__ __forceinline__ float4 act4(float4 v, int act) {
+    if (act == ACT_NONE) return v;
+    return make_float4(apply_activation(v.x, act), apply_activation(v.y, act), apply_activation(v.z, act), apply_activation(v.w, act));
+}
+
 template <int MODE>
 __device__ __forceinline__ void epilogue_block(const EpiParams& P, float* stage, uint32_t row0, uint32_t col0,
                                                const float* acc, uint32_t lane) {
@@ -347,79 +355,122 @@ __device__ __forceinline__ void epilogue_block(const EpiParams& P, float* stage,
         *reinterpret_cast<float4*>(stage + stage_index(lane, 4 * g)) = make_float4(acc[4 * g], acc[4 * g + 1], acc[4 * g + 2], acc[4 * g + 3]);
     __syncwarp();
     const uint32_t rows = min(32u, P.m - row0);
+    // the vector paths need the whole 32-column block inside the matrix and a 16-byte aligned bias (if any)
+    const bool full_cols = col0 + 32 <= P.n && (reinterpret_cast<uintptr_t>(P.ep.bias) & 15) == 0;
     if (MODE == GEMM_SWIGLU) {
-        // columns [0,16) are gate, [16,32) the matching up columns; two rows per step, 16 outputs each
-        const uint32_t oc = lane & 15, half = lane >> 4, ocol = col0 / 2 + oc;
-        const bool col_ok = col0 + 16 + oc < P.n;
-        float bg = 0.0f, bu = 0.0f;
-        if (P.ep.bias && col_ok) { bg = __ldg(P.ep.bias + col0 + oc); bu = __ldg(P.ep.bias + col0 + 16 + oc); }
+        // columns [0,16) are gate, [16,32) the matching up columns.  A lane makes 4 outputs of one row:
+        // 4 lanes per row, 8 rows per step.
+        const uint32_t j = lane & 3, rsub = lane >> 2;
         bf16* out = reinterpret_cast<bf16*>(P.out);
-        for (uint32_t rr = half; rr < rows; rr += 2) {
-            const float g = stage[stage_index(rr, oc)] + bg, u = stage[stage_index(rr, 16 + oc)] + bu;
-            if (col_ok) out[(size_t)(row0 + rr) * P.ldc + ocol] = __float2bfloat16_rn(fast_silu(g) * u);
-        }
-    } else if (MODE == GEMM_QKV) {
-        const uint32_t d = P.qkv.d;
-        const uint32_t pos = P.qkv.d_position ? *P.qkv.d_position : P.qkv.position;
-        if (d % 32 == 0 && col0 + 32 <= P.n) {
-            // the whole block belongs to one of q / K / V; two rows per step, a pair of columns per lane
-            const uint32_t which = col0 / d, cbase = col0 % d, cp = (lane & 15) * 2, half = lane >> 4;
-            float b0 = 0.0f, b1 = 0.0f;
-            if (P.ep.bias) { b0 = __ldg(P.ep.bias + col0 + cp); b1 = __ldg(P.ep.bias + col0 + cp + 1); }
-            for (uint32_t rr = half; rr < rows; rr += 2) {
-                const uint32_t row = row0 + rr;
-                const float2 v = *reinterpret_cast<const float2*>(stage + stage_index(rr, cp));
-                bf16* dst;
-                if (which == 0) {
-                    dst = P.qkv.q + (size_t)row * d;
-                } else {
-                    const size_t crow = (size_t)(row / P.qkv.chunk) * P.qkv.capacity + pos + row % P.qkv.chunk;
-                    dst = (which == 1 ? P.qkv.k_cache : P.qkv.v_cache) + crow * d;
+        if (full_cols && P.ldc % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 7) == 0) {
+            float4 bg = make_float4(0.f, 0.f, 0.f, 0.f), bu = bg;
+            if (P.ep.bias) {
+                bg = __ldg(reinterpret_cast<const float4*>(P.ep.bias + col0 + 4 * j));
+                bu = __ldg(reinterpret_cast<const float4*>(P.ep.bias + col0 + 16 + 4 * j));
+            }
+            const uint32_t ocol = col0 / 2 + 4 * j;
+#pragma unroll
+            for (uint32_t it = 0; it < 4; ++it) {
+                const uint32_t rr = it * 8 + rsub;
+                if (rr < rows) {
+                    const float4 g = stage_load4(stage, rr, 4 * j), u = stage_load4(stage, rr, 16 + 4 * j);
+                    const uint2 o = make_uint2(pack_bf16x2(fast_silu(g.x + bg.x) * (u.x + bu.x), fast_silu(g.y + bg.y) * (u.y + bu.y)),
+                                               pack_bf16x2(fast_silu(g.z + bg.z) * (u.z + bu.z), fast_silu(g.w + bg.w) * (u.w + bu.w)));
+                    *reinterpret_cast<uint2*>(out + (size_t)(row0 + rr) * P.ldc + ocol) = o;
                 }
-                *reinterpret_cast<uint32_t*>(dst + cbase + cp) = pack_bf16x2(v.x + b0, v.y + b1);
             }
         } else {
-            for (uint32_t rr = 0; rr < rows; ++rr)
-                if (col0 + lane < P.n) store_qkv(P, row0 + rr, col0 + lane, stage[stage_index(rr, lane)]);
+            const uint32_t oc = lane & 15, half = lane >> 4;
+            for (uint32_t rr = half; rr < rows; rr += 2)
+                if (col0 + 16 + oc < P.n)
+                    store_swiglu(P, row0 + rr, col0 + oc, col0 / 2 + oc, stage[stage_index(rr, oc)], stage[stage_index(rr, 16 + oc)]);
         }
-    } else if (P.ep.out_dtype == TNSR_B200_BF16 && P.ldc % 2 == 0 && col0 + 32 <= P.n &&
-               (reinterpret_cast<uintptr_t>(P.out) & 3) == 0) {
-        const uint32_t cp = (lane & 15) * 2, half = lane >> 4;
-        float b0 = 0.0f, b1 = 0.0f;
-        if (P.ep.bias) { b0 = __ldg(P.ep.bias + col0 + cp); b1 = __ldg(P.ep.bias + col0 + cp + 1); }
-        bf16* out = reinterpret_cast<bf16*>(P.out);
-        for (uint32_t rr = half; rr < rows; rr += 2) {
-            const float2 v = *reinterpret_cast<const float2*>(stage + stage_index(rr, cp));
-            const size_t orow = map_out_row(P.ep, row0 + rr);
-            *reinterpret_cast<uint32_t*>(out + orow * P.ldc + col0 + cp) =
-                pack_bf16x2(apply_activation(v.x + b0, P.ep.activation), apply_activation(v.y + b1, P.ep.activation));
+    } else if (MODE == GEMM_QKV || P.ep.out_dtype == TNSR_B200_BF16) {
+        // bf16 destinations: a lane converts 8 columns of one row (one 16-byte store): 4 lanes per row, 8 rows per step
+        const uint32_t cg = lane & 3, rsub = lane >> 2, c8 = 8 * cg;
+        bool fast = full_cols;
+        bf16* base = reinterpret_cast<bf16*>(P.out);
+        uint32_t ld = P.ldc, cbase = col0;
+        uint32_t which = 0, pos = 0;
+        if (MODE == GEMM_QKV) {
+            const uint32_t d = P.qkv.d;
+            fast = fast && d % 32 == 0;
+            which = col0 / d;
+            cbase = col0 % d;
+            ld = d;
+            base = which == 0 ? P.qkv.q : (which == 1 ? P.qkv.k_cache : P.qkv.v_cache);
+            pos = P.qkv.d_position ? *P.qkv.d_position : P.qkv.position;
         }
-    } else {
-        // f32 output (optionally + residual), or any ragged / unaligned case: one column per lane
-        const uint32_t col = col0 + lane;
-        const bool col_ok = col < P.n;
-        const float bv = (P.ep.bias && col_ok) ? __ldg(P.ep.bias + col) : 0.0f;
-        if (P.ep.out_dtype == TNSR_B200_F32) {
-            // The residual may be the output buffer itself (the residual stream is updated in place), so the
-            // compiler must not be left to order these loads against the stores: fetch all rows first.
-            float res[32];
+        fast = fast && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0;
+        if (fast) {
+            float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
+            if (P.ep.bias) {
+                b0 = __ldg(reinterpret_cast<const float4*>(P.ep.bias + col0 + c8));
+                b1 = __ldg(reinterpret_cast<const float4*>(P.ep.bias + col0 + c8 + 4));
+            }
+            const int act = MODE == GEMM_QKV ? ACT_NONE : P.ep.activation;
 #pragma unroll
-            for (int rr = 0; rr < 32; ++rr)
-                res[rr] = (P.ep.residual && col_ok && (uint32_t)rr < rows) ? P.ep.residual[(size_t)(row0 + rr) * P.ep.ldr + col] : 0.0f;
-            float* out = reinterpret_cast<float*>(P.out);
-#pragma unroll
-            for (int rr = 0; rr < 32; ++rr) {
-                if (col_ok && (uint32_t)rr < rows) {
-                    const float v = apply_activation(stage[stage_index(rr, lane)] + bv, P.ep.activation) + res[rr];
-                    out[map_out_row(P.ep, row0 + rr) * P.ldc + col] = v;
+            for (uint32_t it = 0; it < 4; ++it) {
+                const uint32_t rr = it * 8 + rsub;
+                if (rr < rows) {
+                    float4 v0 = stage_load4(stage, rr, c8), v1 = stage_load4(stage, rr, c8 + 4);
+                    v0 = act4(make_float4(v0.x + b0.x, v0.y + b0.y, v0.z + b0.z, v0.w + b0.w), act);
+                    v1 = act4(make_float4(v1.x + b1.x, v1.y + b1.y, v1.z + b1.z, v1.w + b1.w), act);
+                    const uint32_t row = row0 + rr;
+                    size_t orow;
+                    if (MODE == GEMM_QKV) orow = which == 0 ? row : (size_t)(row / P.qkv.chunk) * P.qkv.capacity + pos + row % P.qkv.chunk;
+                    else orow = map_out_row(P.ep, row);
+                    *reinterpret_cast<uint4*>(base + orow * ld + cbase + c8) =
+                        make_uint4(pack_bf16x2(v0.x, v0.y), pack_bf16x2(v0.z, v0.w), pack_bf16x2(v1.x, v1.y), pack_bf16x2(v1.z, v1.w));
                 }
             }
         } else {
             for (uint32_t rr = 0; rr < rows; ++rr) {
-                if (!col_ok) continue;
-                const float v = apply_activation(stage[stage_index(rr, lane)] + bv, P.ep.activation);
-                reinterpret_cast<bf16*>(P.out)[map_out_row(P.ep, row0 + rr) * P.ldc + col] = __float2bfloat16_rn(v);
+                if (col0 + lane >= P.n) continue;
+                if (MODE == GEMM_QKV) store_qkv(P, row0 + rr, col0 + lane, stage[stage_index(rr, lane)]);
+                else store_plain(P, row0 + rr, col0 + lane, stage[stage_index(rr, lane)]);
             }
+        }
+    } else {
+        // f32 output (+ optional residual): a lane owns 4 columns of one row (16 bytes): 8 lanes per row, 4 rows per step.
+        // The residual may be the output buffer itself (the residual stream is updated in place), so all residual
+        // rows are fetched before the first store.
+        float* out = reinterpret_cast<float*>(P.out);
+        const float* res = P.ep.residual;
+        const uint32_t c4 = 4 * (lane & 7), rsub = lane >> 3;
+        if (full_cols && P.ldc % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+            (!res || (P.ep.ldr % 4 == 0 && (reinterpret_cast<uintptr_t>(res) & 15) == 0))) {
+            float4 r4[8];
+#pragma unroll
+            for (uint32_t it = 0; it < 8; ++it) {
+                const uint32_t rr = it * 4 + rsub;
+                r4[it] = (res && rr < rows) ? *reinterpret_cast<const float4*>(res + (size_t)(row0 + rr) * P.ep.ldr + col0 + c4)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (P.ep.bias) bv = __ldg(reinterpret_cast<const float4*>(P.ep.bias + col0 + c4));
+#pragma unroll
+            for (uint32_t it = 0; it < 8; ++it) {
+                const uint32_t rr = it * 4 + rsub;
+                if (rr < rows) {
+                    float4 v = stage_load4(stage, rr, c4);
+                    v = act4(make_float4(v.x + bv.x, v.y + bv.y, v.z + bv.z, v.w + bv.w), P.ep.activation);
+                    v = make_float4(v.x + r4[it].x, v.y + r4[it].y, v.z + r4[it].z, v.w + r4[it].w);
+                    *reinterpret_cast<float4*>(out + map_out_row(P.ep, row0 + rr) * P.ldc + col0 + c4) = v;
+                }
+            }
+        } else {
+            const uint32_t col = col0 + lane;
+            const bool col_ok = col < P.n;
+            float rv[32];
+#pragma unroll
+            for (int rr = 0; rr < 32; ++rr)
+                rv[rr] = (res && col_ok && (uint32_t)rr < rows) ? res[(size_t)(row0 + rr) * P.ep.ldr + col] : 0.0f;
+            const float bv = (P.ep.bias && col_ok) ? __ldg(P.ep.bias + col) : 0.0f;
+#pragma unroll
+            for (int rr = 0; rr < 32; ++rr)
+                if (col_ok && (uint32_t)rr < rows)
+                    out[map_out_row(P.ep, row0 + rr) * P.ldc + col] = apply_activation(stage[stage_index(rr, lane)] + bv, P.ep.activation) + rv[rr];
         }
     }
     __syncwarp();  // the buffer is reused by the next block
