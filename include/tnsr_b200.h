@@ -305,6 +305,14 @@ TNSR_B200_API int tnsr_b200_prefill_attention(const void* q, const void* k_cache
                                               uint32_t position, uint32_t capacity, uint32_t heads,
                                               uint32_t head_dim, void* stream);
 
+/* Measurement aid (no reference counterpart): one CTA per SM streams `bytes` of
+ * `buffer` through a shared-memory ring of `stages` x `stage_bytes` with bulk
+ * async copies and discards them -- the K/V ring of the decode-attention kernel
+ * with the arithmetic taken out.  Timing it gives the read bandwidth that ring
+ * can reach on this GPU.  *bytes_read receives the bytes one launch moves. */
+TNSR_B200_API int tnsr_b200_stream_read_probe(const void* buffer, uint64_t bytes, uint32_t stage_bytes,
+                                              uint32_t stages, uint64_t* bytes_read, void* stream);
+
 /* Greedy pick per row: the last index holding the maximum under IEEE
  * totalOrder (src/nn/kv_cache.rs:148-153). */
 TNSR_B200_API int tnsr_b200_argmax(const float* logits, uint32_t* out, uint32_t rows, uint32_t vocab,

@@ -125,6 +125,8 @@ constexpr uint32_t DA_MAX_CTAS = 256;      // upper bound on the grid (one CTA p
 constexpr uint32_t DA_DIRECT = 0xffffffffu;
 struct DaItem {
     uint32_t session, key0, nkeys, slot;
+    uint32_t n_parts, first_slot;  // pieces of the session and the slot of its first piece (for the merge)
+    uint32_t pad[2];
 };
 
 // Work is split by position in the concatenation of all sessions' live keys, counted in stages of
@@ -139,7 +141,7 @@ struct DaItem {
 //   done      : uint32 [batch * heads]  partials stored so far per (session, head); zero between launches
 //   sstart    : uint32 [batch + 1]      first global stage of each session
 //   cta_begin : uint32 [DA_MAX_CTAS + 1] first item of each CTA
-//   items     : DaItem [batch + DA_MAX_CTAS]
+//   items     : DaItem [batch + DA_MAX_CTAS]   (32 bytes each)
 //   partial   : float  [batch + DA_MAX_CTAS][heads][head_dim + 2]   (numerator, then max, then sum)
 struct DaLayout {
     uint64_t first, count, done, sstart, cta_begin, items, partial, bytes;
@@ -251,6 +253,9 @@ da_plan_kernel(const uint32_t* __restrict__ lengths, const uint32_t* __restrict_
             it.key0 = (lo - s0) * DA_KS;
             it.nkeys = min(L, (hi - s0) * DA_KS) - it.key0;
             it.slot = c == 1 ? DA_DIRECT : f + j;
+            it.n_parts = c;
+            it.first_slot = f;
+            it.pad[0] = it.pad[1] = 0;
             items[f + j] = it;
         }
     }
@@ -325,10 +330,13 @@ __device__ __forceinline__ void da_bulk_load(void* dst, const void* src, uint32_
 }
 
 struct DaStageMeta {
-    uint32_t slot;    // partial slot of the item, or DA_DIRECT
-    uint32_t nk;      // valid keys in this stage (1..DA_KS)
-    uint32_t flags;   // bit 0: first stage of the item, bit 1: last stage
+    uint32_t slot;        // partial slot of the item, or DA_DIRECT
+    uint32_t nk;          // valid keys in this stage (1..DA_KS)
+    uint32_t flags;       // bit 0: first stage of the item, bit 1: last stage
     uint32_t session;
+    uint32_t n_parts;     // pieces of this session (for the merge)
+    uint32_t first_slot;  // partial slot of the session's first piece
+    uint32_t pad[2];
 };
 
 struct DaParams {
@@ -383,8 +391,13 @@ decode_attention_kernel(DaParams P) {
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            // item records and the per-session piece counts are fetched one item ahead, so their latency
+            // hides behind the copies of the current item
+            DaItem nxt = {};
+            if (item_begin < item_end) nxt = P.items[item_begin];
             for (uint32_t item = item_begin; ok && item < item_end; ++item) {
-                const DaItem it = P.items[item];
+                const DaItem it = nxt;
+                if (item + 1 < item_end) nxt = P.items[item + 1];
                 const size_t base = ((size_t)it.session * P.capacity + it.key0) * d;
                 const uint32_t n_stages = (it.nkeys + DA_KS - 1) / DA_KS;
                 for (uint32_t s = 0; s < n_stages; ++s) {
@@ -396,6 +409,8 @@ decode_attention_kernel(DaParams P) {
                     mt.nk = nk;
                     mt.flags = (s == 0 ? 1u : 0u) | (s + 1 == n_stages ? 2u : 0u);
                     mt.session = it.session;
+                    mt.n_parts = it.n_parts;
+                    mt.first_slot = it.first_slot;
                     meta[stage] = mt;
                     const uint32_t bytes = nk * row_bytes;
                     da_mbar_expect_tx(full_bar + stage, 2 * bytes + (s == 0 ? row_bytes : 0));
@@ -536,14 +551,14 @@ decode_attention_kernel(DaParams P) {
                     }
                     __syncwarp();
                     // whoever stores the last partial of (session, head) merges them
-                    const uint32_t n_parts = P.count[mt.session];
+                    const uint32_t n_parts = mt.n_parts;
                     uint32_t seen = 0;
                     if (lane == 0) seen = atomicAdd(P.done + (size_t)mt.session * P.heads + h, 1u);
                     seen = __shfl_sync(0xffffffffu, seen, 0);
                     if (seen + 1 == n_parts) {
                         __threadfence();
                         constexpr int DPL = HD / 32;  // output dims per lane
-                        const float* base = P.partial + ((size_t)P.first[mt.session] * P.heads + h) * (HD + 2);
+                        const float* base = P.partial + ((size_t)mt.first_slot * P.heads + h) * (HD + 2);
                         const size_t step = (size_t)P.heads * (HD + 2);
                         float mx = -INFINITY;
                         for (uint32_t i = 0; i < n_parts; ++i) mx = fmaxf(mx, __ldcg(base + i * step + HD));

@@ -5,6 +5,7 @@
     python -m tnsr_b200.opbench mlp         # configuration 2: fused SwiGLU MLP 4096 x 2048 -> 5632 -> 2048
     python -m tnsr_b200.opbench attention   # configuration 3: 64 sessions x 16 heads x 64, ragged lengths <= 4096
     python -m tnsr_b200.opbench serving_attention  # configuration 4's decode attention: 256 x 12 x 64, 641 live keys
+    python -m tnsr_b200.opbench stream_read # read-bandwidth ceiling of the bulk-copy K/V ring
     python -m tnsr_b200.opbench elementwise # LayerNorm, SwiGLU, embedding, greedy pick
     python -m tnsr_b200.opbench all
 
@@ -209,6 +210,19 @@ def bench_attention(samples, serving=False):
          peaks=kind)
 
 
+def bench_stream_read(samples):
+    """Ceiling of the bulk-copy K/V ring: stream 505 MB (one decode-attention launch of configuration 4) and discard."""
+    hbm, _, kind = peaks()
+    buf = torch.randint(0, 255, (505 << 20,), dtype=torch.uint8, device="cuda")
+    moved = C.c_uint64()
+    for stage_bytes, stages in ((16384, 4), (32768, 4), (49152, 4), (65536, 2), (65536, 3)):
+        def launch(_):
+            ok(lib().tnsr_b200_stream_read_probe(ptr(buf), buf.numel(), stage_bytes, stages, C.byref(moved), stream()))
+        ms, _ = timed(launch, 1, samples)
+        emit(op="stream_read_probe", stage_bytes=stage_bytes, stages=stages, ms=ms, gbs=moved.value / ms / 1e6,
+             frac_hbm=moved.value / ms / 1e6 / hbm, peaks=kind)
+
+
 def bench_elementwise(samples):
     hbm, _, kind = peaks()
     rows, d = 131072, 768
@@ -234,15 +248,17 @@ def bench_elementwise(samples):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "serving_gemms", "mlp", "attention", "serving_attention", "elementwise", "all"])
+    ap.add_argument("what", choices=["gemm", "serving_gemms", "mlp", "attention", "serving_attention", "stream_read", "elementwise", "all"])
     ap.add_argument("--samples", type=int, default=20)
     args = ap.parse_args()
     if not torch.cuda.is_available():
         sys.exit("opbench needs a CUDA device")
-    todo = ["gemm", "serving_gemms", "mlp", "attention", "serving_attention", "elementwise"] if args.what == "all" else [args.what]
+    todo = (["gemm", "serving_gemms", "mlp", "attention", "serving_attention", "stream_read", "elementwise"]
+            if args.what == "all" else [args.what])
     for name in todo:
         {"gemm": bench_gemm, "serving_gemms": bench_serving_gemms, "mlp": bench_mlp, "attention": bench_attention,
-         "serving_attention": lambda n: bench_attention(n, serving=True), "elementwise": bench_elementwise}[name](args.samples)
+         "serving_attention": lambda n: bench_attention(n, serving=True), "stream_read": bench_stream_read,
+         "elementwise": bench_elementwise}[name](args.samples)
 
 
 if __name__ == "__main__":
