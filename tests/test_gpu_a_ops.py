@@ -352,6 +352,45 @@ def test_prefill_attention_matches_f64_reference(oracle, hd, chunk, prefix):
     assert np.max(np.abs(got - ref)) <= max(1.0, float(np.max(np.abs(ref)))) / 128
 
 
+@pytest.mark.parametrize("chunk,prefix,heads,batch", [(32, 0, 1, 1), (128, 0, 2, 2), (128, 128, 3, 1), (256, 5, 2, 2),
+                                                      (300, 213, 3, 2), (512, 0, 2, 1), (77, 1000, 1, 2)])
+def test_prefill_attention_tcgen05_kernel_matches_f64_reference_and_warp_mma_kernel(oracle, chunk, prefix, heads, batch):
+    """Chunks of 32 rows and more at head width 64 run on the tcgen05 kernel: one to many 128-key blocks, ragged
+    last query tile, stale (NaN) cache rows past the live range.  Engine 1 selects the warp-level kernel for the
+    same call; both must sit within max|ref|/128 of the f64 reference."""
+    hd = 64
+    d = heads * hd
+    capacity = prefix + chunk + 3
+    salt = lambda n, s: bf16_round(attention_samples(n, s, 53.0, 1.0))
+    q = salt(batch * chunk * d, 7).reshape(batch, chunk, d)
+    k = salt(batch * chunk * d, 23).reshape(batch, chunk, d)
+    v = salt(batch * chunk * d, 31).reshape(batch, chunk, d)
+    ck = salt(batch * capacity * d, 43).reshape(batch, capacity, d)
+    cv = salt(batch * capacity * d, 71).reshape(batch, capacity, d)
+    ref = oracle.attention_f64(q, k, v, ck, cv, heads, prefix)
+    kc, vc = ck.copy(), cv.copy()
+    kc[:, prefix:prefix + chunk] = k
+    vc[:, prefix:prefix + chunk] = v
+    kc[:, prefix + chunk:] = np.nan
+    vc[:, prefix + chunk:] = np.nan
+    dq, dk, dv = dev(q, torch.bfloat16), dev(kc, torch.bfloat16), dev(vc, torch.bfloat16)
+    results = []
+    for engine in (0, 1):
+        out = torch.full((batch, chunk, d), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ok(lib().tnsr_b200_set_gemm_engine(engine))
+        try:
+            ok(lib().tnsr_b200_prefill_attention(ptr(dq), ptr(dk), ptr(dv), ptr(out), batch, chunk, prefix, capacity,
+                                                 heads, hd, stream()))
+            torch.cuda.synchronize()
+        finally:
+            lib().tnsr_b200_set_gemm_engine(0)
+        got = out.float().cpu().numpy().reshape(batch, chunk, heads, hd).transpose(0, 2, 1, 3)
+        assert np.all(np.isfinite(got))
+        assert np.max(np.abs(got - ref)) <= max(1.0, float(np.max(np.abs(ref)))) / 128
+        results.append(got)
+    assert np.max(np.abs(results[0] - results[1])) <= max(1.0, float(np.max(np.abs(ref)))) / 64
+
+
 # ---- greedy pick -------------------------------------------------------------------
 def test_argmax_prefers_the_last_maximum(oracle):
     rng = np.random.default_rng(13)

@@ -184,12 +184,20 @@ int launch_decode_attention(const bf16* q, const bf16* k_cache, const bf16* v_ca
                             uint32_t batch, uint32_t capacity, uint32_t heads, uint32_t head_dim,
                             int* d_status, cudaStream_t stream);
 
-// Tiled causal prefill attention over the cache (tensor cores).
+// Tiled causal prefill attention over the cache (tensor cores).  The tcgen05 kernel runs when the
+// position is known on the host (d_position == nullptr), the head width is 64 and the chunk has at
+// least 32 rows; otherwise the warp-level mma.sync kernel does.  d_status (may be null) receives
+// DEV_TIMEOUT if a bounded wait of the tcgen05 kernel gives up.
 bool prefill_attention_supported(uint32_t head_dim);
 int launch_prefill_attention(const bf16* q, const bf16* k_cache, const bf16* v_cache, bf16* out,
                              uint32_t sessions, uint32_t chunk, uint32_t position,
                              const uint32_t* d_position, uint32_t capacity, uint32_t heads,
-                             uint32_t head_dim, cudaStream_t stream);
+                             uint32_t head_dim, int* d_status, cudaStream_t stream);
+bool prefill_attention_tc_eligible(uint32_t sessions, uint32_t chunk, uint32_t position, const uint32_t* d_position,
+                                   uint32_t capacity, uint32_t heads, uint32_t head_dim);
+int launch_prefill_attention_tc(const bf16* q, const bf16* k_cache, const bf16* v_cache, bf16* out, uint32_t sessions,
+                                uint32_t chunk, uint32_t position, uint32_t capacity, uint32_t heads, int* d_status,
+                                cudaStream_t stream);
 
 // ---- device helpers ----------------------------------------------------------
 #ifdef __CUDACC__

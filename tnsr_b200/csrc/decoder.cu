@@ -392,7 +392,7 @@ int step_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, 
             planned = true;
         } else if (chunk > 1 && prefill_attention_supported(hd)) {
             RUN(dec, launch_prefill_attention(q, (const bf16*)L.kcache, (const bf16*)L.vcache, att, B, chunk, position, d_position,
-                                              c.capacity, H, hd, st));
+                                              c.capacity, H, hd, dec->d_status, st));
         } else {
             RUN(dec, launch_attention_generic(q, (const bf16*)L.kcache, (const bf16*)L.vcache, att, B, chunk, position, d_position,
                                               c.capacity, H, hd, st));

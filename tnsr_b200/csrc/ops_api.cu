@@ -120,7 +120,7 @@ int tnsr_b200_prefill_attention(const void* q, const void* k_cache, const void* 
     if ((uint64_t)position + chunk > capacity) return bad("prefill_attention: position + chunk exceeds the capacity");
     if (prefill_attention_supported(head_dim))
         return launch_prefill_attention((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, batch, chunk,
-                                        position, nullptr, capacity, heads, head_dim, as_stream(stream));
+                                        position, nullptr, capacity, heads, head_dim, nullptr, as_stream(stream));
     return launch_attention_generic((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, batch, chunk,
                                     position, nullptr, capacity, heads, head_dim, as_stream(stream));
 }

@@ -7,6 +7,9 @@
 // the part of the reference's `decoder_prefill_bf16` (src/nn/kv_cache/prefill.rs:
 // 170-607: 16/32 queries x 32-key steps on 16x16x16 wmma, key partitions merged
 // afterwards); here one CTA walks all keys of its query block, so no merge pass.
+// Large chunks at a host-known position go to the tcgen05 kernel (prefill_tc.cu);
+// this one serves device-resident positions, short chunks and the CUDA-core-only
+// engine setting.
 #include "common.cuh"
 
 namespace tb {
@@ -201,7 +204,7 @@ bool prefill_attention_supported(uint32_t head_dim) { return head_dim == PF_HD; 
 int launch_prefill_attention(const bf16* q, const bf16* k_cache, const bf16* v_cache, bf16* out,
                              uint32_t sessions, uint32_t chunk, uint32_t position,
                              const uint32_t* d_position, uint32_t capacity, uint32_t heads,
-                             uint32_t head_dim, cudaStream_t stream) {
+                             uint32_t head_dim, int* d_status, cudaStream_t stream) {
     if (sessions == 0 || chunk == 0) return TNSR_B200_OK;
     if (head_dim != PF_HD) {
         set_thread_error("prefill attention: head_dim must be 64");
@@ -213,6 +216,8 @@ int launch_prefill_attention(const bf16* q, const bf16* k_cache, const bf16* v_c
         set_thread_error("prefill attention: pointers must be 16-byte aligned");
         return TNSR_B200_ERR_INVALID_ARGUMENT;
     }
+    if (prefill_attention_tc_eligible(sessions, chunk, position, d_position, capacity, heads, head_dim))
+        return launch_prefill_attention_tc(q, k_cache, v_cache, out, sessions, chunk, position, capacity, heads, d_status, stream);
     const float scale_log2 = (1.0f / sqrtf((float)head_dim)) * 1.4426950408889634f;
     dim3 grid(ceil_div(chunk, PF_BQ), heads, sessions);
     prefill_attention_kernel<<<grid, PF_THREADS, 0, stream>>>(q, k_cache, v_cache, out, chunk, position, d_position,

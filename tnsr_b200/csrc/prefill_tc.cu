@@ -1,0 +1,361 @@
+// Causal prefill attention on the 5th-generation tensor cores (tcgen05), head
+// width 64, bf16 cache.  The job is the reference's `decoder_prefill_bf16`
+// (src/nn/kv_cache/prefill.rs:170-607): `chunk` new queries per session attend
+// keys 0 .. position + t of the cache that already holds their own rows.
+//
+// One CTA = 128 queries of one (session, head); the accumulator row of a query is
+// one TMEM lane.  Keys arrive in blocks of 128.
+//
+//   warp 0      TMA: the Q tile once, then K and V blocks into a three-stage ring
+//               (3-D tensor maps {width, live rows, sessions}: rows past
+//               position + chunk read as zeros, so stale cache rows never meet
+//               the arithmetic).
+//   warp 1      one thread issues the MMAs: S_j = Q K_j^T (M128 N128 K64) into one
+//               of two TMEM score buffers, then O_j = P_j V_j (M128 N64 K128) into
+//               one of two TMEM output buffers.  V is consumed where TMA put it,
+//               as an MN-major operand -- no transpose pass.
+//   warps 2-5   softmax, one thread per query: read the score row from TMEM (twice:
+//               row maximum, then exponentials), write P_j as bf16 into shared
+//               memory in the K-major swizzled layout the MMA reads, and fold the
+//               PREVIOUS block's O_{j-1} into the running output in registers
+//               (rescaled by exp2(m_old - m_new)), so the fold overlaps P_j V_j.
+//
+// Ordering that needs no barrier: the MMAs of one thread complete in issue order,
+// so when S_{j+2} is signalled, P_j V_j has finished reading P buffer j % 2 and
+// O buffer j % 2 was folded before P_{j+2} was signalled.
+//
+// Every wait is bounded; a wait that gives up raises the CTA's abort flag, the
+// roles fall through to the common teardown and the status word is set.
+#include "tc_common.cuh"
+
+namespace tb {
+
+constexpr int PT_BQ = 128, PT_BK = 128, PT_HD = 64;
+constexpr int PT_KV_STAGES = 3;
+constexpr int PT_THREADS = 192;
+constexpr uint32_t PT_TILE_BYTES = 128 * 128;         // 128 rows of 64 bf16
+constexpr uint32_t PT_KV_BYTES = 2 * PT_TILE_BYTES;   // K block + V block
+constexpr uint32_t PT_P_BYTES = 2 * PT_TILE_BYTES;    // 128 x 128 bf16 as two 64-key sub-tiles
+constexpr uint32_t PT_SMEM_BYTES = 1024 + PT_TILE_BYTES + PT_KV_STAGES * PT_KV_BYTES + 2 * PT_P_BYTES + 256;
+constexpr uint32_t PT_TMEM_COLS = 512;                // scores 2 x 128, outputs 2 x 64 (power of two)
+constexpr uint32_t PT_O_COL = 256;
+
+// kind::f16 instruction descriptors: f32 accumulator, bf16 operands, M = 128.
+constexpr uint32_t PT_IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+// B operand (V) MN-major: bit 16
+constexpr uint32_t PT_IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ float pt_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+struct PtParams {
+    bf16* out;
+    uint32_t chunk, position, heads, q_tiles;
+    float scale_log2;
+    int* d_status;
+};
+
+__global__ void __launch_bounds__(PT_THREADS, 1)
+prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, PtParams prm) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    uint8_t* q_tile = smem;
+    uint8_t* kv_ring = smem + PT_TILE_BYTES;
+    uint8_t* p_tiles = kv_ring + PT_KV_STAGES * PT_KV_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(p_tiles + 2 * PT_P_BYTES);
+    uint64_t* q_full = bars;                       // [1]
+    uint64_t* kv_full = q_full + 1;                // [PT_KV_STAGES]
+    uint64_t* kv_empty = kv_full + PT_KV_STAGES;   // [PT_KV_STAGES]
+    uint64_t* s_full = kv_empty + PT_KV_STAGES;    // [2]
+    uint64_t* s_empty = s_full + 2;                // [2]
+    uint64_t* p_full = s_empty + 2;                // [2]
+    uint64_t* o_full = p_full + 2;                 // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the longest query tiles (most key blocks) are scheduled first
+    const uint32_t q_tile_index = prm.q_tiles - 1 - blockIdx.x;
+    const uint32_t q0 = q_tile_index * PT_BQ, h = blockIdx.y, s = blockIdx.z;
+    const uint32_t last_q = min(q0 + PT_BQ, prm.chunk) - 1;
+    const uint32_t total = prm.position + last_q + 1;              // keys visible to the tile's last query
+    const uint32_t n_blocks = (total + PT_BK - 1) / PT_BK;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int i = 0; i < PT_KV_STAGES; ++i) { mbar_init(kv_full + i, 1); mbar_init(kv_empty + i, 1); }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(s_full + i, 1);
+            mbar_init(s_empty + i, 4);
+            mbar_init(p_full + i, 4);
+            mbar_init(o_full + i, 1);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    pdl_wait();
+    pdl_trigger();
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, PT_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            mbar_expect_tx(q_full, PT_TILE_BYTES);
+            tma_load_3d(q_tile, &map_q, (int32_t)(h * PT_HD), (int32_t)q0, (int32_t)s, q_full);
+            uint32_t stage = 0, phase = 0;
+            for (uint32_t j = 0; j < n_blocks; ++j) {
+                if (!mbar_wait(kv_empty + stage, phase ^ 1, abort_flag)) break;
+                uint8_t* dst = kv_ring + stage * PT_KV_BYTES;
+                mbar_expect_tx(kv_full + stage, PT_KV_BYTES);
+                tma_load_3d(dst, &map_k, (int32_t)(h * PT_HD), (int32_t)(j * PT_BK), (int32_t)s, kv_full + stage);
+                tma_load_3d(dst + PT_TILE_BYTES, &map_v, (int32_t)(h * PT_HD), (int32_t)(j * PT_BK), (int32_t)s, kv_full + stage);
+                if (++stage == PT_KV_STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint64_t qdesc = make_kmajor_sw128_desc(smem_u32(q_tile));
+            // S_j = Q K_j^T : four K steps of 16 dims, +32 bytes inside the swizzle row each
+            auto issue_s = [&](uint32_t j, uint32_t stage) {
+                const uint64_t kdesc = make_kmajor_sw128_desc(smem_u32(kv_ring + stage * PT_KV_BYTES));
+                const uint32_t d_tmem = tmem_base + (j & 1) * PT_BK;
+#pragma unroll
+                for (uint32_t kk = 0; kk < PT_HD / 16; ++kk) umma_bf16(d_tmem, qdesc + kk * 2, kdesc + kk * 2, PT_IDESC_S, kk != 0);
+                umma_commit(s_full + (j & 1));
+            };
+            bool ok = mbar_wait(q_full, 0, abort_flag);
+            uint32_t s_stage = 0, s_phase = 0;   // ring position of the next K block to multiply
+            uint32_t o_stage = 0;                // ring position of the next V block to multiply
+            if (ok) ok = mbar_wait(kv_full + 0, 0, abort_flag);
+            if (ok) {
+                tc_fence_after();
+                issue_s(0, 0);
+                if (++s_stage == PT_KV_STAGES) { s_stage = 0; s_phase ^= 1; }
+            }
+            for (uint32_t j = 0; ok && j < n_blocks; ++j) {
+                if (j + 1 < n_blocks) {
+                    if (!mbar_wait(kv_full + s_stage, s_phase, abort_flag)) { ok = false; break; }
+                    // score buffer (j + 1) % 2 was last used by block j - 1
+                    if (j >= 1 && !mbar_wait(s_empty + ((j + 1) & 1), ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    issue_s(j + 1, s_stage);
+                    if (++s_stage == PT_KV_STAGES) { s_stage = 0; s_phase ^= 1; }
+                }
+                if (!mbar_wait(p_full + (j & 1), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                // O_j = P_j V_j : eight K steps of 16 keys.  P: two K-major sub-tiles of 64 keys; V: MN-major,
+                // 16 keys = two 8-key groups 1024 bytes apart, so each step starts 2048 bytes further on.
+                const uint32_t p_addr = smem_u32(p_tiles + (j & 1) * PT_P_BYTES);
+                const uint32_t v_addr = smem_u32(kv_ring + o_stage * PT_KV_BYTES + PT_TILE_BYTES);
+                const uint32_t d_tmem = tmem_base + PT_O_COL + (j & 1) * PT_HD;
+#pragma unroll
+                for (uint32_t kk = 0; kk < PT_BK / 16; ++kk) {
+                    const uint64_t pdesc = make_kmajor_sw128_desc(p_addr + (kk >> 2) * PT_TILE_BYTES) + (kk & 3) * 2;
+                    const uint64_t vdesc = make_mnmajor_sw128_desc(v_addr + kk * 2048, PT_TILE_BYTES, 1024);
+                    umma_bf16(d_tmem, pdesc, vdesc, PT_IDESC_O, kk != 0);
+                }
+                umma_commit(o_full + (j & 1));
+                umma_commit(kv_empty + o_stage);   // both products of this ring stage are done
+                if (++o_stage == PT_KV_STAGES) o_stage = 0;
+            }
+        }
+    } else {
+        // ---------------- softmax warps: one query row per thread ----------------
+        const uint32_t quarter = warp & 3;
+        const uint32_t row = quarter * 32 + lane;
+        const uint32_t q_idx = min(q0 + row, prm.chunk - 1);
+        const uint32_t limit = prm.position + q_idx;             // last visible key of this row
+        const uint32_t lane_taddr = tmem_base + ((quarter * 32u) << 16);
+        const float sl2 = prm.scale_log2;
+        float acc[PT_HD];
+#pragma unroll
+        for (int i = 0; i < PT_HD; ++i) acc[i] = 0.0f;
+        float m = -INFINITY, l = 0.0f, corr_pending = 0.0f;
+        bool ok = true;
+
+        // acc = acc * corr + O_b  (O_b: this row's 64 outputs of block b)
+        auto fold = [&](uint32_t b, float corr) -> bool {
+            if (!mbar_wait(o_full + (b & 1), (b >> 1) & 1, abort_flag)) return false;
+            tc_fence_after();
+            const uint32_t taddr = lane_taddr + PT_O_COL + (b & 1) * PT_HD;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                float v[32];
+                tmem_ld32(taddr + c * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], corr, v[i]);
+            }
+            return true;
+        };
+
+        for (uint32_t j = 0; j < n_blocks; ++j) {
+            const uint32_t sb = j & 1;
+            if (!mbar_wait(s_full + sb, (j >> 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = lane_taddr + sb * PT_BK;
+            const uint32_t kbase = j * PT_BK;
+            const bool need_mask = kbase + PT_BK - 1 > limit;
+            // pass 1: row maximum of the raw scores
+            float mx = m;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                float v[32];
+                tmem_ld32(taddr + c * 32, v);
+                tmem_ld_wait();
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) if (kbase + c * 32 + i > limit) v[i] = -INFINITY;
+                }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+            }
+            const float ms = (mx == -INFINITY) ? 0.0f : mx;
+            const float corr = pt_ex2((m - ms) * sl2);      // 0 for the first block
+            m = mx;
+            const float neg = -ms * sl2;
+            // pass 2: p = exp2(s * scale - m * scale), bf16, into the P tile (row = 128 bytes per 64 keys,
+            // 16-byte chunk c of row r at c ^ (r & 7))
+            uint8_t* p_row = p_tiles + sb * PT_P_BYTES + row * 128u;
+            float rs = 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                float v[32];
+                tmem_ld32(taddr + c * 32, v);
+                tmem_ld_wait();
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) if (kbase + c * 32 + i > limit) v[i] = -INFINITY;
+                }
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float p0 = pt_ex2(fmaf(v[2 * i], sl2, neg)), p1 = pt_ex2(fmaf(v[2 * i + 1], sl2, neg));
+                    rs += p0 + p1;
+                    packed[i] = pack_bf16x2(p0, p1);
+                }
+                uint8_t* sub = p_row + (c >> 1) * PT_TILE_BYTES;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t chunk16 = (uint32_t)((c & 1) * 4 + i);
+                    *reinterpret_cast<uint4*>(sub + (((chunk16 ^ row) & 7u) << 4)) =
+                        make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                }
+            }
+            l = l * corr + rs;
+            // scores consumed: the buffer may take S_{j+2}; P written: visible to the tensor core, then signal
+            tc_fence_before();
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(s_empty + sb);
+                mbar_arrive(p_full + sb);
+            }
+            if (j > 0 && !fold(j - 1, corr_pending)) { ok = false; break; }
+            corr_pending = corr;
+        }
+        if (ok && n_blocks > 0) ok = fold(n_blocks - 1, corr_pending);
+        if (ok && q0 + row < prm.chunk) {
+            const float inv = 1.0f / l;
+            bf16* og = prm.out + ((size_t)s * prm.chunk + q0 + row) * ((size_t)prm.heads * PT_HD) + (size_t)h * PT_HD;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                uint4 w;
+                w.x = pack_bf16x2(acc[8 * i] * inv, acc[8 * i + 1] * inv);
+                w.y = pack_bf16x2(acc[8 * i + 2] * inv, acc[8 * i + 3] * inv);
+                w.z = pack_bf16x2(acc[8 * i + 4] * inv, acc[8 * i + 5] * inv);
+                w.w = pack_bf16x2(acc[8 * i + 6] * inv, acc[8 * i + 7] * inv);
+                *reinterpret_cast<uint4*>(og + 8 * i) = w;
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // give copies that are still in flight time to land before the CTA's shared memory is released
+        const uint64_t start = global_timer_ns();
+        while (global_timer_ns() - start < 200000ull) __nanosleep(1000);
+        if (threadIdx.x == 0 && prm.d_status) atomicCAS(prm.d_status, DEV_OK, DEV_TIMEOUT);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, PT_TMEM_COLS);
+    }
+}
+
+// {width, rows, sessions} bf16, `row_stride` elements between rows of one session, `session_rows`
+// rows between sessions; box = 64 columns x 128 rows x 1 session.
+static bool make_map3(CUtensorMap* map, const void* base, uint64_t width, uint64_t rows, uint64_t sessions,
+                      uint64_t session_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {width, rows, sessions};
+    cuuint64_t strides[2] = {width * 2, session_rows * width * 2};
+    cuuint32_t box[3] = {(cuuint32_t)PT_HD, 128, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+bool prefill_attention_tc_eligible(uint32_t sessions, uint32_t chunk, uint32_t position, const uint32_t* d_position,
+                                   uint32_t capacity, uint32_t heads, uint32_t head_dim) {
+    // the live row count goes into the tensor maps, so the position must be known on the host
+    if (d_position != nullptr || head_dim != PT_HD) return false;
+    if (g_gemm_engine == 1) return false;
+    if ((uint64_t)position + chunk > capacity) return false;
+    if (heads > 65535u || sessions > 65535u || chunk < 32) return false;
+    return encode_fn() != nullptr;
+}
+
+int launch_prefill_attention_tc(const bf16* q, const bf16* k_cache, const bf16* v_cache, bf16* out, uint32_t sessions,
+                                uint32_t chunk, uint32_t position, uint32_t capacity, uint32_t heads, int* d_status,
+                                cudaStream_t stream) {
+    const uint64_t width = (uint64_t)heads * PT_HD;
+    CUtensorMap mq, mk, mv;
+    if (!make_map3(&mq, q, width, chunk, sessions, chunk) ||
+        !make_map3(&mk, k_cache, width, (uint64_t)position + chunk, sessions, capacity) ||
+        !make_map3(&mv, v_cache, width, (uint64_t)position + chunk, sessions, capacity)) {
+        set_thread_error("prefill attention: tensor map encoding failed");
+        return TNSR_B200_ERR_CUDA;
+    }
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        if (cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PT_SMEM_BYTES) != cudaSuccess)
+            return check_launch("prefill_attention_tc attribute");
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    PtParams prm;
+    prm.out = out;
+    prm.chunk = chunk;
+    prm.position = position;
+    prm.heads = heads;
+    prm.q_tiles = ceil_div(chunk, (uint32_t)PT_BQ);
+    prm.scale_log2 = (1.0f / sqrtf((float)PT_HD)) * 1.4426950408889634f;
+    prm.d_status = d_status;
+    dim3 grid(prm.q_tiles, heads, sessions);
+    launch_kernel(prefill_attention_tc_kernel, grid, dim3(PT_THREADS), (size_t)PT_SMEM_BYTES, stream, mq, mk, mv, prm);
+    count_launch();
+    return check_launch("prefill_attention_tc");
+}
+
+}  // namespace tb

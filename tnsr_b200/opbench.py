@@ -7,6 +7,7 @@
     python -m tnsr_b200.opbench serving_attention  # configuration 4's decode attention: 256 x 12 x 64, 641 live keys
     python -m tnsr_b200.opbench stream_read # read-bandwidth ceiling of the bulk-copy K/V ring
     python -m tnsr_b200.opbench elementwise # LayerNorm, SwiGLU, embedding, greedy pick
+    python -m tnsr_b200.opbench prefill_attention  # configuration 4's prefill attention on both engines
     python -m tnsr_b200.opbench all
 
 Every line is one JSON object: algorithmic flops / bytes, CUDA-event time (median of `--samples`
@@ -210,6 +211,33 @@ def bench_attention(samples, serving=False):
          peaks=kind)
 
 
+def bench_prefill_attention(samples, sessions=64):
+    """Prefill attention of configuration 4 (512 new queries at position 0, 12 heads x 64, capacity 768) on both
+    engines: tcgen05 (engine 0) and warp-level mma.sync (engine 1).  Causal FLOPs: 4 * hd per (query, visible key)."""
+    _, tf, kind = peaks()
+    heads, hd, chunk, position, capacity = 12, 64, 512, 0, 768
+    d = heads * hd
+    g = torch.Generator(device="cuda").manual_seed(6)
+    q = torch.randn((sessions, chunk, d), device="cuda", generator=g).to(torch.bfloat16)
+    kc = torch.randn((sessions, capacity, d), device="cuda", generator=g).to(torch.bfloat16)
+    vc = torch.randn((sessions, capacity, d), device="cuda", generator=g).to(torch.bfloat16)
+    out = torch.empty((sessions, chunk, d), device="cuda", dtype=torch.bfloat16)
+    pairs = sessions * heads * sum(position + t + 1 for t in range(chunk))
+    flops = 4.0 * hd * pairs
+    results = {}
+    for engine, name in ((0, "tcgen05"), (1, "mma.sync")):
+        ok(lib().tnsr_b200_set_gemm_engine(engine))
+        try:
+            ms, _ = timed(lambda _: ok(lib().tnsr_b200_prefill_attention(ptr(q), ptr(kc), ptr(vc), ptr(out), sessions, chunk,
+                                                                         position, capacity, heads, hd, stream())), 1, samples)
+        finally:
+            lib().tnsr_b200_set_gemm_engine(0)
+        results[name] = out.float().clone()
+        emit(op="prefill_attention", engine=name, sessions=sessions, chunk=chunk, position=position, heads=heads, head_dim=hd,
+             ms=ms, causal_tflops=flops / ms / 1e9, frac_tensor=flops / ms / 1e9 / tf, peaks=kind)
+    emit(op="prefill_attention", max_abs_difference_between_engines=float((results["tcgen05"] - results["mma.sync"]).abs().max()))
+
+
 def bench_stream_read(samples):
     """Ceiling of the bulk-copy K/V ring: stream 505 MB (one decode-attention launch of configuration 4) and discard."""
     hbm, _, kind = peaks()
@@ -248,17 +276,17 @@ def bench_elementwise(samples):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "serving_gemms", "mlp", "attention", "serving_attention", "stream_read", "elementwise", "all"])
+    ap.add_argument("what", choices=["gemm", "serving_gemms", "mlp", "attention", "serving_attention", "stream_read", "elementwise", "prefill_attention", "all"])
     ap.add_argument("--samples", type=int, default=20)
     args = ap.parse_args()
     if not torch.cuda.is_available():
         sys.exit("opbench needs a CUDA device")
-    todo = (["gemm", "serving_gemms", "mlp", "attention", "serving_attention", "stream_read", "elementwise"]
+    todo = (["gemm", "serving_gemms", "mlp", "attention", "serving_attention", "stream_read", "elementwise", "prefill_attention"]
             if args.what == "all" else [args.what])
     for name in todo:
         {"gemm": bench_gemm, "serving_gemms": bench_serving_gemms, "mlp": bench_mlp, "attention": bench_attention,
          "serving_attention": lambda n: bench_attention(n, serving=True), "stream_read": bench_stream_read,
-         "elementwise": bench_elementwise}[name](args.samples)
+         "elementwise": bench_elementwise, "prefill_attention": bench_prefill_attention}[name](args.samples)
 
 
 if __name__ == "__main__":
