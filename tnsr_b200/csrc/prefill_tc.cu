@@ -4,25 +4,35 @@
 // keys 0 .. position + t of the cache that already holds their own rows.
 //
 // One CTA = 128 queries of one (session, head); the accumulator row of a query is
-// one TMEM lane.  Keys arrive in blocks of 128.
+// one TMEM lane.  Keys arrive in blocks of 128.  Two CTAs share an SM (about 100 KB
+// of shared memory and 256 TMEM columns each), so one CTA's loads, softmax and
+// hand-overs overlap the other's.
 //
-//   warp 0      TMA: the Q tile once, then K and V blocks into a three-stage ring
+//   warp 0      TMA: the Q tile once, then K and V blocks into a two-stage ring
 //               (3-D tensor maps {width, live rows, sessions}: rows past
 //               position + chunk read as zeros, so stale cache rows never meet
 //               the arithmetic).
-//   warp 1      one thread issues the MMAs: S_j = Q K_j^T (M128 N128 K64) into one
-//               of two TMEM score buffers, then O_j = P_j V_j (M128 N64 K128) into
-//               one of two TMEM output buffers.  V is consumed where TMA put it,
-//               as an MN-major operand -- no transpose pass.
-//   warps 2-5   softmax, one thread per query: read the score row from TMEM (twice:
-//               row maximum, then exponentials), write P_j as bf16 into shared
-//               memory in the K-major swizzled layout the MMA reads, and fold the
-//               PREVIOUS block's O_{j-1} into the running output in registers
-//               (rescaled by exp2(m_old - m_new)), so the fold overlaps P_j V_j.
+//   warp 1      one thread issues the MMAs: S_j = Q K_j^T (M128 N128 K64) into the
+//               TMEM score buffer, O_j = P_j V_j (M128 N64 K128) into the TMEM
+//               output buffer.  V is consumed where TMA put it, as an MN-major
+//               operand -- no transpose pass.
+//   warps 2-9   softmax, two threads per query row (a warp may only read its own
+//               quarter of the TMEM lanes; the two warps of a quarter take 64 score
+//               columns and 32 output columns each).  Per block: row maximum of the
+//               own half, exchanged with the partner through shared memory; fold
+//               O_{j-1} into the running output (rescaled by exp2(m_old - m_new));
+//               exponentials as bf16 into the P tile in the K-major swizzled layout
+//               the MMA reads.  Keys 0-63 of P_j go where K_j was (dead once S_j is
+//               complete, not reloaded before P_j V_j is), keys 64-127 to a tile of
+//               their own.
 //
-// Ordering that needs no barrier: the MMAs of one thread complete in issue order,
-// so when S_{j+2} is signalled, P_j V_j has finished reading P buffer j % 2 and
-// O buffer j % 2 was folded before P_{j+2} was signalled.
+// Hand-overs (single-buffered, phase parity = block index & 1):
+//   s_full   S_j complete                      MMA commit  -> softmax
+//   pair     both halves of a row wrote their maximum      softmax <-> softmax (per lane quarter)
+//   p_full   P_j written, S_j no longer needed softmax     -> MMA (issues S_{j+1}, then P_j V_j)
+//   o_full   O_j complete, P_j no longer read  MMA commit  -> softmax (fold; then block j+1 may overwrite the
+//                                                             upper P tile; the next P V overwrites O only after
+//                                                             the following p_full, i.e. after the fold)
 //
 // Every wait is bounded; a wait that gives up raises the CTA's abort flag, the
 // roles fall through to the common teardown and the status word is set.
@@ -31,14 +41,14 @@
 namespace tb {
 
 constexpr int PT_BQ = 128, PT_BK = 128, PT_HD = 64;
-constexpr int PT_KV_STAGES = 3;
-constexpr int PT_THREADS = 192;
+constexpr int PT_KV_STAGES = 2;
+constexpr int PT_THREADS = 320;
 constexpr uint32_t PT_TILE_BYTES = 128 * 128;         // 128 rows of 64 bf16
 constexpr uint32_t PT_KV_BYTES = 2 * PT_TILE_BYTES;   // K block + V block
-constexpr uint32_t PT_P_BYTES = 2 * PT_TILE_BYTES;    // 128 x 128 bf16 as two 64-key sub-tiles
-constexpr uint32_t PT_SMEM_BYTES = 1024 + PT_TILE_BYTES + PT_KV_STAGES * PT_KV_BYTES + 2 * PT_P_BYTES + 256;
-constexpr uint32_t PT_TMEM_COLS = 512;                // scores 2 x 128, outputs 2 x 64 (power of two)
-constexpr uint32_t PT_O_COL = 256;
+constexpr uint32_t PT_XM_BYTES = 2 * 2 * 128 * 4;     // row maxima: [block parity][half][row]
+constexpr uint32_t PT_SMEM_BYTES = 1024 + PT_TILE_BYTES + PT_KV_STAGES * PT_KV_BYTES + PT_TILE_BYTES + PT_XM_BYTES + 256;
+constexpr uint32_t PT_TMEM_COLS = 256;                // scores 128, outputs 64 (power of two)
+constexpr uint32_t PT_O_COL = 128;
 
 // kind::f16 instruction descriptors: f32 accumulator, bf16 operands, M = 128.
 constexpr uint32_t PT_IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
@@ -50,6 +60,7 @@ __device__ __forceinline__ float pt_ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ float pt_max4(const float* v) { return fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3])); }
 
 struct PtParams {
     bf16* out;
@@ -58,7 +69,7 @@ struct PtParams {
     int* d_status;
 };
 
-__global__ void __launch_bounds__(PT_THREADS, 1)
+__global__ void __launch_bounds__(PT_THREADS, 2)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, PtParams prm) {
     extern __shared__ uint8_t smem_raw[];
@@ -66,16 +77,17 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
     uint8_t* q_tile = smem;
     uint8_t* kv_ring = smem + PT_TILE_BYTES;
-    uint8_t* p_tiles = kv_ring + PT_KV_STAGES * PT_KV_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(p_tiles + 2 * PT_P_BYTES);
+    uint8_t* p_upper = kv_ring + PT_KV_STAGES * PT_KV_BYTES;     // keys 64-127 of P
+    float* xm = reinterpret_cast<float*>(p_upper + PT_TILE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(p_upper + PT_TILE_BYTES + PT_XM_BYTES);
     uint64_t* q_full = bars;                       // [1]
     uint64_t* kv_full = q_full + 1;                // [PT_KV_STAGES]
     uint64_t* kv_empty = kv_full + PT_KV_STAGES;   // [PT_KV_STAGES]
-    uint64_t* s_full = kv_empty + PT_KV_STAGES;    // [2]
-    uint64_t* s_empty = s_full + 2;                // [2]
-    uint64_t* p_full = s_empty + 2;                // [2]
-    uint64_t* o_full = p_full + 2;                 // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+    uint64_t* s_full = kv_empty + PT_KV_STAGES;    // [1]
+    uint64_t* p_full = s_full + 1;                 // [1]
+    uint64_t* o_full = p_full + 1;                 // [1]
+    uint64_t* pair = o_full + 1;                   // [4], one per lane quarter
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -89,12 +101,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int i = 0; i < PT_KV_STAGES; ++i) { mbar_init(kv_full + i, 1); mbar_init(kv_empty + i, 1); }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(s_full + i, 1);
-            mbar_init(s_empty + i, 4);
-            mbar_init(p_full + i, 4);
-            mbar_init(o_full + i, 1);
-        }
+        mbar_init(s_full, 1);
+        mbar_init(p_full, 8);
+        mbar_init(o_full, 1);
+        for (int i = 0; i < 4; ++i) mbar_init(pair + i, 2);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -129,90 +139,92 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (lane == 0) {
             const uint64_t qdesc = make_kmajor_sw128_desc(smem_u32(q_tile));
             // S_j = Q K_j^T : four K steps of 16 dims, +32 bytes inside the swizzle row each
-            auto issue_s = [&](uint32_t j, uint32_t stage) {
+            auto issue_s = [&](uint32_t stage) {
                 const uint64_t kdesc = make_kmajor_sw128_desc(smem_u32(kv_ring + stage * PT_KV_BYTES));
-                const uint32_t d_tmem = tmem_base + (j & 1) * PT_BK;
 #pragma unroll
-                for (uint32_t kk = 0; kk < PT_HD / 16; ++kk) umma_bf16(d_tmem, qdesc + kk * 2, kdesc + kk * 2, PT_IDESC_S, kk != 0);
-                umma_commit(s_full + (j & 1));
+                for (uint32_t kk = 0; kk < PT_HD / 16; ++kk) umma_bf16(tmem_base, qdesc + kk * 2, kdesc + kk * 2, PT_IDESC_S, kk != 0);
+                umma_commit(s_full);
             };
             bool ok = mbar_wait(q_full, 0, abort_flag);
-            uint32_t s_stage = 0, s_phase = 0;   // ring position of the next K block to multiply
-            uint32_t o_stage = 0;                // ring position of the next V block to multiply
             if (ok) ok = mbar_wait(kv_full + 0, 0, abort_flag);
             if (ok) {
                 tc_fence_after();
-                issue_s(0, 0);
-                if (++s_stage == PT_KV_STAGES) { s_stage = 0; s_phase ^= 1; }
+                issue_s(0);
             }
             for (uint32_t j = 0; ok && j < n_blocks; ++j) {
+                const uint32_t stage = j % PT_KV_STAGES;
+                // P_j is in place and the softmax warps are done with S_j
+                if (!mbar_wait(p_full, j & 1, abort_flag)) { ok = false; break; }
                 if (j + 1 < n_blocks) {
-                    if (!mbar_wait(kv_full + s_stage, s_phase, abort_flag)) { ok = false; break; }
-                    // score buffer (j + 1) % 2 was last used by block j - 1
-                    if (j >= 1 && !mbar_wait(s_empty + ((j + 1) & 1), ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                    const uint32_t next = (j + 1) % PT_KV_STAGES;
+                    if (!mbar_wait(kv_full + next, ((j + 1) / PT_KV_STAGES) & 1, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    issue_s(j + 1, s_stage);
-                    if (++s_stage == PT_KV_STAGES) { s_stage = 0; s_phase ^= 1; }
+                    issue_s(next);
                 }
-                if (!mbar_wait(p_full + (j & 1), (j >> 1) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                // O_j = P_j V_j : eight K steps of 16 keys.  P: two K-major sub-tiles of 64 keys; V: MN-major,
-                // 16 keys = two 8-key groups 1024 bytes apart, so each step starts 2048 bytes further on.
-                const uint32_t p_addr = smem_u32(p_tiles + (j & 1) * PT_P_BYTES);
-                const uint32_t v_addr = smem_u32(kv_ring + o_stage * PT_KV_BYTES + PT_TILE_BYTES);
-                const uint32_t d_tmem = tmem_base + PT_O_COL + (j & 1) * PT_HD;
+                // O_j = P_j V_j : eight K steps of 16 keys.  P: K-major, keys 0-63 in the K slot of this stage, keys
+                // 64-127 in the upper tile; V: MN-major, 16 keys = two 8-key groups 1024 bytes apart, so each step
+                // starts 2048 bytes further on.
+                const uint32_t p_lower = smem_u32(kv_ring + stage * PT_KV_BYTES);
+                const uint32_t v_addr = p_lower + PT_TILE_BYTES;
 #pragma unroll
                 for (uint32_t kk = 0; kk < PT_BK / 16; ++kk) {
-                    const uint64_t pdesc = make_kmajor_sw128_desc(p_addr + (kk >> 2) * PT_TILE_BYTES) + (kk & 3) * 2;
+                    const uint64_t pdesc = make_kmajor_sw128_desc(kk < 4 ? p_lower : smem_u32(p_upper)) + (kk & 3) * 2;
                     const uint64_t vdesc = make_mnmajor_sw128_desc(v_addr + kk * 2048, PT_TILE_BYTES, 1024);
-                    umma_bf16(d_tmem, pdesc, vdesc, PT_IDESC_O, kk != 0);
+                    umma_bf16(tmem_base + PT_O_COL, pdesc, vdesc, PT_IDESC_O, kk != 0);
                 }
-                umma_commit(o_full + (j & 1));
-                umma_commit(kv_empty + o_stage);   // both products of this ring stage are done
-                if (++o_stage == PT_KV_STAGES) o_stage = 0;
+                umma_commit(o_full);
+                umma_commit(kv_empty + stage);   // both products of this ring stage are done
             }
         }
     } else {
-        // ---------------- softmax warps: one query row per thread ----------------
-        const uint32_t quarter = warp & 3;
+        // ---------------- softmax warps: two threads per query row ----------------
+        const uint32_t quarter = warp & 3, half = (warp - 2) >> 2;
         const uint32_t row = quarter * 32 + lane;
         const uint32_t q_idx = min(q0 + row, prm.chunk - 1);
         const uint32_t limit = prm.position + q_idx;             // last visible key of this row
         const uint32_t lane_taddr = tmem_base + ((quarter * 32u) << 16);
         const float sl2 = prm.scale_log2;
-        float acc[PT_HD];
+        float acc[32];                                           // output columns [32 half, 32 half + 32)
 #pragma unroll
-        for (int i = 0; i < PT_HD; ++i) acc[i] = 0.0f;
-        float m = -INFINITY, l = 0.0f, corr_pending = 0.0f;
+        for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
+        float m = -INFINITY, l = 0.0f, corr_pending = 0.0f;      // l: sum over this thread's key columns only
         bool ok = true;
+        uint32_t pair_uses = 0;
 
-        // acc = acc * corr + O_b  (O_b: this row's 64 outputs of block b)
+        // Both threads of a row publish a value and read the partner's.
+        auto exchange = [&](float mine, float& other) -> bool {
+            float* slot = xm + (pair_uses & 1) * 256;
+            slot[half * 128 + row] = mine;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(pair + quarter);
+            if (!mbar_wait(pair + quarter, pair_uses & 1, abort_flag)) return false;
+            other = slot[(half ^ 1) * 128 + row];
+            ++pair_uses;
+            return true;
+        };
+        // acc = acc * corr + O_b  (this thread's 32 outputs of block b)
         auto fold = [&](uint32_t b, float corr) -> bool {
-            if (!mbar_wait(o_full + (b & 1), (b >> 1) & 1, abort_flag)) return false;
+            if (!mbar_wait(o_full, b & 1, abort_flag)) return false;
             tc_fence_after();
-            const uint32_t taddr = lane_taddr + PT_O_COL + (b & 1) * PT_HD;
+            float v[32];
+            tmem_ld32(lane_taddr + PT_O_COL + half * 32, v);
+            tmem_ld_wait();
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                float v[32];
-                tmem_ld32(taddr + c * 32, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], corr, v[i]);
-            }
+            for (int i = 0; i < 32; ++i) acc[i] = fmaf(acc[i], corr, v[i]);
             return true;
         };
 
         for (uint32_t j = 0; j < n_blocks; ++j) {
-            const uint32_t sb = j & 1;
-            if (!mbar_wait(s_full + sb, (j >> 1) & 1, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(s_full, j & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t taddr = lane_taddr + sb * PT_BK;
-            const uint32_t kbase = j * PT_BK;
-            const bool need_mask = kbase + PT_BK - 1 > limit;
-            // pass 1: row maximum of the raw scores
-            float mx = m;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            const uint32_t taddr = lane_taddr + half * 64;
+            const uint32_t kbase = j * PT_BK + half * 64;           // first key of this thread's columns
+            const bool need_mask = kbase + 63 > limit;
+            // pass 1: maximum of the raw scores of the own 64 columns (four independent chains)
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
                 float v[32];
                 tmem_ld32(taddr + c * 32, v);
                 tmem_ld_wait();
@@ -221,18 +233,24 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     for (int i = 0; i < 32; ++i) if (kbase + c * 32 + i > limit) v[i] = -INFINITY;
                 }
 #pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+                for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
             }
+            float mx = pt_max4(mx4), other;
+            if (!exchange(mx, other)) { ok = false; break; }
+            mx = fmaxf(m, fmaxf(mx, other));
             const float ms = (mx == -INFINITY) ? 0.0f : mx;
             const float corr = pt_ex2((m - ms) * sl2);      // 0 for the first block
             m = mx;
             const float neg = -ms * sl2;
-            // pass 2: p = exp2(s * scale - m * scale), bf16, into the P tile (row = 128 bytes per 64 keys,
-            // 16-byte chunk c of row r at c ^ (r & 7))
-            uint8_t* p_row = p_tiles + sb * PT_P_BYTES + row * 128u;
-            float rs = 0.0f;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            // the previous block's output; once it is complete the upper P tile may be overwritten
+            if (j > 0 && !fold(j - 1, corr_pending)) { ok = false; break; }
+            corr_pending = corr;
+            // pass 2: p = exp2(s * scale - m * scale) as bf16 into this thread's 128-byte row of the P tile
+            // (16-byte chunk c of row r at c ^ (r & 7))
+            uint8_t* p_row = (half ? p_upper : kv_ring + (j % PT_KV_STAGES) * PT_KV_BYTES) + row * 128u;
+            float rs4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
                 float v[32];
                 tmem_ld32(taddr + c * 32, v);
                 tmem_ld_wait();
@@ -244,35 +262,31 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const float p0 = pt_ex2(fmaf(v[2 * i], sl2, neg)), p1 = pt_ex2(fmaf(v[2 * i + 1], sl2, neg));
-                    rs += p0 + p1;
+                    rs4[i & 3] += p0 + p1;
                     packed[i] = pack_bf16x2(p0, p1);
                 }
-                uint8_t* sub = p_row + (c >> 1) * PT_TILE_BYTES;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const uint32_t chunk16 = (uint32_t)((c & 1) * 4 + i);
-                    *reinterpret_cast<uint4*>(sub + (((chunk16 ^ row) & 7u) << 4)) =
+                    const uint32_t chunk16 = (uint32_t)(c * 4 + i);
+                    *reinterpret_cast<uint4*>(p_row + (((chunk16 ^ row) & 7u) << 4)) =
                         make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
                 }
             }
-            l = l * corr + rs;
-            // scores consumed: the buffer may take S_{j+2}; P written: visible to the tensor core, then signal
+            l = l * corr + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
+            // scores consumed: the buffer may take S_{j+1}; P written: visible to the tensor core, then signal
             tc_fence_before();
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(s_empty + sb);
-                mbar_arrive(p_full + sb);
-            }
-            if (j > 0 && !fold(j - 1, corr_pending)) { ok = false; break; }
-            corr_pending = corr;
+            if (lane == 0) mbar_arrive(p_full);
         }
         if (ok && n_blocks > 0) ok = fold(n_blocks - 1, corr_pending);
+        float l_other = 0.0f;
+        if (ok) ok = exchange(l, l_other);
         if (ok && q0 + row < prm.chunk) {
-            const float inv = 1.0f / l;
-            bf16* og = prm.out + ((size_t)s * prm.chunk + q0 + row) * ((size_t)prm.heads * PT_HD) + (size_t)h * PT_HD;
+            const float inv = 1.0f / (l + l_other);
+            bf16* og = prm.out + ((size_t)s * prm.chunk + q0 + row) * ((size_t)prm.heads * PT_HD) + (size_t)h * PT_HD + half * 32;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < 4; ++i) {
                 uint4 w;
                 w.x = pack_bf16x2(acc[8 * i] * inv, acc[8 * i + 1] * inv);
                 w.y = pack_bf16x2(acc[8 * i + 2] * inv, acc[8 * i + 3] * inv);
@@ -340,7 +354,9 @@ int launch_prefill_attention_tc(const bf16* q, const bf16* k_cache, const bf16* 
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        if (cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PT_SMEM_BYTES) != cudaSuccess)
+        if (cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PT_SMEM_BYTES) != cudaSuccess ||
+            cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 (int)cudaSharedmemCarveoutMaxShared) != cudaSuccess)
             return check_launch("prefill_attention_tc attribute");
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
