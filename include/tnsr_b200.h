@@ -113,7 +113,9 @@ TNSR_B200_API const char* tnsr_b200_last_error(const tnsr_b200_decoder* dec);
 TNSR_B200_API uint64_t tnsr_b200_kernel_launches(void);
 /* GEMM engine of the bf16 path: 0 = tcgen05/TMEM kernel where the shape
  * allows it, else the CUDA-core kernel (default); 1 = always the CUDA-core
- * kernel; 2 = tcgen05 only (unsupported shapes fail).  Process-wide. */
+ * kernel; 2 = tcgen05 only (unsupported shapes fail).  Process-wide.  Engine 1
+ * also keeps prefill attention off tcgen05 (the warp-level mma.sync kernel
+ * runs), which is how tests compare the two. */
 TNSR_B200_API int tnsr_b200_set_gemm_engine(int engine);
 
 /* ---- session: replaces cuda::CudaDecoder -------------------------------- */
@@ -299,7 +301,9 @@ TNSR_B200_API int tnsr_b200_decode_attention_static(const void* q, const void* k
 /* Causal attention of `chunk` new queries per session over `position + chunk`
  * cached keys (the new rows are already in the cache), the job of the tiled
  * prefill (src/nn/kv_cache/prefill.rs:170-607).  q, out: [batch, chunk, width]
- * bf16; caches as above. */
+ * bf16; caches as above.  Head width 64 with at least 32 new rows runs on the
+ * tcgen05 kernel (scores and outputs in TMEM); other shapes on the warp-level
+ * tensor-core kernel (head width 64) or the generic one. */
 TNSR_B200_API int tnsr_b200_prefill_attention(const void* q, const void* k_cache, const void* v_cache,
                                               void* out, uint32_t batch, uint32_t chunk,
                                               uint32_t position, uint32_t capacity, uint32_t heads,
