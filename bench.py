@@ -40,10 +40,11 @@ DECODE_STEPS = 256
 FALLBACK_HBM_GBS = 6650.0
 
 # Per-launch DRAM traffic of decode_attention_kernel relative to its algorithmic
-# bytes, from the ncu capture summarised in profiles/decode_attention_c4_small.md
-# (dram__bytes_read.sum + dram__bytes_write.sum of a smaller launch; traffic
-# grows in proportion to the live keys, so it is scaled by that ratio).
-NCU_TRAFFIC_RATIO = 1.033
+# bytes, from the ncu capture summarised in profiles/decode_attention_c4_full_size.md
+# (dram__bytes_read.sum + dram__bytes_write.sum = 509.48 MB for 504.89 MB of live K/V
+# rows and q/out at 256 sessions x 641 live keys, the mean length of the timed steps;
+# traffic grows in proportion to the live keys, so the ratio is applied to every step).
+NCU_TRAFFIC_RATIO = 1.009
 
 
 def parse_args():

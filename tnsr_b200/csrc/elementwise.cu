@@ -250,9 +250,31 @@ argmax_kernel(const float* __restrict__ logits, uint32_t* __restrict__ out, uint
     int best = INT_MIN;
     uint32_t best_i = 0;
     bool have = false;
-    for (uint32_t i = threadIdx.x; i < vocab; i += blockDim.x) {
-        int key = total_order_key(row[i]);
+    auto take = [&](float v, uint32_t i) {
+        const int key = total_order_key(v);
         if (!have || key >= best) { best = key; best_i = i; have = true; }
+    };
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0 && vocab % 4 == 0) {
+        // 16-byte loads, four in flight per thread before the first compare
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        const uint32_t n4 = vocab >> 2, step = blockDim.x;
+        uint32_t i = threadIdx.x;
+        for (; i + 3 * step < n4; i += 4 * step) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = __ldcs(row4 + i + u * step);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t base = (i + u * step) << 2;
+                take(v[u].x, base); take(v[u].y, base + 1); take(v[u].z, base + 2); take(v[u].w, base + 3);
+            }
+        }
+        for (; i < n4; i += step) {
+            const float4 v = __ldcs(row4 + i);
+            take(v.x, 4 * i); take(v.y, 4 * i + 1); take(v.z, 4 * i + 2); take(v.w, 4 * i + 3);
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < vocab; i += blockDim.x) take(row[i], i);
     }
     // per-thread scan visits indices in increasing order, so >= keeps the last; merge likewise
 #pragma unroll

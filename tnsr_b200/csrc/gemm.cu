@@ -239,9 +239,32 @@ __device__ __forceinline__ float4 act4(float4 v, int act) {
     return make_float4(apply_activation(v.x, act), apply_activation(v.y, act), apply_activation(v.z, act), apply_activation(v.w, act));
 }
 
+// True when the f32 epilogue of this block takes its 16-byte path (whole block inside the matrix, aligned
+// pointers and leading dimensions).
+__device__ __forceinline__ bool f32_vector_path(const EpiParams& P, uint32_t col0) {
+    const float* res = P.ep.residual;
+    return col0 + 32 <= P.n && (reinterpret_cast<uintptr_t>(P.ep.bias) & 15) == 0 && P.ldc % 4 == 0 &&
+           (reinterpret_cast<uintptr_t>(P.out) & 15) == 0 &&
+           (!res || (P.ep.ldr % 4 == 0 && (reinterpret_cast<uintptr_t>(res) & 15) == 0));
+}
+
+// Residual values of this lane for the 16-byte f32 path: rows (it * 4 + lane / 8), columns 4 * (lane % 8) .. + 3.
+__device__ __forceinline__ void load_residual_block(const EpiParams& P, uint32_t row0, uint32_t col0, uint32_t lane, float4* r4) {
+    const float* res = P.ep.residual;
+    const uint32_t c4 = 4 * (lane & 7), rsub = lane >> 3;
+    const uint32_t rows = row0 < P.m ? min(32u, P.m - row0) : 0u;
+#pragma unroll
+    for (uint32_t it = 0; it < 8; ++it) {
+        const uint32_t rr = it * 4 + rsub;
+        r4[it] = (res && rr < rows) ? *reinterpret_cast<const float4*>(res + (size_t)(row0 + rr) * P.ep.ldr + col0 + c4)
+                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+}
+
+// `pre` (optional): residual values already fetched with load_residual_block for this very block.
 template <int MODE>
 __device__ __forceinline__ void epilogue_block(const EpiParams& P, float* stage, uint32_t row0, uint32_t col0,
-                                               const float* acc, uint32_t lane) {
+                                               const float* acc, uint32_t lane, const float4* pre = nullptr) {
     if (row0 >= P.m || col0 >= P.n) return;  // warp-uniform
 #pragma unroll
     for (int g = 0; g < 8; ++g)
@@ -331,14 +354,13 @@ __device__ __forceinline__ void epilogue_block(const EpiParams& P, float* stage,
         float* out = reinterpret_cast<float*>(P.out);
         const float* res = P.ep.residual;
         const uint32_t c4 = 4 * (lane & 7), rsub = lane >> 3;
-        if (full_cols && P.ldc % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
-            (!res || (P.ep.ldr % 4 == 0 && (reinterpret_cast<uintptr_t>(res) & 15) == 0))) {
+        if (f32_vector_path(P, col0)) {
             float4 r4[8];
+            if (pre) {
 #pragma unroll
-            for (uint32_t it = 0; it < 8; ++it) {
-                const uint32_t rr = it * 4 + rsub;
-                r4[it] = (res && rr < rows) ? *reinterpret_cast<const float4*>(res + (size_t)(row0 + rr) * P.ep.ldr + col0 + c4)
-                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (uint32_t it = 0; it < 8; ++it) r4[it] = pre[it];
+            } else {
+                load_residual_block(P, row0, col0, lane, r4);
             }
             float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
             if (P.ep.bias) bv = __ldg(reinterpret_cast<const float4*>(P.ep.bias + col0 + c4));
@@ -465,9 +487,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t ab = it & 1, aphase = (it >> 1) & 1;
             uint32_t tm, tn;
             tile_coords(tile, prm.tiles_m, prm.tiles_n, tm, tn);
+            const uint32_t row0 = tm * BM + quarter * 32;
+            // f32 output with a residual: fetch this warp's first block of residual rows while the tile is still
+            // being accumulated (the rows are final: only this warp rewrites them, after this read)
+            float4 res_pre[8];
+            bool have_pre = false;
+            if (MODE == GEMM_PLAIN && prm.epi.ep.out_dtype == TNSR_B200_F32 && prm.epi.ep.residual && half * 32 < BN) {
+                const uint32_t col0 = tn * BN + half * 32;
+                if (row0 < prm.epi.m && col0 < prm.epi.n && f32_vector_path(prm.epi, col0)) {
+                    load_residual_block(prm.epi, row0, col0, lane, res_pre);
+                    have_pre = true;
+                }
+            }
             if (!mbar_wait(acc_full + ab, aphase, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t row0 = tm * BM + quarter * 32;
             const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + ab * BN;
             if (MODE == GEMM_ARGMAX) {
                 // no matrix leaves the kernel: every lane scans its own row; the first warp of the quarter does all chunks
@@ -496,7 +529,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     float acc[32];
                     tmem_ld32(taddr + c, acc);
                     tmem_ld_wait();
-                    epilogue_block<MODE>(prm.epi, stage, row0, tn * BN + c, acc, lane);
+                    epilogue_block<MODE>(prm.epi, stage, row0, tn * BN + c, acc, lane, (have_pre && c == half * 32) ? res_pre : nullptr);
                 }
             }
             tc_fence_before();
