@@ -5,9 +5,13 @@
 
 Workload ("c4"): the serving configuration -- 12 layers, d_model 768, 12 heads x
 64, SwiGLU 2048, vocab 32000, bf16 weights N(0, 0.02) seed 5; 256 independent
-sessions sharded 256/N over the GPUs, each a 512-token prefill of uniform random
-ids followed by greedy decode steps.  A benchmark "step" is one decode step: one
-new token for every session of the rank.  The timed region is K steps starting
+sessions, each a 512-token prefill of uniform random ids followed by greedy
+decode steps.  Sessions are independent, so N GPUs hold disjoint shards and no
+collective runs on the data path.  With the default `--scaling weak` every GPU
+holds the configuration's 256 sessions (256 N in total: the per-GPU work is the
+1-GPU workload whatever N is); `--scaling strong` divides the same 256 sessions
+256/N per GPU, which is how the configuration words it.  A benchmark "step" is
+one decode step: one new token for every session of the rank.  The timed region is K steps starting
 at position 512 (the default K = 256 is the configuration's decode length), with
 token ids living on the device; `value` is total tokens/s over all ranks, timed
 with CUDA events on the session's stream, max over ranks.  `e2e` repeats the K
@@ -53,7 +57,10 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=DECODE_STEPS)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--sessions", type=int, default=TOTAL_SESSIONS, help="total sessions over all GPUs")
+    ap.add_argument("--sessions", type=int, default=TOTAL_SESSIONS,
+                    help="sessions per GPU (weak scaling) or in total (strong scaling)")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: every GPU holds --sessions sessions; strong: --sessions are divided over the GPUs")
     ap.add_argument("--prefill", type=int, default=PREFILL)
     ap.add_argument("--layers", type=int, default=12)
     ap.add_argument("--vocab", type=int, default=32000)
@@ -188,7 +195,7 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": "decode_tokens_per_s", "value": r["tokens_per_s"], "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": r["steps"], "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args, args.gpus),
         "cpu_baseline": {"value": r["tokens_per_s"], "unit": "tokens/s", "cores": r["threads"], "kind": "port",
                          "sample": sample},
@@ -198,12 +205,18 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def sessions_per_gpu(args, n_gpus):
+    return args.sessions if args.scaling == "weak" else args.sessions // n_gpus
+
+
 def workload_config(args, n_gpus):
+    per_gpu = sessions_per_gpu(args, n_gpus)
     return {
         "workload": "c4: GPT 12x768 (12 heads x 64, SwiGLU 2048, vocab 32000, ctx 2048), "
-                    f"{args.sessions} sessions x ({args.prefill}-token prefill + greedy decode), 1 token/session/step",
-        "sessions_total": args.sessions, "sessions_per_gpu": args.sessions // n_gpus, "prefill": args.prefill,
-        "layers": args.layers, "vocab": args.vocab, "parallelism": f"sessions sharded over {n_gpus} GPU(s), no collective",
+                    f"{per_gpu} sessions per GPU x ({args.prefill}-token prefill + greedy decode), 1 token/session/step",
+        "sessions_total": per_gpu * n_gpus, "sessions_per_gpu": per_gpu, "prefill": args.prefill,
+        "layers": args.layers, "vocab": args.vocab,
+        "parallelism": f"independent sessions on {n_gpus} GPU(s), {args.scaling} scaling, no collective",
         "l2": "inputs larger than L2: each step streams the live K/V rows (GBs) and 222 MB of weights",
     }
 
@@ -234,7 +247,7 @@ def run_b200(args):
         torch.cuda.synchronize()
 
     cfg = serving_config(args)
-    sessions = args.sessions // world
+    sessions = sessions_per_gpu(args, world)
     K, W = args.steps, args.warmup
     capacity = min(cfg.max_sequence_length, args.prefill + max(K, W) + 1)
     lib = _native.lib()
@@ -367,7 +380,7 @@ def run_b200(args):
         prefill_tokens = total_sessions * args.prefill
         line = {
             "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": elapsed_ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "ms_per_step": elapsed_ms / K, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "config": workload_config(args, world),
             "roofline": roofline,
             "gpu_launches": total_launches,
