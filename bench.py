@@ -18,6 +18,10 @@ with CUDA events on the session's stream, max over ranks.  `e2e` repeats the K
 steps through the host API (`tnsr_b200_decoder_decode`): ids go up from host
 memory and greedy ids come back every step.
 
+`--workload c0|c1|c2|c3` measures the smaller configurations on one GPU (the f32
+4-layer model end to end, the GEMM sweep, the SwiGLU MLP, ragged decode attention),
+each with the CPU restatement timed beside it on a stated sample.
+
 The CPU arm times this repository's restatement of the reference's CPU executor
 (oracle/) on the host cores: the reference is Rust and cannot be built here.
 """
@@ -64,6 +68,11 @@ def parse_args():
     ap.add_argument("--prefill", type=int, default=PREFILL)
     ap.add_argument("--layers", type=int, default=12)
     ap.add_argument("--vocab", type=int, default=32000)
+    ap.add_argument("--workload", default="c4", choices=["c4", "c0", "c1", "c2", "c3"],
+                    help="c4 (default): the serving decode benchmark; c0: the 4-layer d128 f32 model, 16-token prompt + 64 "
+                         "greedy steps; c1: GEMM sweep; c2: SwiGLU MLP; c3: ragged decode attention -- each with the CPU "
+                         "restatement timed beside it (1 GPU)")
+    ap.add_argument("--samples", type=int, default=20, help="timed launches per case of the operator workloads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -219,6 +228,154 @@ def workload_config(args, n_gpus):
         "parallelism": f"independent sessions on {n_gpus} GPU(s), {args.scaling} scaling, no collective",
         "l2": "inputs larger than L2: each step streams the live K/V rows (GBs) and 222 MB of weights",
     }
+
+
+# ---------------------------------------------------------------------------
+# the smaller configurations: this library on one GPU, the CPU restatement beside it
+# ---------------------------------------------------------------------------
+def _timed_cpu(fn, repeats=1):
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        fn()
+        best = min(best, time.perf_counter() - t0)
+    return best
+
+
+def _op_line(args, metric, unit, value, ms, dtype, workload, roofline, cpu_baseline, cases, launches, clocks):
+    return {"metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": args.samples, "warmup": 3,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": dtype,
+            "data": "synthetic", "config": {"workload": workload, "l2": "operands rotate through copies larger than L2 "
+                                            "or exceed it by themselves"},
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": None, "gpu_launches": launches, "clocks": clocks,
+            "cases": cases}
+
+
+def run_ops(args):
+    """Configurations 0-3 on one GPU.  The GPU side is tnsr_b200.opbench (operator calls through the C ABI, CUDA events)
+    or, for c0, the session API; the CPU side is the restatement in oracle/ on a stated sample."""
+    import torch
+    from tnsr_b200 import _native, opbench
+    from oracle import oracle
+    torch.cuda.set_device(0)
+    opbench.QUIET = True
+    hbm, tf, kind = opbench.peaks()
+    lib = _native.lib()
+    threads = oracle.max_threads()
+    oracle.set_threads(threads)
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches0 = lib.tnsr_b200_kernel_launches()
+    rng = np.random.default_rng(2)
+    if args.workload == "c0":
+        from tests.helpers import cpu_decoder
+        from tests.workloads import config0_model, config0_prompt, set_model_arrays
+        from tnsr_b200 import Backend, Gpt
+        from tnsr_b200.nn import argmax_last
+        cfg, arrays = config0_model("relu")
+        model = Gpt(cfg)
+        set_model_arrays(model, arrays)
+        prompt = [int(t) for t in config0_prompt()]
+
+        def greedy(decoder):
+            """reset, 16-token prefill, 64 cached greedy steps: (ids, prefill seconds, decode seconds)"""
+            decoder.reset()
+            t0 = time.perf_counter()
+            logits = decoder.decode(prompt)
+            t1 = time.perf_counter()
+            ids = []
+            for _ in range(64):
+                ids.append(argmax_last(logits[logits.size - cfg.vocab_size:]))
+                logits = decoder.decode([ids[-1]])
+            return ids, t1 - t0, time.perf_counter() - t1
+
+        gpu_dec = model.decoder(Backend.Cuda, 1)
+        greedy(gpu_dec)                                           # first use: allocations, graph capture
+        runs = [greedy(gpu_dec) for _ in range(max(5, args.samples // 2))]
+        got = runs[-1][0]
+        gpu_prefill_s, gpu_s = float(np.median([r[1] for r in runs])), float(np.median([r[2] for r in runs]))
+        cpu_dec = cpu_decoder(model, 1)
+        greedy(cpu_dec)
+        cpu_runs = [greedy(cpu_dec) for _ in range(3)]
+        want = cpu_runs[-1][0]
+        cpu_prefill_s, cpu_s = float(np.median([r[1] for r in cpu_runs])), float(np.median([r[2] for r in cpu_runs]))
+        same = want == got
+        weight_bytes = 4.0 * sum(int(np.asarray(a).size) for a in arrays)
+        value = 64 / gpu_s
+        roof = {"bound": "hbm", "achieved": weight_bytes * 64 / gpu_s / 1e9, "peak": hbm, "unit": "GB/s",
+                "frac": weight_bytes * 64 / gpu_s / 1e9 / hbm, "traffic": None,
+                "note": "latency-bound: 3.3 MB of f32 weights per step, kernels that keep the reference's operation order, "
+                        "one host round trip per token (logits returned every step as the reference's decode does)"}
+        cpu = {"value": 64 / cpu_s, "unit": "tokens/s", "cores": 1, "kind": "port",
+               "sample": "the whole configuration: 16-token prefill (%.2f ms) + 64 cached greedy steps, batch 1, one thread, "
+                         "same GptDecoder wrapper over the CPU restatement" % (cpu_prefill_s * 1e3)}
+        line = _op_line(args, "decode_tokens_per_s", "tokens/s", value, gpu_s * 1e3 / 64, "f32",
+                        "c0: GPT 4x128 (4 heads x 32, ReLU FFN 512, vocab 96, ctx 128), f32, batch 1, 16-token prompt then 64 cached "
+                        "greedy steps through GptDecoder.decode (steps timed; prefill reported in cases)", roof, cpu,
+                        [{"greedy_ids_equal_to_cpu": same, "us_per_token_gpu": gpu_s * 1e6 / 64, "us_per_token_cpu": cpu_s * 1e6 / 64,
+                          "prefill_ms_gpu": gpu_prefill_s * 1e3, "prefill_ms_cpu": cpu_prefill_s * 1e3}],
+                        0, None)
+        line["e2e"] = {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4 * cfg.vocab_size}
+    elif args.workload == "c1":
+        opbench.bench_gemm(args.samples)
+        cases = list(opbench.RESULTS)
+        top = max((c for c in cases if c["m"] == 8192 and c["out"] == "bf16"), key=lambda c: c["tflops"])
+        a = (rng.random((1024, 1024), dtype=np.float32) * 2 - 1)
+        b = (rng.random((1024, 1024), dtype=np.float32) * 2 - 1)
+        cpu_s = _timed_cpu(lambda: oracle.matmul_bf16(a, b))
+        w = (rng.random((4096, 4096), dtype=np.float32) * 2 - 1)
+        skinny = {}
+        for m in (1, 8, 64):
+            x = (rng.random((m, 4096), dtype=np.float32) * 2 - 1)
+            skinny[m] = _timed_cpu(lambda: oracle.matmul_bf16(x, w))
+        roof = {"bound": "tensor", "achieved": top["tflops"], "peak": tf, "unit": "TFLOP/s", "frac": top["tflops"] / tf,
+                "traffic": None, "kernel": "gemm_tc_kernel<256,0>, 8192^3, bf16 out"}
+        cpu = {"value": 2.0 * 1024 ** 3 / cpu_s / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+               "sample": "1024^3 in %.2f s; skinny M=1/8/64 x 4096 x 4096 in %.3f / %.3f / %.3f s (reference operation order, "
+                         "bf16-rounded operands, f32 accumulation); 8192^3 would take about %.0f s" %
+                         (cpu_s, skinny[1], skinny[8], skinny[64], cpu_s * 512)}
+        line = _op_line(args, "gemm_tflops", "TFLOP/s", top["tflops"], top["ms"], "bf16",
+                        "c1: bf16 GEMM sweep M=N=K in {1024,2048,4096,8192} + skinny M in {1,8,64} x 4096 x 4096, bf16 and f32 out; "
+                        "value = 8192^3 with bf16 output", roof, cpu, cases, 0, None)
+    elif args.workload == "c2":
+        opbench.bench_mlp(args.samples)
+        r = opbench.RESULTS[-1]
+        rows, d, f = 16, 2048, 5632
+        x = rng.standard_normal((rows, d)).astype(np.float32)
+        wg = (rng.standard_normal((d, f)) * 0.02).astype(np.float32)
+        wu = (rng.standard_normal((d, f)) * 0.02).astype(np.float32)
+        wd = (rng.standard_normal((f, d)) * 0.02).astype(np.float32)
+        zf, zd = np.zeros(f, np.float32), np.zeros(d, np.float32)
+        cpu_s = _timed_cpu(lambda: oracle.swiglu_mlp(x, wg, zf, wu, zf, wd, zd))
+        roof = {"bound": "tensor", "achieved": r["tflops"], "peak": tf, "unit": "TFLOP/s", "frac": r["tflops"] / tf,
+                "traffic": None, "kernel": "gemm_tc_kernel (gate/up + SwiGLU epilogue, then down)"}
+        cpu = {"value": 3 * 2.0 * rows * d * f / cpu_s / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+               "sample": "%d of the 4096 rows in %.2f s (f32, reference operation order); the whole block would take about %.0f s"
+                         % (rows, cpu_s, cpu_s * 4096 / rows)}
+        line = _op_line(args, "swiglu_mlp_tflops", "TFLOP/s", r["tflops"], r["ms"], "bf16",
+                        "c2: fused SwiGLU MLP, x [4096, 2048] -> 5632 -> 2048, bf16", roof, cpu, [r], 0, None)
+    else:
+        opbench.bench_attention(args.samples)
+        r = opbench.RESULTS[-1]
+        batch, heads, hd, capacity = 16, 16, 64, 4096
+        d = heads * hd
+        lengths = np.random.default_rng(4).integers(1, capacity + 1, size=64).astype(np.uint32)[:batch]
+        q = oracle.bf16_round_np(rng.standard_normal((batch, d)).astype(np.float32))
+        kc = oracle.bf16_round_np(rng.standard_normal((batch, capacity, d)).astype(np.float32))
+        vc = oracle.bf16_round_np(rng.standard_normal((batch, capacity, d)).astype(np.float32))
+        cpu_s = _timed_cpu(lambda: oracle.decode_attention(q, kc, vc, lengths, heads))
+        cpu_bytes = float(lengths.astype(np.int64).sum()) * 4 * d
+        roof = {"bound": "hbm", "achieved": r["gbs"], "peak": hbm, "unit": "GB/s", "frac": r["gbs"] / hbm,
+                "traffic": r["algorithmic_bytes"] * NCU_TRAFFIC_RATIO, "kernel": "da_plan_kernel + decode_attention_kernel<64,1> per call"}
+        cpu = {"value": cpu_bytes / cpu_s / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+               "sample": "the first 16 of the 64 sessions (%.0f MB of bf16 K/V, counted as on the GPU) in %.3f s" % (cpu_bytes / 1e6, cpu_s)}
+        line = _op_line(args, "kv_attention_gbs", "GB/s", r["gbs"], r["ms"], "bf16",
+                        "c3: decode attention, 64 sessions x 16 heads x 64, bf16 cache of capacity 4096, live lengths uniform [1, 4096] "
+                        "(seed 4)", roof, cpu, [r], 0, None)
+    line["gpu_launches"] = int(lib.tnsr_b200_kernel_launches() - launches0)
+    line["clocks"] = sampler.stop()
+    line["roofline"]["peak_source"] = kind
+    print(json.dumps(line), flush=True)
 
 
 # ---------------------------------------------------------------------------
@@ -412,6 +569,9 @@ def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "c4":
+        if int(os.environ.get("RANK", "0")) == 0:
+            run_ops(args)
     else:
         run_b200(args)
 

@@ -300,6 +300,41 @@ def test_graph_replay_of_single_token_steps_matches_direct_launches(monkeypatch)
         assert np.array_equal(x.view(np.uint32), y.view(np.uint32))
 
 
+@pytest.mark.parametrize("kv_bf16", [False, True])
+def test_graph_replay_on_the_strict_f32_path_matches_direct_launches(monkeypatch, kv_bf16):
+    """The strict path replays single-token steps from a graph too; logits must be bit-identical to direct launches and,
+    as everywhere on this path, the greedy ids must equal the CPU checker's."""
+    from tests.workloads import config0_model, config0_prompt
+    cfg, arrays = config0_model("relu")
+    prompt = config0_prompt().reshape(1, -1)
+    steps = 20
+
+    def run(no_graph):
+        if no_graph:
+            monkeypatch.setenv("TNSR_B200_NO_GRAPH", "1")
+        else:
+            monkeypatch.delenv("TNSR_B200_NO_GRAPH", raising=False)
+        s = B200Session(cfg, 1, cfg.max_sequence_length, options=GptDecoderOptions(
+            attention_precision=GptAttentionPrecision.Bf16 if kv_bf16 else GptAttentionPrecision.F32))
+        for i, a in enumerate(arrays):
+            s.refresh(i, a)
+        logits, ids = s.decode_full(prompt, 0)
+        trace, tokens = [logits.copy()], [int(ids[0])]
+        for step in range(steps):
+            logits, ids = s.decode_full(ids.reshape(1, 1), prompt.shape[1] + step)
+            trace.append(logits.copy())
+            tokens.append(int(ids[0]))
+        logits, _ = s.decode_full(prompt[:, :1], prompt.shape[1] + 3)     # jump back
+        trace.append(logits.copy())
+        s.close()
+        return trace, tokens
+
+    (a, ta), (b, tb) = run(False), run(True)
+    assert ta == tb
+    for x, y in zip(a, b):
+        assert np.array_equal(x.view(np.uint32), y.view(np.uint32))
+
+
 def test_full_context_forward_and_uncached_generate_on_the_gpu():
     """Gpt::forward / Gpt::generate (src/nn.rs:629-715) through the library vs the CPU checker."""
     model = kv_model(9)

@@ -309,12 +309,14 @@ int ensure_rows(tnsr_b200_decoder* dec, uint32_t rows, uint32_t logit_rows) {
 }
 
 // ---- one step on the strict f32 path -----------------------------------------
-int step_strict(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, uint32_t position, uint32_t logit_rows) {
+// `d_position` (optional): the position as a device scalar, for replay from a captured graph.
+int step_strict(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, uint32_t position,
+                const uint32_t* d_position, uint32_t logit_rows) {
     const tnsr_b200_config& c = dec->cfg;
     const uint32_t d = c.embed_dim, f = c.feed_forward_dim, H = c.num_heads, B = c.batch, rows = B * chunk;
     cudaStream_t st = dec->stream;
     const int kvdt = dec->kv_bf16 ? TNSR_B200_BF16 : TNSR_B200_F32;
-    RUN(dec, launch_embedding(dec->tok, dec->pos, d_tokens, dec->h, rows, chunk, position, nullptr, c.vocab_size, d,
+    RUN(dec, launch_embedding(dec->tok, dec->pos, d_tokens, dec->h, rows, chunk, position, d_position, c.vocab_size, d,
                               TNSR_B200_F32, dec->d_status, st));
     float* n = (float*)dec->n; float* q = (float*)dec->q; float* att = (float*)dec->att; float* ff = (float*)dec->ff;
     for (Layer& L : dec->layers) {
@@ -326,12 +328,12 @@ int step_strict(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk
         GemmEpilogue ek;
         ek.round_bf16 = dec->kv_bf16;
         ek.out_dtype = kvdt;
-        ek.rows_per_session = chunk; ek.out_session_rows = c.capacity; ek.row_offset = position;
+        ek.rows_per_session = chunk; ek.out_session_rows = c.capacity; ek.row_offset = position; ek.d_row_offset = d_position;
         ek.bias = L.bk;
         RUN(dec, launch_gemm_strict(n, (const float*)L.wk, L.kcache, d, rows, d, d, false, ek, st));
         ek.bias = L.bv;
         RUN(dec, launch_gemm_strict(n, (const float*)L.wv, L.vcache, d, rows, d, d, false, ek, st));
-        RUN(dec, launch_attention_strict(q, L.kcache, L.vcache, att, B, chunk, position, nullptr, c.capacity, H, d / H, kvdt,
+        RUN(dec, launch_attention_strict(q, L.kcache, L.vcache, att, B, chunk, position, d_position, c.capacity, H, d / H, kvdt,
                                          dec->kv_bf16, st));
         GemmEpilogue eo;
         eo.bias = L.bo; eo.residual = dec->h; eo.ldr = d;
@@ -447,7 +449,7 @@ int run_step_direct(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t c
     t_attention_timer = dec->profile_attention ? &dec->attention_timer : nullptr;
     t_pdl = dec->use_pdl && dec->bf16_path && chunk == 1;
     int rc = dec->bf16_path ? step_bf16(dec, d_tokens, chunk, position, d_position, logit_rows, fuse_ids ? d_argmax_out : nullptr)
-                            : step_strict(dec, d_tokens, chunk, position, logit_rows);
+                            : step_strict(dec, d_tokens, chunk, position, d_position, logit_rows);
     t_attention_timer = nullptr;
     if (rc) { t_pdl = false; return rc; }
     if (d_argmax_out && !fuse_ids) {
@@ -469,11 +471,10 @@ int run_step_direct(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t c
     return TNSR_B200_OK;
 }
 
-// One step.  Single-token steps of the bf16 path are captured once per (ids pointer, output pointer) pair
-// and replayed: the kernels read the position from dec->d_pos, which a one-thread kernel sets before each replay.
+// One step.  Single-token steps are captured once per (ids pointer, output pointer) pair and replayed: the
+// kernels read the position from dec->d_pos, which a one-thread kernel sets before each replay.
 int run_step(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, uint32_t position, uint32_t* d_argmax_out) {
-    const bool graphable = dec->use_graphs && dec->bf16_path && chunk == 1 && !dec->profile_attention && dec->stepped_once &&
-                           !debug_sync_enabled();
+    const bool graphable = dec->use_graphs && chunk == 1 && !dec->profile_attention && dec->stepped_once && !debug_sync_enabled();
     if (!graphable) {
         int rc = run_step_direct(dec, d_tokens, chunk, position, nullptr, d_argmax_out);
         if (rc == TNSR_B200_OK && chunk == 1) dec->stepped_once = true;

@@ -91,9 +91,76 @@ gemm_strict_kernel(const float* __restrict__ a, const float* __restrict__ b, voi
         reinterpret_cast<float*>(out)[orow * ldc + col] = v;
 }
 
+// Few rows (decode steps, short prefills): one block per (row, 32 output columns).  The sum of an output is
+// still ONE sequential chain in increasing k -- that is the reference's arithmetic -- but the terms are
+// independent of the chain, so all 512 threads first form the rounded products a[row,p] * b[p,col] side by
+// side into shared memory (every global load of the block is in flight at once), and then one lane per column
+// walks its K products in order.  Same values, same order of additions as gemm_strict_kernel.
+constexpr int SR_COLS = 32, SR_THREADS = 512;
+
+template <bool BT>
+__global__ void __launch_bounds__(SR_THREADS)
+gemm_strict_rows_kernel(const float* __restrict__ a, const float* __restrict__ b, void* __restrict__ out,
+                        uint32_t ldc, uint32_t m, uint32_t k, uint32_t n, GemmEpilogue ep) {
+    extern __shared__ float prod[];   // [k][SR_COLS]
+    const uint32_t row = blockIdx.y, col0 = blockIdx.x * SR_COLS;
+    const float* ar = a + (size_t)row * k;
+    if (BT) {
+        // b is [n, k]: lanes run along p so that a warp reads one contiguous piece of a b row
+        for (uint32_t e = threadIdx.x; e < k * SR_COLS; e += SR_THREADS) {
+            const uint32_t c = e / k, p = e % k, col = col0 + c;
+            prod[p * SR_COLS + c] = col < n ? ar[p] * b[(size_t)col * k + p] : 0.0f;
+        }
+    } else {
+        for (uint32_t e = threadIdx.x; e < k * SR_COLS; e += SR_THREADS) {
+            const uint32_t p = e / SR_COLS, c = e % SR_COLS, col = col0 + c;
+            prod[e] = col < n ? ar[p] * b[(size_t)p * n + col] : 0.0f;
+        }
+    }
+    __syncthreads();
+    const uint32_t col = col0 + threadIdx.x;
+    if (threadIdx.x >= SR_COLS || col >= n) return;
+    float sum = 0.0f;
+#pragma unroll 8
+    for (uint32_t p = 0; p < k; ++p) sum = sum + prod[p * SR_COLS + threadIdx.x];
+    float v = sum;
+    if (ep.bias) v = v + ep.bias[col];
+    if (ep.activation == ACT_RELU) v = fmaxf(v, 0.0f);
+    else if (ep.activation == ACT_GELU) v = strict_gelu(v);
+    if (ep.residual) v = ep.residual[(size_t)row * ep.ldr + col] + v;
+    if (ep.round_bf16) v = round_to_bf16(v);
+    size_t orow = row;
+    if (ep.rows_per_session) {
+        uint32_t off = ep.d_row_offset ? *ep.d_row_offset : ep.row_offset;
+        orow = (size_t)(row / ep.rows_per_session) * ep.out_session_rows + off + row % ep.rows_per_session;
+    }
+    if (ep.out_dtype == TNSR_B200_BF16)
+        reinterpret_cast<bf16*>(out)[orow * ldc + col] = __float2bfloat16_rn(v);
+    else
+        reinterpret_cast<float*>(out)[orow * ldc + col] = v;
+}
+
 int launch_gemm_strict(const float* a, const float* b, void* out, uint32_t ldc, uint32_t m, uint32_t k,
                        uint32_t n, bool b_transposed, const GemmEpilogue& ep, cudaStream_t stream) {
     if (m == 0 || n == 0) return TNSR_B200_OK;
+    const size_t rows_smem = (size_t)k * SR_COLS * sizeof(float);
+    if (m <= 64 && k > 0 && rows_smem <= 200 * 1024) {
+        static bool configured[2] = {false, false};
+        if (rows_smem > 48 * 1024 && !configured[b_transposed]) {
+            cudaError_t e = b_transposed
+                ? cudaFuncSetAttribute(gemm_strict_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
+                : cudaFuncSetAttribute(gemm_strict_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e != cudaSuccess) return check_launch("gemm_strict_rows attribute");
+            configured[b_transposed] = true;
+        }
+        dim3 grid(ceil_div(n, SR_COLS), m);
+        if (b_transposed)
+            gemm_strict_rows_kernel<true><<<grid, SR_THREADS, rows_smem, stream>>>(a, b, out, ldc, m, k, n, ep);
+        else
+            gemm_strict_rows_kernel<false><<<grid, SR_THREADS, rows_smem, stream>>>(a, b, out, ldc, m, k, n, ep);
+        count_launch();
+        return check_launch("gemm_strict_rows");
+    }
     dim3 grid(ceil_div(n, ST), ceil_div(m, ST)), block(ST, ST);
     if (grid.y > 65535u) {
         set_thread_error("strict GEMM: too many rows for one launch");
@@ -115,22 +182,39 @@ int launch_gemm_strict(const float* a, const float* b, void* out, uint32_t ldc, 
 __global__ void __launch_bounds__(128)
 layernorm_strict_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
                         float* __restrict__ y, uint32_t width, float eps) {
-    extern __shared__ float row[];
+    // The two sums are sequential chains in index order (the reference's arithmetic); their terms -- x/n and
+    // (x - mean)^2/n -- do not depend on the chain, so all threads form them side by side and one thread adds them up.
+    extern __shared__ float row[];     // [width] values, then [width] terms
+    float* term = row + width;
     __shared__ float stats[2];
     const float* xr = x + (size_t)blockIdx.x * width;
-    for (uint32_t c = threadIdx.x; c < width; c += blockDim.x) row[c] = xr[c];
+    const float nf = (float)width;
+    for (uint32_t c = threadIdx.x; c < width; c += blockDim.x) {
+        const float v = xr[c];
+        row[c] = v;
+        term[c] = v / nf;
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
-        const float nf = (float)width;
         float mean = 0.0f;
-        for (uint32_t c = 0; c < width; ++c) mean = mean + row[c] / nf;
-        float var = 0.0f;
-        for (uint32_t c = 0; c < width; ++c) {
-            float d = row[c] - mean;
-            float sq = d * d;
-            var = var + sq / nf;
-        }
+#pragma unroll 8
+        for (uint32_t c = 0; c < width; ++c) mean = mean + term[c];
         stats[0] = mean;
+    }
+    __syncthreads();
+    {
+        const float mean0 = stats[0];
+        for (uint32_t c = threadIdx.x; c < width; c += blockDim.x) {
+            float d = row[c] - mean0;
+            float sq = d * d;
+            term[c] = sq / nf;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float var = 0.0f;
+#pragma unroll 8
+        for (uint32_t c = 0; c < width; ++c) var = var + term[c];
         stats[1] = strict_expf(strict_logf(var + eps) * -0.5f);
     }
     __syncthreads();
@@ -145,7 +229,7 @@ layernorm_strict_kernel(const float* __restrict__ x, const float* __restrict__ w
 int launch_layernorm_strict(const float* x, const float* w, const float* b, float* out, uint32_t rows,
                             uint32_t width, float eps, cudaStream_t stream) {
     if (rows == 0) return TNSR_B200_OK;
-    size_t smem = (size_t)width * sizeof(float);
+    size_t smem = 2 * (size_t)width * sizeof(float);
     if (smem > 200 * 1024) {
         set_thread_error("strict LayerNorm: row does not fit shared memory");
         return TNSR_B200_ERR_UNSUPPORTED;

@@ -79,8 +79,14 @@ def copies_for(bytes_per_set):
     return max(1, min(64, -(-2 * L2_BYTES // max(bytes_per_set, 1))))
 
 
+RESULTS = []      # every emitted record, for callers that import the bench functions
+QUIET = False     # True: collect only
+
+
 def emit(**kw):
-    print(json.dumps(kw), flush=True)
+    RESULTS.append(kw)
+    if not QUIET:
+        print(json.dumps(kw), flush=True)
 
 
 def bench_gemm(samples):
