@@ -113,7 +113,9 @@ TNSR_B200_API const char* tnsr_b200_last_error(const tnsr_b200_decoder* dec);
 TNSR_B200_API uint64_t tnsr_b200_kernel_launches(void);
 /* GEMM engine of the bf16 path: 0 = tcgen05/TMEM kernel where the shape
  * allows it, else the CUDA-core kernel (default); 1 = always the CUDA-core
- * kernel; 2 = tcgen05 only (unsupported shapes fail).  Process-wide.  Engine 1
+ * kernel; 2 = tcgen05 only (unsupported shapes fail); 3 = as 0, but products
+ * of at most 64 rows always take the few-row engine (by default only those
+ * shapes do for which it is the faster one).  Process-wide.  Engine 1
  * also keeps prefill attention off tcgen05 (the warp-level mma.sync kernel
  * runs), which is how tests compare the two. */
 TNSR_B200_API int tnsr_b200_set_gemm_engine(int engine);
@@ -234,6 +236,19 @@ TNSR_B200_API int tnsr_b200_gemm_f32_strict(const float* a, const float* b, cons
 TNSR_B200_API int tnsr_b200_gemm_bf16(const void* a, const void* bt, const float* bias,
                                       const float* residual, void* out, uint32_t m, uint32_t n,
                                       uint32_t k, int activation, int out_dtype, void* stream);
+/* The same product with scratch lent by the caller (no reference counterpart).
+ * It matters for m <= 64, where the weights are streamed once with the
+ * operands of the MMA swapped: with scratch the K range of every 128-column
+ * tile is divided over several CTAs so that all SMs pull on HBM, and the CTA
+ * that finishes last adds the partial tiles in a fixed order (results do not
+ * depend on timing).  `workspace`: tnsr_b200_gemm_workspace() bytes, 16-byte
+ * aligned, zeroed once before the first use (every launch leaves it zeroed);
+ * launches that may overlap on the GPU must not share it. */
+TNSR_B200_API uint64_t tnsr_b200_gemm_workspace(void);
+TNSR_B200_API int tnsr_b200_gemm_bf16_ws(const void* a, const void* bt, const float* bias,
+                                         const float* residual, void* out, uint32_t m, uint32_t n,
+                                         uint32_t k, int activation, int out_dtype,
+                                         void* workspace, uint64_t workspace_bytes, void* stream);
 /* Transposes a [k, n] row-major bf16 matrix into the [n, k] layout above. */
 TNSR_B200_API int tnsr_b200_transpose_bf16(const void* in, void* out, uint32_t k, uint32_t n,
                                            void* stream);

@@ -51,12 +51,17 @@ def rel_err(actual, expected):
     return float(np.max(np.abs(actual - expected)) / max(np.max(np.abs(expected)), 1e-30))
 
 
-def gemm_bf16(a, bt, bias=None, residual=None, activation=-1, out_dtype=F32):
-    """a [m,k] bf16 cuda, bt [n,k] bf16 cuda -> out [m,n]."""
+def gemm_bf16(a, bt, bias=None, residual=None, activation=-1, out_dtype=F32, workspace=None):
+    """a [m,k] bf16 cuda, bt [n,k] bf16 cuda -> out [m,n].  `workspace` (a zeroed uint8 cuda tensor of
+    tnsr_b200_gemm_workspace() bytes) lends split-K scratch to the few-row engine."""
     m, k = a.shape
     n = bt.shape[0]
     out = torch.empty((m, n), dtype=torch.float32 if out_dtype == F32 else torch.bfloat16, device="cuda")
-    ok(lib().tnsr_b200_gemm_bf16(ptr(a), ptr(bt), ptr(bias), ptr(residual), ptr(out), m, n, k, activation, out_dtype,
-                                 stream()))
+    if workspace is None:
+        ok(lib().tnsr_b200_gemm_bf16(ptr(a), ptr(bt), ptr(bias), ptr(residual), ptr(out), m, n, k, activation, out_dtype,
+                                     stream()))
+    else:
+        ok(lib().tnsr_b200_gemm_bf16_ws(ptr(a), ptr(bt), ptr(bias), ptr(residual), ptr(out), m, n, k, activation, out_dtype,
+                                        ptr(workspace), workspace.numel(), stream()))
     torch.cuda.synchronize()
     return out

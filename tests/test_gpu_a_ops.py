@@ -194,6 +194,44 @@ def test_gemm_bf16_epilogues(engine):
     assert rel_err(gelu, orc.gelu(z.astype(np.float32))) <= 1 / 128
 
 
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (8, 4096, 4096), (64, 4096, 4096), (17, 768, 768), (32, 768, 2048),
+                                   (64, 2304, 768), (5, 100, 72), (33, 129, 520), (16, 32000, 768), (1, 128, 64)])
+def test_gemm_bf16_few_rows_engine_matches_f64_with_and_without_split_k(shape):
+    """m <= 64 with scratch lent: weights on the M side of the MMA, K divided over several CTAs per 128-column tile and
+    merged in a fixed order.  Same tolerance as the other engines; two runs are bit-identical; the scratch counters are
+    back at zero; the epilogues (bias, activation, residual, bf16 output, in place on the residual stream) run on the
+    merged tile.  Without scratch the same call takes whichever engine the shape selects and must agree as well."""
+    m, n, k = shape
+    a, bt, ref = gemm_case(m, n, k, seed=11)
+    rng = np.random.default_rng(12)
+    bias = rng.standard_normal(n).astype(np.float32)
+    resid = rng.standard_normal((m, n)).astype(np.float32)
+    da, dbt, dbias, dres = dev(a, torch.bfloat16), dev(bt, torch.bfloat16), dev(bias), dev(resid)
+    ws = torch.zeros(lib().tnsr_b200_gemm_workspace(), dtype=torch.uint8, device="cuda")
+    tol = 4e-6 * k
+    ok(lib().tnsr_b200_set_gemm_engine(3))      # the few-row engine for every shape here, not only where it is faster
+    try:
+        first = gemm_bf16(da, dbt, workspace=ws)
+        assert np.max(np.abs(first.cpu().numpy() - ref)) <= tol
+        assert int(ws[:8192].view(torch.int32).abs().sum()) == 0
+        assert torch.equal(first, gemm_bf16(da, dbt, workspace=ws))
+        unsplit = gemm_bf16(da, dbt)                 # same engine, no scratch: one CTA per 128 columns
+        assert np.max(np.abs(unsplit.cpu().numpy() - ref)) <= tol
+        fused = gemm_bf16(da, dbt, bias=dbias, residual=dres, workspace=ws).cpu().numpy()
+        assert np.max(np.abs(fused - (ref + bias + resid))) <= tol + 1e-5
+        relu = gemm_bf16(da, dbt, bias=dbias, activation=0, out_dtype=BF16, workspace=ws).float().cpu().numpy()
+        assert rel_err(relu, np.maximum(ref + bias, 0)) <= 1 / 128
+        stream_buf = dres.clone()      # in place on the residual stream, as the decoder calls it
+        ok(lib().tnsr_b200_gemm_bf16_ws(ptr(da), ptr(dbt), ptr(dbias), ptr(stream_buf), ptr(stream_buf), m, n, k, -1, 0,
+                                        ptr(ws), ws.numel(), stream()))
+        torch.cuda.synchronize()
+        assert np.array_equal(stream_buf.cpu().numpy(), fused)
+    finally:
+        lib().tnsr_b200_set_gemm_engine(0)
+    default = gemm_bf16(da, dbt, workspace=ws)      # whichever engine the shape selects by default
+    assert np.max(np.abs(default.cpu().numpy() - ref)) <= tol
+
+
 # ---- SwiGLU ----------------------------------------------------------------------
 def test_swiglu_elementwise(oracle):
     import json, os

@@ -60,6 +60,8 @@ SIGNATURES = {
     "tnsr_b200_layernorm": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _f, _i, _i, _vp]),
     "tnsr_b200_gemm_f32_strict": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _i, _vp]),
     "tnsr_b200_gemm_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _i, _i, _vp]),
+    "tnsr_b200_gemm_workspace": (_u64, []),
+    "tnsr_b200_gemm_bf16_ws": (_i, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _i, _i, _vp, _u64, _vp]),
     "tnsr_b200_transpose_bf16": (_i, [_vp, _vp, _u32, _u32, _vp]),
     "tnsr_b200_swiglu": (_i, [_vp, _vp, _vp, _u64, _vp]),
     "tnsr_b200_swiglu_mlp": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),

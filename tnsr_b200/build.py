@@ -21,7 +21,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(CSRC, "libtnsr_b200.so")
 
-SOURCES = ["decoder.cu", "ops_api.cu", "elementwise.cu", "strict.cu", "gemm.cu", "attention.cu", "prefill.cu", "prefill_tc.cu",
+SOURCES = ["decoder.cu", "ops_api.cu", "elementwise.cu", "strict.cu", "gemm.cu", "gemm_skinny.cu", "attention.cu", "prefill.cu", "prefill_tc.cu",
            "decode_attention_static.cu", "probe.cu"]
 EXTRA = {"strict.cu": ["--fmad=false"]}
 

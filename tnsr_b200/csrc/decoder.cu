@@ -572,7 +572,7 @@ const char* tnsr_b200_last_error(const tnsr_b200_decoder* dec) { return dec ? de
 uint64_t tnsr_b200_kernel_launches(void) { return g_launches.load(); }
 
 int tnsr_b200_set_gemm_engine(int engine) {
-    if (engine < 0 || engine > 2) return TNSR_B200_ERR_INVALID_ARGUMENT;
+    if (engine < 0 || engine > 3) return TNSR_B200_ERR_INVALID_ARGUMENT;
     g_gemm_engine = engine;
     return TNSR_B200_OK;
 }

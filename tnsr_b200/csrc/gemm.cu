@@ -649,6 +649,19 @@ static int launch_gemm_impl(const bf16* a, const bf16* bt, void* out, uint32_t l
         }
         return simple();
     }
+    // A handful of rows against a large weight matrix: stream the weights with the operands swapped (gemm_skinny.cu)
+    // when that engine can fill the GPU, i.e. with split-K scratch lent by the caller or with at least half as many
+    // 128-column tiles as SMs.  Measured inside a CUDA graph, 4096 x 4096 weights: 14.8 / 16.3 us at 1 / 8 rows against
+    // 28 us for the engine below; at 64 rows (33.6 against 21.5 us) and for the small matrices of a decode step (the
+    // split-K hand-over through L2 costs more than it saves) the engine below is the faster one.
+    // Engine 3 (tests) takes it for every eligible shape up to 64 rows.
+    if (mode == GEMM_PLAIN && m <= 64 && g_gemm_engine != 1 && gemm_skinny_eligible(a, bt, m, n, k, ep)) {
+        const bool pays = m <= 16 && (uint64_t)n * k >= (4ull << 20) &&
+                          ((ep.skinny_ws && ep.skinny_ws_bytes >= gemm_skinny_workspace_bytes()) ||
+                           2 * ceil_div(n, 128u) >= (uint32_t)sm_count());
+        if (pays || g_gemm_engine == 3)
+            return launch_gemm_skinny(a, bt, out, ldc, m, n, k, ep, ep.skinny_ws, ep.skinny_ws_bytes, d_status, stream);
+    }
     // tile width: the widest that still gives every SM a tile (32 at the narrowest)
     const uint32_t tiles_m = ceil_div(m, BM);
     uint32_t bn = 256;

@@ -43,6 +43,14 @@ int tnsr_b200_gemm_f32_strict(const float* a, const float* b, const float* bias,
 
 int tnsr_b200_gemm_bf16(const void* a, const void* bt, const float* bias, const float* residual, void* out, uint32_t m,
                         uint32_t n, uint32_t k, int activation, int out_dtype, void* stream) {
+    return tnsr_b200_gemm_bf16_ws(a, bt, bias, residual, out, m, n, k, activation, out_dtype, nullptr, 0, stream);
+}
+
+uint64_t tnsr_b200_gemm_workspace(void) { return gemm_skinny_workspace_bytes(); }
+
+int tnsr_b200_gemm_bf16_ws(const void* a, const void* bt, const float* bias, const float* residual, void* out, uint32_t m,
+                           uint32_t n, uint32_t k, int activation, int out_dtype, void* workspace, uint64_t workspace_bytes,
+                           void* stream) {
     if (!a || !bt || !out) return bad("gemm_bf16: null pointer");
     if (out_dtype != TNSR_B200_F32 && out_dtype != TNSR_B200_BF16) return bad("gemm_bf16: bad output dtype");
     if (activation < -1 || activation > TNSR_B200_ACT_GELU) return bad("gemm_bf16: activation must be -1, RELU or GELU");
@@ -53,6 +61,12 @@ int tnsr_b200_gemm_bf16(const void* a, const void* bt, const float* bias, const 
     ep.ldr = n;
     ep.activation = activation;
     ep.out_dtype = out_dtype;
+    if (workspace) {
+        if (workspace_bytes < gemm_skinny_workspace_bytes() || (reinterpret_cast<uintptr_t>(workspace) & 15))
+            return bad("gemm_bf16_ws: workspace too small or not 16-byte aligned");
+        ep.skinny_ws = workspace;
+        ep.skinny_ws_bytes = workspace_bytes;
+    }
     return launch_gemm_bf16((const bf16*)a, (const bf16*)bt, out, n, m, n, k, GEMM_PLAIN, ep, nullptr, nullptr,
                             as_stream(stream));
 }

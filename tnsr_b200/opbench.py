@@ -75,6 +75,33 @@ def timed(launch, sets, samples):
     return float(np.median(times)), times
 
 
+def timed_graph(launch, sets, samples, reps=None):
+    """Per-launch milliseconds of a SHORT kernel: `reps` launches, rotating over the operand copies, are captured into
+    one CUDA graph and the replay is timed -- a single launch between two events would mostly measure the host (tensor-map
+    encoding, the ctypes call, the launch itself), not the GPU.  Includes the ~1.2 us a dependent graph node costs."""
+    reps = reps or max(sets, 16)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for i in range(3):
+            launch(i % sets)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(reps):
+                launch(i % sets)
+        times = []
+        for i in range(samples + 2):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            e1.synchronize()
+            if i >= 2:
+                times.append(e0.elapsed_time(e1) / reps)
+    torch.cuda.synchronize()
+    return float(np.median(times)), times
+
+
 def copies_for(bytes_per_set):
     return max(1, min(64, -(-2 * L2_BYTES // max(bytes_per_set, 1))))
 
@@ -102,10 +129,16 @@ def bench_gemm(samples):
             b = [(torch.rand((n, k), device="cuda", generator=g) * 2 - 1).to(torch.bfloat16) for _ in range(sets)]
             o = [torch.empty((m, n), device="cuda", dtype=torch.bfloat16 if out_dtype else torch.float32) for _ in range(sets)]
 
-            def launch(i):
-                ok(lib().tnsr_b200_gemm_bf16(ptr(a[i]), ptr(b[i]), None, None, ptr(o[i]), m, n, k, -1, out_dtype, stream()))
+            ws = torch.zeros(lib().tnsr_b200_gemm_workspace(), dtype=torch.uint8, device="cuda") if m <= 64 else None
 
-            ms, _ = timed(launch, sets, samples)
+            def launch(i):
+                if ws is None:
+                    ok(lib().tnsr_b200_gemm_bf16(ptr(a[i]), ptr(b[i]), None, None, ptr(o[i]), m, n, k, -1, out_dtype, stream()))
+                else:   # few rows: lend split-K scratch, as a decoder session does
+                    ok(lib().tnsr_b200_gemm_bf16_ws(ptr(a[i]), ptr(b[i]), None, None, ptr(o[i]), m, n, k, -1, out_dtype,
+                                                    ptr(ws), ws.numel(), stream()))
+
+            ms, _ = timed_graph(launch, sets, samples) if m <= 64 else timed(launch, sets, samples)
             ref = (a[0].float() @ b[0].float().T)
             launch(0)
             torch.cuda.synchronize()
@@ -125,37 +158,25 @@ def bench_serving_gemms(samples):
     for rows in (131072, 256):
         for name, n, k, out_dtype, resid in (("qkv", 2304, 768, 1, False), ("attn_out", 768, 768, 0, True),
                                              ("gate_up", 4096, 768, 1, False), ("ffn_down", 768, 2048, 0, True)):
-            a = (torch.randn((rows, k), device="cuda", generator=g)).to(torch.bfloat16)
-            b = (torch.randn((n, k), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
-            r = torch.randn((rows, n), device="cuda", generator=g) if resid else None
-            o = torch.empty((rows, n), device="cuda", dtype=torch.bfloat16 if out_dtype else torch.float32)
-            flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if rows <= 1024 else None
+            osz = 2 if out_dtype else 4
+            per_set = 2 * (rows * k + n * k) + osz * rows * n * (2 if resid else 1)
+            sets = copies_for(per_set) if rows <= 1024 else 1    # small operands would otherwise sit in L2 between launches
+            a = [(torch.randn((rows, k), device="cuda", generator=g)).to(torch.bfloat16) for _ in range(sets)]
+            b = [(torch.randn((n, k), device="cuda", generator=g) * 0.02).to(torch.bfloat16) for _ in range(sets)]
+            r = [torch.randn((rows, n), device="cuda", generator=g) if resid else None for _ in range(sets)]
+            o = [torch.empty((rows, n), device="cuda", dtype=torch.bfloat16 if out_dtype else torch.float32) for _ in range(sets)]
 
-            def launch(_):
-                if flush is not None:
-                    flush.zero_()  # small operands would otherwise sit in L2 between launches
-                ok(lib().tnsr_b200_gemm_bf16(ptr(a), ptr(b), None, ptr(r), ptr(o), rows, n, k, -1, out_dtype, stream()))
+            def launch(i):
+                ok(lib().tnsr_b200_gemm_bf16(ptr(a[i]), ptr(b[i]), None, ptr(r[i]), ptr(o[i]), rows, n, k, -1, out_dtype, stream()))
 
-            if flush is None:
-                ms, _ = timed(launch, 1, samples)
-            else:
-                # time only the GEMM: events around it, the L2 flush outside
-                for _ in range(3):
-                    launch(0)
-                ts = []
-                for _ in range(samples):
-                    flush.zero_()
-                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    e0.record()
-                    ok(lib().tnsr_b200_gemm_bf16(ptr(a), ptr(b), None, ptr(r), ptr(o), rows, n, k, -1, out_dtype, stream()))
-                    e1.record()
-                    e1.synchronize()
-                    ts.append(e0.elapsed_time(e1))
-                ms = float(np.median(ts))
+            # decode-size launches are a few microseconds: time them inside a graph, as the decoder runs them
+            ms, _ = timed_graph(launch, sets, samples) if rows <= 1024 else timed(launch, 1, samples)
             flops = 2.0 * rows * n * k
             emit(op="serving_gemm", which=name, rows=rows, n=n, k=k, out="bf16" if out_dtype else "f32+residual", ms=ms,
-                 tflops=flops / ms / 1e9, frac_tensor=flops / ms / 1e9 / tf, peaks=kind)
-            del a, b, r, o, flush
+                 tflops=flops / ms / 1e9, frac_tensor=flops / ms / 1e9 / tf, operand_sets=sets,
+                 timing="graph of back-to-back launches over rotating operand sets" if rows <= 1024 else "one launch between events",
+                 peaks=kind)
+            del a, b, r, o
 
 
 def bench_mlp(samples):
