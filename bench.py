@@ -407,6 +407,14 @@ def run_b200(args):
     sessions = sessions_per_gpu(args, world)
     K, W = args.steps, args.warmup
     capacity = min(cfg.max_sequence_length, args.prefill + max(K, W) + 1)
+    # positions of the decode steps: prefill, prefill + 1, ...; a run longer than the context allows starts over at
+    # `prefill` (the cache rows are overwritten), so any K can be timed
+    span = capacity - args.prefill
+    if span < 1:
+        raise SystemExit("--prefill leaves no room for decode steps in the model context")
+
+    def position_of(step):
+        return args.prefill + step % span
     lib = _native.lib()
 
     def make_session():
@@ -448,7 +456,7 @@ def run_b200(args):
     def device_loop(n, cur):
         """n greedy steps from position `prefill`; ids stay in `cur` on the device."""
         for step in range(n):
-            sess.decode_device(cur.data_ptr(), 1, args.prefill + step, cur.data_ptr())
+            sess.decode_device(cur.data_ptr(), 1, position_of(step), cur.data_ptr())
         return cur
 
     # ---- warm-up, then the timed region ----
@@ -482,12 +490,12 @@ def run_b200(args):
     if not args.no_e2e:
         cur = first_host.copy()
         for step in range(min(W, K)):
-            _, cur = sess.decode_full(cur.reshape(sessions, 1), args.prefill + step)
+            _, cur = sess.decode_full(cur.reshape(sessions, 1), position_of(step))
         cur = first_host.copy()
         barrier()
         t0 = time.perf_counter()
         for step in range(K):
-            _, cur = sess.decode_full(cur.reshape(sessions, 1), args.prefill + step)
+            _, cur = sess.decode_full(cur.reshape(sessions, 1), position_of(step))
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t0
         barrier()
@@ -519,7 +527,7 @@ def run_b200(args):
         peak, peak_kind, peaks = measured_peaks()
         # algorithmic bytes of one attention launch at decode step t: every session's live K and V rows
         # (prefill + t + 1 keys x d x 2 B x 2 tensors) plus q and out rows
-        live = args.prefill + (K - 1) / 2.0 + 1.0
+        live = float(np.mean([position_of(t) + 1 for t in range(K)]))     # keys a step at position p attends: p + 1
         bytes_per_launch = sessions * (live * d * 2 * 2 + 2 * d * 2)
         attn_avg_ms = attn_ms / max(attn_launches, 1)
         achieved = bytes_per_launch / (attn_avg_ms * 1e-3) / 1e9 if attn_launches else None

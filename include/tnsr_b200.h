@@ -164,6 +164,19 @@ TNSR_B200_API int tnsr_b200_decoder_decode(tnsr_b200_decoder* dec, const uint32_
                                            uint32_t chunk, uint32_t position, float* logits_out,
                                            uint32_t* argmax_out);
 
+/* Ragged single-token step (no reference counterpart: the reference's sessions
+ * advance together; its documentation lists ragged batches as future work,
+ * docs/kv-cache.md:94-95).  Session b consumes tokens[b] at its own position
+ * positions[b] (< capacity): its K/V row is written there and it attends rows
+ * 0 .. positions[b].  The caller keeps the per-session lengths; rows past a
+ * session's position are never read.  bf16 weights only (weight_dtype BF16) and
+ * head widths the split-KV attention kernel covers (32, 64, 128).  logits_out:
+ * [batch, vocab] f32 or NULL; argmax_out: [batch] or NULL.  Synchronous like
+ * tnsr_b200_decoder_decode. */
+TNSR_B200_API int tnsr_b200_decoder_decode_ragged(tnsr_b200_decoder* dec, const uint32_t* tokens,
+                                                  const uint32_t* positions, float* logits_out,
+                                                  uint32_t* argmax_out);
+
 /* Device-resident form of the same step for serving loops: ids are read from
  * and greedy ids written to device memory, nothing is copied and nothing is
  * synchronised; work is queued on the session's stream.  Ids are validated on

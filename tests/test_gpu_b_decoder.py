@@ -335,6 +335,78 @@ def test_graph_replay_on_the_strict_f32_path_matches_direct_launches(monkeypatch
         assert np.array_equal(x.view(np.uint32), y.view(np.uint32))
 
 
+@pytest.mark.parametrize("logits_mode", ["last", "none"])
+def test_ragged_decode_every_session_at_its_own_position(logits_mode):
+    """tnsr_b200_decoder_decode_ragged: after a common 12-token prefill, session b is rewound by 3 b tokens and all
+    sessions then advance together from different positions.  Each must reproduce a batch-1 session of the same library
+    that was prefilled with exactly its own prefix (bit for bit in the greedy ids, and logits within the bf16 tolerance),
+    and the CPU checker on bf16-rounded weights within 2e-2."""
+    cfg, model, rounded_arrays = small_bf16_model("swiglu", 128, 2, 256, vocab=300)
+    params = [p.values() for p in model_parameters(model)]
+    rng = np.random.default_rng(21)
+    batch, prompt_len, steps = 4, 12, 6
+    prompt = rng.integers(0, cfg.vocab_size, size=(batch, prompt_len)).astype(np.uint32)
+    feed = rng.integers(0, cfg.vocab_size, size=(steps, batch)).astype(np.uint32)
+    starts = np.array([prompt_len - 3 * b for b in range(batch)], dtype=np.uint32)      # 12, 9, 6, 3
+
+    def session(b, mode):
+        s = B200Session(cfg, b, cfg.max_sequence_length, logits_mode=mode)
+        for i, p in enumerate(params):
+            s.refresh(i, p)
+        return s
+
+    ragged = session(batch, logits_mode)
+    ragged.decode_full(prompt, 0)
+    got_logits, got_ids = [], []
+    for t in range(steps):
+        logits, ids = ragged.decode_ragged(feed[t], starts + t)
+        got_logits.append(None if logits is None else logits.reshape(batch, -1).copy())
+        got_ids.append(ids.copy())
+    ragged.close()
+
+    for b in range(batch):
+        single = session(1, "last")
+        single.decode_full(prompt[b:b + 1, :int(starts[b])], 0)
+        for t in range(steps):
+            logits, ids = single.decode_full(feed[t, b].reshape(1, 1), int(starts[b]) + t)
+            assert int(ids[0]) == int(got_ids[t][b])
+            if got_logits[t] is not None:
+                assert rel_err(got_logits[t][b], logits) <= 2e-3
+        single.close()
+
+    if logits_mode == "last":
+        rounded = Gpt(cfg)
+        set_model_arrays(rounded, rounded_arrays)
+        for b in (0, batch - 1):
+            cpu = cpu_decoder(rounded, 1)
+            cpu.decode([int(x) for x in prompt[b, :int(starts[b])]])
+            for t in range(steps):
+                ref = cpu.decode([int(feed[t, b])])
+                assert rel_err(got_logits[t][b], ref) <= 2e-2
+
+
+def test_ragged_decode_rejects_what_it_cannot_do():
+    from tnsr_b200.nn import TnsrError
+    cfg, arrays = config0_model("relu")                      # f32 weights: the strict path has no ragged step
+    s = B200Session(cfg, 2, 32)
+    for i, a in enumerate(arrays):
+        s.refresh(i, a)
+    with pytest.raises(TnsrError):
+        s.decode_ragged(np.zeros(2, np.uint32), np.zeros(2, np.uint32))
+    s.close()
+    cfg, model, _ = small_bf16_model("swiglu", 128, 2, 256, vocab=300)
+    s = B200Session(cfg, 2, 16, logits_mode="last")
+    for i, p in enumerate(model_parameters(model)):
+        s.refresh(i, p.values())
+    with pytest.raises(TnsrError):
+        s.decode_ragged(np.zeros(2, np.uint32), np.array([0, 16], np.uint32))      # position == capacity
+    with pytest.raises(TnsrError):
+        s.decode_ragged(np.array([0, 300], np.uint32), np.zeros(2, np.uint32))      # token == vocab
+    logits, ids = s.decode_ragged(np.array([1, 2], np.uint32), np.array([0, 0], np.uint32))   # still usable afterwards
+    assert np.all(np.isfinite(logits))
+    s.close()
+
+
 def test_full_context_forward_and_uncached_generate_on_the_gpu():
     """Gpt::forward / Gpt::generate (src/nn.rs:629-715) through the library vs the CPU checker."""
     model = kv_model(9)

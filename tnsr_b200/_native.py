@@ -49,6 +49,7 @@ SIGNATURES = {
     "tnsr_b200_decoder_upload": (_i, [_vp, _u32, _fp, _u64]),
     "tnsr_b200_decoder_reset": (_i, [_vp]),
     "tnsr_b200_decoder_decode": (_i, [_vp, _u32p, _u32, _u32, _fp, _u32p]),
+    "tnsr_b200_decoder_decode_ragged": (_i, [_vp, _u32p, _u32p, _fp, _u32p]),
     "tnsr_b200_decoder_decode_device": (_i, [_vp, _vp, _u32, _u32, _vp]),
     "tnsr_b200_decoder_synchronize": (_i, [_vp]),
     "tnsr_b200_decoder_stream": (_vp, [_vp]),

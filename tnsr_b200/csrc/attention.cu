@@ -178,7 +178,7 @@ bool decode_attention_supported(uint32_t heads, uint32_t head_dim) {
 }
 
 // ---- plan: one block ---------------------------------------------------------------
-// lengths == nullptr means every session has (d_position ? *d_position : 0) + extra keys.
+// Session b has lengths[b] + extra keys; lengths == nullptr means (d_position ? *d_position : 0) + extra for all.
 __global__ void __launch_bounds__(1024)
 da_plan_kernel(const uint32_t* __restrict__ lengths, const uint32_t* __restrict__ d_position, uint32_t extra,
                uint32_t batch, uint32_t heads, uint32_t capacity, uint32_t grid, uint32_t* __restrict__ header,
@@ -190,7 +190,7 @@ da_plan_kernel(const uint32_t* __restrict__ lengths, const uint32_t* __restrict_
     pdl_trigger();
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     auto len_of = [&](uint32_t b) -> uint32_t {
-        uint32_t L = lengths ? lengths[b] : ((d_position ? *d_position : 0u) + extra);
+        uint32_t L = (lengths ? lengths[b] : (d_position ? *d_position : 0u)) + extra;
         if (L > capacity) {
             if (d_status) atomicCAS(d_status, DEV_OK, DEV_BAD_LENGTH);
             L = capacity;

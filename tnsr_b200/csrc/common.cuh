@@ -125,6 +125,7 @@ struct GemmQkvTargets {
     uint32_t d = 0, chunk = 0, capacity = 0;
     const uint32_t* d_position = nullptr;  // device scalar: first new row
     uint32_t position = 0;                 // used when d_position == nullptr
+    uint32_t position_stride = 0;          // 1: d_position is an array with one entry per session (ragged batches)
 };
 int launch_gemm_bf16(const bf16* a, const bf16* bt, void* out, uint32_t ldc, uint32_t m, uint32_t n,
                      uint32_t k, GemmMode mode, const GemmEpilogue& ep, const GemmQkvTargets* qkv,
@@ -143,7 +144,7 @@ int launch_lm_head_argmax(const bf16* a, const bf16* bt, uint32_t m, uint32_t n,
 
 int launch_embedding(const void* tok, const void* pos, const uint32_t* ids, float* out, uint32_t rows,
                      uint32_t chunk, uint32_t position0, const uint32_t* d_position, uint32_t vocab,
-                     uint32_t width, int dtype, int* d_status, cudaStream_t stream);
+                     uint32_t width, int dtype, int* d_status, cudaStream_t stream, uint32_t position_stride = 0);
 int launch_layernorm(const float* x, const float* w, const float* b, void* out, uint32_t rows,
                      uint32_t width, float eps, int out_dtype, bool strict, cudaStream_t stream);
 // Gathers row (s * chunk + chunk - 1) of x for every session s into out[s, :] (f32).

@@ -88,6 +88,8 @@ struct tnsr_b200_decoder {
     int* d_status = nullptr;
     void* attn_ws = nullptr;
     uint64_t attn_ws_bytes = 0;
+    uint32_t* d_positions = nullptr;   // [batch] per-session positions of a ragged step
+    uint32_t* h_positions = nullptr;   // pinned staging for them
     // pinned staging
     uint32_t* h_tokens = nullptr;
     uint32_t* h_argmax = nullptr;
@@ -368,15 +370,17 @@ int step_strict(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk
 // `d_position` (optional): the position as a device scalar, so that a captured graph of the step can be replayed
 // while the position advances.  `fused_ids` (optional): greedy ids come straight out of the LM-head GEMM and no
 // logits are written (only when the logits mode is NONE).
+// `ragged`: d_position is an array with one position per session (single-token steps only).
 int step_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, uint32_t position,
-              const uint32_t* d_position, uint32_t logit_rows, uint32_t* fused_ids) {
+              const uint32_t* d_position, uint32_t logit_rows, uint32_t* fused_ids, bool ragged = false) {
     const tnsr_b200_config& c = dec->cfg;
     const uint32_t d = c.embed_dim, f = c.feed_forward_dim, H = c.num_heads, hd = d / H, B = c.batch, rows = B * chunk;
     cudaStream_t st = dec->stream;
     bf16* n = (bf16*)dec->n; bf16* q = (bf16*)dec->q; bf16* att = (bf16*)dec->att; bf16* ff = (bf16*)dec->ff;
     RUN(dec, launch_embedding(dec->tok, dec->pos, d_tokens, dec->h, rows, chunk, position, d_position, c.vocab_size, d,
-                              TNSR_B200_BF16, dec->d_status, st));
+                              TNSR_B200_BF16, dec->d_status, st, ragged ? 1u : 0u));
     const bool fast_decode = chunk == 1 && dec->attn_ws && decode_attention_supported(H, hd);
+    if (ragged && !fast_decode) return fail(dec, TNSR_B200_ERR_UNSUPPORTED, "ragged decode needs the split-KV attention kernel (head width 32, 64 or 128)");
     bool planned = false;
     for (Layer& L : dec->layers) {
         RUN(dec, launch_layernorm(dec->h, L.ln1w, L.ln1b, n, rows, d, c.layer_norm_epsilon, TNSR_B200_BF16, false, st));
@@ -385,9 +389,15 @@ int step_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, 
         GemmQkvTargets tg;
         tg.q = q; tg.k_cache = (bf16*)L.kcache; tg.v_cache = (bf16*)L.vcache;
         tg.d = d; tg.chunk = chunk; tg.capacity = c.capacity; tg.position = position; tg.d_position = d_position;
+        tg.position_stride = ragged ? 1u : 0u;
         RUN(dec, launch_gemm_bf16(n, L.wqkv, nullptr, 0, rows, 3 * d, d, GEMM_QKV, eq, &tg, dec->d_status, st));
         if (fast_decode) {
             // every session holds position + 1 keys; the item list is the same for all layers of this step
+            if (ragged)   // session b holds d_position[b] + 1 keys
+                RUN(dec, launch_decode_attention_ex(q, (const bf16*)L.kcache, (const bf16*)L.vcache, d_position, nullptr, 1, att,
+                                                    dec->attn_ws, dec->attn_ws_bytes, B, c.capacity, H, hd, !planned,
+                                                    dec->d_status, st));
+            else
             RUN(dec, launch_decode_attention_ex(q, (const bf16*)L.kcache, (const bf16*)L.vcache, nullptr, d_position,
                                                 d_position ? 1 : position + 1, att, dec->attn_ws, dec->attn_ws_bytes, B,
                                                 c.capacity, H, hd, !planned, dec->d_status, st));
@@ -653,6 +663,7 @@ void tnsr_b200_decoder_destroy(tnsr_b200_decoder* dec) {
     for (void* p : dec->allocations) cudaFree(p);
     if (dec->h_tokens) cudaFreeHost(dec->h_tokens);
     if (dec->h_argmax) cudaFreeHost(dec->h_argmax);
+    if (dec->h_positions) cudaFreeHost(dec->h_positions);
     if (dec->h_status) cudaFreeHost(dec->h_status);
     if (dec->h_stage) cudaFreeHost(dec->h_stage);
     drop_graphs(dec);
@@ -819,6 +830,55 @@ int tnsr_b200_decoder_decode(tnsr_b200_decoder* dec, const uint32_t* tokens, uin
     if ((rc = run_step(dec, dec->d_tokens, chunk, position, argmax_out ? dec->d_argmax : nullptr))) return rc;
     if (logits_out)
         CU(dec, cudaMemcpyAsync(logits_out, dec->logits, (size_t)logit_rows * c.vocab_size * 4, cudaMemcpyDeviceToHost, dec->stream));
+    if (argmax_out)
+        CU(dec, cudaMemcpyAsync(dec->h_argmax, dec->d_argmax, (size_t)c.batch * 4, cudaMemcpyDeviceToHost, dec->stream));
+    CU(dec, cudaMemcpyAsync(dec->h_status, dec->d_status, 4, cudaMemcpyDeviceToHost, dec->stream));
+    CU(dec, cudaStreamSynchronize(dec->stream));
+    if (*dec->h_status != DEV_OK) {
+        int status = *dec->h_status;
+        cudaMemsetAsync(dec->d_status, 0, 16, dec->stream);
+        return device_status_to_code(dec, status);
+    }
+    if (argmax_out) std::memcpy(argmax_out, dec->h_argmax, (size_t)c.batch * 4);
+    dec->failed = false;
+    return TNSR_B200_OK;
+}
+
+// One new token per session, every session at its own position (no reference counterpart: the reference's
+// sessions advance together).  Session b writes its K/V row at positions[b] and attends rows 0 .. positions[b].
+int tnsr_b200_decoder_decode_ragged(tnsr_b200_decoder* dec, const uint32_t* tokens, const uint32_t* positions,
+                                    float* logits_out, uint32_t* argmax_out) {
+    if (!dec) return fail(nullptr, TNSR_B200_ERR_INVALID_ARGUMENT, "null decoder");
+    if (dec->failed) return fail(dec, TNSR_B200_ERR_FAILED_STATE, "decoder execution failed; reset the cache before reuse");
+    const tnsr_b200_config& c = dec->cfg;
+    if (!dec->bf16_path) return fail(dec, TNSR_B200_ERR_UNSUPPORTED, "ragged decode is implemented for bf16 weights only");
+    if (!tokens || !positions) return fail(dec, TNSR_B200_ERR_INVALID_ARGUMENT, "null token or position pointer");
+    if (c.logits_mode == TNSR_B200_LOGITS_NONE && logits_out)
+        return fail(dec, TNSR_B200_ERR_INVALID_ARGUMENT, "logits_out must be NULL when logits_mode is NONE");
+    for (uint32_t b = 0; b < c.batch; ++b) {
+        if (positions[b] >= c.capacity) return fail(dec, TNSR_B200_ERR_CAPACITY, "decoder context capacity exceeded");
+        if (tokens[b] >= c.vocab_size) return fail(dec, TNSR_B200_ERR_TOKEN_RANGE, "decoder token is outside the vocabulary");
+    }
+    CU(dec, cudaSetDevice(c.device));
+    int rc;
+    if ((rc = ensure_rows(dec, c.batch, c.batch))) return rc;
+    if (!dec->d_positions) {
+        if ((rc = dev_alloc(dec, (void**)&dec->d_positions, (size_t)c.batch * 4, true))) return rc;
+        CU(dec, cudaMallocHost((void**)&dec->h_positions, (size_t)c.batch * 4));
+    }
+    dec->failed = true;
+    std::memcpy(dec->h_tokens, tokens, (size_t)c.batch * 4);
+    std::memcpy(dec->h_positions, positions, (size_t)c.batch * 4);
+    CU(dec, cudaMemcpyAsync(dec->d_tokens, dec->h_tokens, (size_t)c.batch * 4, cudaMemcpyHostToDevice, dec->stream));
+    CU(dec, cudaMemcpyAsync(dec->d_positions, dec->h_positions, (size_t)c.batch * 4, cudaMemcpyHostToDevice, dec->stream));
+    const bool fuse_ids = c.logits_mode == TNSR_B200_LOGITS_NONE && argmax_out && dec->lm_candidates;
+    if ((rc = step_bf16(dec, dec->d_tokens, 1, 0, dec->d_positions, c.batch, fuse_ids ? dec->d_argmax : nullptr, true))) return rc;
+    if (argmax_out && !fuse_ids) {
+        rc = launch_argmax(dec->logits, dec->d_argmax, c.batch, c.vocab_size, c.vocab_size, dec->stream);
+        if (rc) { dec->error = thread_error(); return rc; }
+    }
+    if (logits_out)
+        CU(dec, cudaMemcpyAsync(logits_out, dec->logits, (size_t)c.batch * c.vocab_size * 4, cudaMemcpyDeviceToHost, dec->stream));
     if (argmax_out)
         CU(dec, cudaMemcpyAsync(dec->h_argmax, dec->d_argmax, (size_t)c.batch * 4, cudaMemcpyDeviceToHost, dec->stream));
     CU(dec, cudaMemcpyAsync(dec->h_status, dec->d_status, 4, cudaMemcpyDeviceToHost, dec->stream));

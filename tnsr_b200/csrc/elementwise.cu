@@ -35,12 +35,13 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 embedding_kernel(const T* __restrict__ tok, const T* __restrict__ pos, const uint32_t* __restrict__ ids,
                  float* __restrict__ out, uint32_t chunk, uint32_t position0,
-                 const uint32_t* __restrict__ d_position, uint32_t vocab, uint32_t width,
+                 const uint32_t* __restrict__ d_position, uint32_t position_stride, uint32_t vocab, uint32_t width,
                  int* __restrict__ d_status) {
     pdl_wait();
     pdl_trigger();
     const uint32_t r = blockIdx.x;
-    const uint32_t position = (d_position ? *d_position : position0) + r % chunk;
+    // position_stride 0: one position for all sessions; 1: d_position[session]
+    const uint32_t position = (d_position ? d_position[(r / chunk) * position_stride] : position0) + r % chunk;
     uint32_t id = ids[r];
     float* o = out + (size_t)r * width;
     if (id >= vocab) {
@@ -64,15 +65,15 @@ embedding_kernel(const T* __restrict__ tok, const T* __restrict__ pos, const uin
 
 int launch_embedding(const void* tok, const void* pos, const uint32_t* ids, float* out, uint32_t rows,
                      uint32_t chunk, uint32_t position0, const uint32_t* d_position, uint32_t vocab,
-                     uint32_t width, int dtype, int* d_status, cudaStream_t stream) {
+                     uint32_t width, int dtype, int* d_status, cudaStream_t stream, uint32_t position_stride) {
     if (rows == 0) return TNSR_B200_OK;
     if (chunk == 0) return TNSR_B200_ERR_INVALID_ARGUMENT;
     if (dtype == TNSR_B200_BF16)
         launch_kernel(embedding_kernel<bf16>, dim3(rows), dim3(128), 0, stream, (const bf16*)tok, (const bf16*)pos, ids, out,
-                      chunk, position0, d_position, vocab, width, d_status);
+                      chunk, position0, d_position, position_stride, vocab, width, d_status);
     else
         launch_kernel(embedding_kernel<float>, dim3(rows), dim3(128), 0, stream, (const float*)tok, (const float*)pos, ids, out,
-                      chunk, position0, d_position, vocab, width, d_status);
+                      chunk, position0, d_position, position_stride, vocab, width, d_status);
     count_launch();
     return check_launch("embedding");
 }

@@ -60,8 +60,9 @@ __device__ __forceinline__ void store_qkv(const EpiParams& P, uint32_t row, uint
     if (which == 0) {
         P.qkv.q[(size_t)row * d + c] = __float2bfloat16_rn(v);
     } else {
-        uint32_t pos = P.qkv.d_position ? *P.qkv.d_position : P.qkv.position;
-        size_t crow = (size_t)(row / P.qkv.chunk) * P.qkv.capacity + pos + row % P.qkv.chunk;
+        const uint32_t session = row / P.qkv.chunk;
+        uint32_t pos = P.qkv.d_position ? P.qkv.d_position[session * P.qkv.position_stride] : P.qkv.position;
+        size_t crow = (size_t)session * P.qkv.capacity + pos + row % P.qkv.chunk;
         (which == 1 ? P.qkv.k_cache : P.qkv.v_cache)[crow * d + c] = __float2bfloat16_rn(v);
     }
 }
@@ -315,7 +316,7 @@ __device__ __forceinline__ void epilogue_block(const EpiParams& P, float* stage,
             cbase = col0 % d;
             ld = d;
             base = which == 0 ? P.qkv.q : (which == 1 ? P.qkv.k_cache : P.qkv.v_cache);
-            pos = P.qkv.d_position ? *P.qkv.d_position : P.qkv.position;
+            pos = (P.qkv.d_position && !P.qkv.position_stride) ? *P.qkv.d_position : P.qkv.position;
         }
         fast = fast && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0;
         if (fast) {
@@ -334,7 +335,11 @@ __device__ __forceinline__ void epilogue_block(const EpiParams& P, float* stage,
                     v1 = act4(make_float4(v1.x + b1.x, v1.y + b1.y, v1.z + b1.z, v1.w + b1.w), act);
                     const uint32_t row = row0 + rr;
                     size_t orow;
-                    if (MODE == GEMM_QKV) orow = which == 0 ? row : (size_t)(row / P.qkv.chunk) * P.qkv.capacity + pos + row % P.qkv.chunk;
+                    if (MODE == GEMM_QKV) {
+                        const uint32_t session = row / P.qkv.chunk;
+                        const uint32_t p = P.qkv.position_stride ? P.qkv.d_position[session] : pos;   // ragged: one position per session
+                        orow = which == 0 ? row : (size_t)session * P.qkv.capacity + p + row % P.qkv.chunk;
+                    }
                     else orow = map_out_row(P.ep, row);
                     *reinterpret_cast<uint4*>(base + orow * ld + cbase + c8) =
                         make_uint4(pack_bf16x2(v0.x, v0.y), pack_bf16x2(v0.z, v0.w), pack_bf16x2(v1.x, v1.y), pack_bf16x2(v1.z, v1.w));

@@ -79,6 +79,19 @@ class B200Session:
                                                    position, lp, ap))
         return logits, argmax
 
+    def decode_ragged(self, tokens: np.ndarray, positions: np.ndarray, want_argmax: bool = True):
+        """One new token per session, session b at positions[b]: (logits [batch * vocab] or None, greedy ids or None)."""
+        tok = np.ascontiguousarray(tokens, dtype=np.uint32).reshape(-1)
+        pos = np.ascontiguousarray(positions, dtype=np.uint32).reshape(-1)
+        assert tok.size == self.batch and pos.size == self.batch
+        logits = None if self.logits_mode == "none" else np.empty(self.batch * self.vocab, dtype=np.float32)
+        lp = logits.ctypes.data_as(C.POINTER(C.c_float)) if logits is not None else None
+        argmax = np.empty(self.batch, dtype=np.uint32) if want_argmax else None
+        ap = argmax.ctypes.data_as(C.POINTER(C.c_uint32)) if want_argmax else None
+        u32p = C.POINTER(C.c_uint32)
+        self._check(lib().tnsr_b200_decoder_decode_ragged(self.handle, tok.ctypes.data_as(u32p), pos.ctypes.data_as(u32p), lp, ap))
+        return logits, argmax
+
     def decode_device(self, d_tokens_ptr: int, chunk: int, position: int, d_argmax_ptr: int) -> None:
         self._check(lib().tnsr_b200_decoder_decode_device(self.handle, d_tokens_ptr, chunk, position, d_argmax_ptr))
 
