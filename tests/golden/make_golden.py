@@ -95,7 +95,9 @@ def config0(activation):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of tninesling/tnsr>")
+    ref = sys.argv[1]
     data = literal_vectors()
     data["activations"] = activation_vectors(ref)
     with open(os.path.join(HERE, "reference_vectors.json"), "w") as f:
