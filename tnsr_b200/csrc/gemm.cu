@@ -24,6 +24,8 @@
 namespace tb {
 
 int g_gemm_engine = 0;
+// measurement switch: TNSR_B200_EPI16=0 keeps every tcgen05 GEMM at 8 epilogue warps
+static bool t_epi16 = [] { const char* v = std::getenv("TNSR_B200_EPI16"); return !(v && v[0] == '0'); }();
 
 struct EpiParams {
     GemmEpilogue ep;
@@ -182,19 +184,21 @@ static int launch_simple(const bf16* a, uint32_t lda, const bf16* bt, const EpiP
 constexpr int BM = 128;           // rows per tile = TMEM lanes
 constexpr int BK = 64;            // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;        // K per tcgen05.mma for 16-bit operands
-constexpr int TC_EPI_WARPS = 8;   // two warps per TMEM lane quarter, each taking every other 32-column chunk
-constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: epilogue
+// Epilogue warps per CTA (template parameter EPI): 8 = two per TMEM lane quarter, 16 = four per quarter; the warps of a
+// quarter take 32-column chunks in turn.  Warp 0: TMA, warp 1: MMA + TMEM owner, warps 2 .. EPI + 1: epilogue.
 constexpr uint32_t TC_STAGE_TILE_BYTES = 32 * 32 * 4;  // per-warp transpose buffer: 32 rows x 32 f32 columns
 
-template <int BN>
+template <int BN, int EPI>
 struct TcShape {
-    static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);  // 196 KB (160 KB at BN 32)
+    static constexpr int THREADS = 64 + 32 * EPI;
+    // 4 stages of 48 KB at BN 256 with 8 epilogue warps; 3 with 16 (their transpose buffers take 64 KB)
+    static constexpr int STAGES = BN >= 256 ? (EPI > 8 ? 3 : 4) : (BN >= 128 ? 6 : 8);
     static constexpr uint32_t A_BYTES = BM * BK * 2;
     static constexpr uint32_t B_BYTES = BN * BK * 2;
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators; power of two
     static constexpr uint32_t SMEM_BYTES =
-        STAGES * STAGE_BYTES + 1024 /* alignment slack */ + TC_EPI_WARPS * TC_STAGE_TILE_BYTES + 256 /* barriers */;
+        STAGES * STAGE_BYTES + 1024 /* alignment slack */ + EPI * TC_STAGE_TILE_BYTES + 256 /* barriers */;
 };
 
 // Instruction descriptor, kind::f16: f32 accumulator (bit 4), bf16 A (bit 7)
@@ -396,16 +400,18 @@ __device__ __forceinline__ void epilogue_block(const EpiParams& P, float* stage,
     __syncwarp();  // the buffer is reused by the next block
 }
 
-template <int BN, int MODE>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+template <int BN, int MODE, int EPI>
+__global__ void __launch_bounds__(64 + 32 * EPI, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams prm) {
-    using S = TcShape<BN>;
+    using S = TcShape<BN, EPI>;
+    constexpr int PER_QUARTER = EPI / 4;             // epilogue warps per TMEM lane quarter
+    constexpr uint32_t CHUNK_STRIDE = 32 * PER_QUARTER;
     extern __shared__ uint8_t smem_raw[];
     // 128-byte-swizzled tiles want a 1024-byte aligned base
     const uint32_t raw_addr = smem_u32(smem_raw);
     uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
     float* stage_tiles = reinterpret_cast<float*>(smem + S::STAGES * S::STAGE_BYTES);
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::STAGES * S::STAGE_BYTES + TC_EPI_WARPS * TC_STAGE_TILE_BYTES);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::STAGES * S::STAGE_BYTES + EPI * TC_STAGE_TILE_BYTES);
     uint64_t* empty_bar = full_bar + S::STAGES;
     uint64_t* acc_full = empty_bar + S::STAGES;   // [2]
     uint64_t* acc_empty = acc_full + 2;           // [2]
@@ -418,7 +424,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S::STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(acc_full + s, 1); mbar_init(acc_empty + s, TC_EPI_WARPS); }
+        for (int s = 0; s < 2; ++s) { mbar_init(acc_full + s, 1); mbar_init(acc_empty + s, EPI); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -482,8 +488,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     } else {
         // ---------------- epilogue warps ----------------
-        // TMEM lane quarter = warp % 4 (a warp may only read its own quarter); the two warps of a quarter
-        // take alternate 32-column chunks.
+        // TMEM lane quarter = warp % 4 (a warp may only read its own quarter); the warps of a quarter take the
+        // 32-column chunks in turn (`half` = this warp's place among them).
         const uint32_t quarter = warp & 3, half = (warp - 2) >> 2;
         float* stage = stage_tiles + (warp - 2) * (TC_STAGE_TILE_BYTES / 4);
         uint32_t it = 0;
@@ -497,7 +503,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // being accumulated (the rows are final: only this warp rewrites them, after this read)
             float4 res_pre[8];
             bool have_pre = false;
-            if (MODE == GEMM_PLAIN && prm.epi.ep.out_dtype == TNSR_B200_F32 && prm.epi.ep.residual && half * 32 < BN) {
+            if (MODE == GEMM_PLAIN && prm.epi.ep.out_dtype == TNSR_B200_F32 && prm.epi.ep.residual && half * 32 < (uint32_t)BN) {
                 const uint32_t col0 = tn * BN + half * 32;
                 if (row0 < prm.epi.m && col0 < prm.epi.n && f32_vector_path(prm.epi, col0)) {
                     load_residual_block(prm.epi, row0, col0, lane, res_pre);
@@ -530,7 +536,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
             } else {
 #pragma unroll 1
-                for (uint32_t c = half * 32; c < BN; c += 64) {
+                for (uint32_t c = half * 32; c < BN; c += CHUNK_STRIDE) {
                     float acc[32];
                     tmem_ld32(taddr + c, acc);
                     tmem_ld_wait();
@@ -586,22 +592,32 @@ static int sm_count() {
     return n;
 }
 
-template <int BN, int MODE>
-static int launch_tc_t(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& prm, cudaStream_t stream) {
-    using S = TcShape<BN>;
+template <int BN, int MODE, int EPI>
+static int launch_tc_e(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& prm, cudaStream_t stream) {
+    using S = TcShape<BN, EPI>;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        if (cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM_BYTES) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM_BYTES) != cudaSuccess)
             return check_launch("gemm_tc attribute");
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     uint32_t tiles = prm.tiles_m * prm.tiles_n;
     uint32_t grid = tiles < (uint32_t)sm_count() ? tiles : (uint32_t)sm_count();
-    launch_kernel(gemm_tc_kernel<BN, MODE>, dim3(grid), dim3(TC_THREADS), S::SMEM_BYTES, stream, ma, mb, prm);
+    launch_kernel(gemm_tc_kernel<BN, MODE, EPI>, dim3(grid), dim3(S::THREADS), S::SMEM_BYTES, stream, ma, mb, prm);
     count_launch();
     return check_launch("gemm_tc");
+}
+
+// Wide tiles with a bf16 epilogue (QKV routing, SwiGLU) and a short K: the main loop of a K = 768 tile is shorter than
+// 8 warps need to drain the previous accumulator, so these run 16 epilogue warps (and 3 ring stages instead of 4, which
+// is why longer K keeps 8: there the deeper ring is worth more).
+template <int BN, int MODE>
+static int launch_tc_t(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& prm, cudaStream_t stream) {
+    if (BN == 256 && (MODE == GEMM_QKV || MODE == GEMM_SWIGLU) && t_epi16 && prm.k <= 1024)
+        return launch_tc_e<BN, MODE, (BN == 256 && (MODE == GEMM_QKV || MODE == GEMM_SWIGLU)) ? 16 : 8>(ma, mb, prm, stream);
+    return launch_tc_e<BN, MODE, 8>(ma, mb, prm, stream);
 }
 
 template <int BN>
