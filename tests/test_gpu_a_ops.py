@@ -232,6 +232,33 @@ def test_gemm_bf16_few_rows_engine_matches_f64_with_and_without_split_k(shape):
     assert np.max(np.abs(default.cpu().numpy() - ref)) <= tol
 
 
+@pytest.mark.parametrize("shape", [(256, 768, 768), (256, 768, 2048), (1024, 768, 768), (300, 200, 136), (129, 132, 72),
+                                   (33, 36, 40), (4096, 768, 2048)])
+@pytest.mark.parametrize("activation", [-1, 1])
+def test_gemm_bf16_in_place_residual_update_equals_out_of_place(shape, activation):
+    """out == residual (how the decoder updates its residual stream): the tcgen05 engine hands the blocks to a TMA
+    reduce-add instead of reading and rewriting the rows.  One add per element, so the bits must equal the out-of-place
+    result of the same engine, block edges and clipped tiles included."""
+    m, n, k = shape
+    a, bt, ref = gemm_case(m, n, k, seed=31, scale=0.1)
+    rng = np.random.default_rng(32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    resid = rng.standard_normal((m, n)).astype(np.float32)
+    da, dbt, dbias, dres = dev(a, torch.bfloat16), dev(bt, torch.bfloat16), dev(bias), dev(resid)
+    apart = gemm_bf16(da, dbt, bias=dbias, residual=dres, activation=activation)
+    buf = dres.clone()
+    ok(lib().tnsr_b200_gemm_bf16(ptr(da), ptr(dbt), ptr(dbias), ptr(buf), ptr(buf), m, n, k, activation, 0, stream()))
+    torch.cuda.synchronize()
+    assert torch.equal(buf, apart)
+    if activation == -1:
+        assert np.max(np.abs(buf.cpu().numpy() - (ref + bias + resid))) <= 2e-3
+    twice = buf.clone()        # a second update accumulates on top of the first
+    ok(lib().tnsr_b200_gemm_bf16(ptr(da), ptr(dbt), ptr(dbias), ptr(twice), ptr(twice), m, n, k, activation, 0, stream()))
+    torch.cuda.synchronize()
+    again = gemm_bf16(da, dbt, bias=dbias, residual=buf, activation=activation)
+    assert torch.equal(twice, again)
+
+
 # ---- SwiGLU ----------------------------------------------------------------------
 def test_swiglu_elementwise(oracle):
     import json, os

@@ -24,6 +24,8 @@
 namespace tb {
 
 int g_gemm_engine = 0;
+// measurement switch: TNSR_B200_TMA_REDUCE=0 keeps the in-place residual update in the warps (read, add, store)
+static bool t_tma_reduce = [] { const char* v = std::getenv("TNSR_B200_TMA_REDUCE"); return !(v && v[0] == '0'); }();
 // measurement switch: TNSR_B200_EPI16=0 keeps every tcgen05 GEMM at 8 epilogue warps
 static bool t_epi16 = [] { const char* v = std::getenv("TNSR_B200_EPI16"); return !(v && v[0] == '0'); }();
 
@@ -212,6 +214,9 @@ struct TcParams {
     uint32_t k;
     uint32_t tiles_m, tiles_n;
     int* d_status;
+    // 1: f32 output accumulated in place on the residual (out == residual): the epilogue hands each 32 x 32 block of
+    // act(acc + bias) to a TMA reduce-add on `map_out` instead of reading, adding and storing the rows itself
+    uint32_t tma_reduce;
 };
 
 // Grouped tile order: 8 row-tiles share each column-tile before moving on, so a
@@ -263,6 +268,41 @@ __device__ __forceinline__ void load_residual_block(const EpiParams& P, uint32_t
         const uint32_t rr = it * 4 + rsub;
         r4[it] = (res && rr < rows) ? *reinterpret_cast<const float4*>(res + (size_t)(row0 + rr) * P.ep.ldr + col0 + c4)
                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+}
+
+// In-place residual update through TMA: the lane's accumulator row (+ bias, activation) goes into the warp's 4 KB
+// buffer in the 128-byte-swizzled layout of a 32-row x 32-column f32 box, and one bulk tensor reduce-add folds the
+// box into the residual stream in global memory.  The warp neither reads the residual nor issues stores; rows and
+// columns outside the matrix are clipped by the tensor map.  One add per element, so the result is the same
+// residual + value an explicit read-add-store gives.
+__device__ __forceinline__ void epilogue_block_reduce(const EpiParams& P, const CUtensorMap* map_out, float* stage,
+                                                      uint32_t row0, uint32_t col0, const float* acc, uint32_t lane) {
+    // the previous box of this warp must have been read out of the buffer
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    __syncwarp();
+    float4* row = reinterpret_cast<float4*>(stage) + lane * 8;
+    const bool bias_vec = P.ep.bias && (reinterpret_cast<uintptr_t>(P.ep.bias) & 15) == 0 && col0 + 32 <= P.n;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (bias_vec) {
+            b = __ldg(reinterpret_cast<const float4*>(P.ep.bias + col0 + 4 * g));
+        } else if (P.ep.bias) {
+            const uint32_t c = col0 + 4 * g;
+            b = make_float4(c < P.n ? P.ep.bias[c] : 0.f, c + 1 < P.n ? P.ep.bias[c + 1] : 0.f,
+                            c + 2 < P.n ? P.ep.bias[c + 2] : 0.f, c + 3 < P.n ? P.ep.bias[c + 3] : 0.f);
+        }
+        const float4 v = act4(make_float4(acc[4 * g] + b.x, acc[4 * g + 1] + b.y, acc[4 * g + 2] + b.z, acc[4 * g + 3] + b.w),
+                              P.ep.activation);
+        row[(g ^ lane) & 7] = v;     // 16-byte chunk g of row r sits at g ^ (r & 7)
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) {
+        asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                     ::"l"(map_out), "r"((int32_t)col0), "r"((int32_t)row0), "r"(smem_u32(stage)) : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
     }
 }
 
@@ -402,7 +442,8 @@ __device__ __forceinline__ void epilogue_block(const EpiParams& P, float* stage,
 
 template <int BN, int MODE, int EPI>
 __global__ void __launch_bounds__(64 + 32 * EPI, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams prm) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_out, TcParams prm) {
     using S = TcShape<BN, EPI>;
     constexpr int PER_QUARTER = EPI / 4;             // epilogue warps per TMEM lane quarter
     constexpr uint32_t CHUNK_STRIDE = 32 * PER_QUARTER;
@@ -503,7 +544,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // being accumulated (the rows are final: only this warp rewrites them, after this read)
             float4 res_pre[8];
             bool have_pre = false;
-            if (MODE == GEMM_PLAIN && prm.epi.ep.out_dtype == TNSR_B200_F32 && prm.epi.ep.residual && half * 32 < (uint32_t)BN) {
+            const bool reduce = MODE == GEMM_PLAIN && prm.tma_reduce;
+            if (!reduce && MODE == GEMM_PLAIN && prm.epi.ep.out_dtype == TNSR_B200_F32 && prm.epi.ep.residual && half * 32 < (uint32_t)BN) {
                 const uint32_t col0 = tn * BN + half * 32;
                 if (row0 < prm.epi.m && col0 < prm.epi.n && f32_vector_path(prm.epi, col0)) {
                     load_residual_block(prm.epi, row0, col0, lane, res_pre);
@@ -540,13 +582,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     float acc[32];
                     tmem_ld32(taddr + c, acc);
                     tmem_ld_wait();
-                    epilogue_block<MODE>(prm.epi, stage, row0, tn * BN + c, acc, lane, (have_pre && c == half * 32) ? res_pre : nullptr);
+                    const uint32_t col0 = tn * BN + c;
+                    if (reduce) {
+                        if (row0 < prm.epi.m && col0 < prm.epi.n) epilogue_block_reduce(prm.epi, &map_out, stage, row0, col0, acc, lane);
+                    } else {
+                        epilogue_block<MODE>(prm.epi, stage, row0, col0, acc, lane, (have_pre && c == half * 32) ? res_pre : nullptr);
+                    }
                 }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty + ab);
         }
+        // bulk reduce operations of this warp must be complete before the CTA gives up its shared memory
+        if (MODE == GEMM_PLAIN && prm.tma_reduce && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
 
     // ---------------- teardown ----------------
@@ -593,7 +642,7 @@ static int sm_count() {
 }
 
 template <int BN, int MODE, int EPI>
-static int launch_tc_e(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& prm, cudaStream_t stream) {
+static int launch_tc_e(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const TcParams& prm, cudaStream_t stream) {
     using S = TcShape<BN, EPI>;
     static bool configured[64] = {};
     int dev = 0;
@@ -605,7 +654,7 @@ static int launch_tc_e(const CUtensorMap& ma, const CUtensorMap& mb, const TcPar
     }
     uint32_t tiles = prm.tiles_m * prm.tiles_n;
     uint32_t grid = tiles < (uint32_t)sm_count() ? tiles : (uint32_t)sm_count();
-    launch_kernel(gemm_tc_kernel<BN, MODE, EPI>, dim3(grid), dim3(S::THREADS), S::SMEM_BYTES, stream, ma, mb, prm);
+    launch_kernel(gemm_tc_kernel<BN, MODE, EPI>, dim3(grid), dim3(S::THREADS), S::SMEM_BYTES, stream, ma, mb, mo, prm);
     count_launch();
     return check_launch("gemm_tc");
 }
@@ -614,19 +663,19 @@ static int launch_tc_e(const CUtensorMap& ma, const CUtensorMap& mb, const TcPar
 // 8 warps need to drain the previous accumulator, so these run 16 epilogue warps (and 3 ring stages instead of 4, which
 // is why longer K keeps 8: there the deeper ring is worth more).
 template <int BN, int MODE>
-static int launch_tc_t(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& prm, cudaStream_t stream) {
+static int launch_tc_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const TcParams& prm, cudaStream_t stream) {
     if (BN == 256 && (MODE == GEMM_QKV || MODE == GEMM_SWIGLU) && t_epi16 && prm.k <= 1024)
-        return launch_tc_e<BN, MODE, (BN == 256 && (MODE == GEMM_QKV || MODE == GEMM_SWIGLU)) ? 16 : 8>(ma, mb, prm, stream);
-    return launch_tc_e<BN, MODE, 8>(ma, mb, prm, stream);
+        return launch_tc_e<BN, MODE, (BN == 256 && (MODE == GEMM_QKV || MODE == GEMM_SWIGLU)) ? 16 : 8>(ma, mb, mo, prm, stream);
+    return launch_tc_e<BN, MODE, 8>(ma, mb, mo, prm, stream);
 }
 
 template <int BN>
-static int launch_tc_mode(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& prm, GemmMode mode, cudaStream_t stream) {
+static int launch_tc_mode(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const TcParams& prm, GemmMode mode, cudaStream_t stream) {
     switch (mode) {
-        case GEMM_PLAIN: return launch_tc_t<BN, GEMM_PLAIN>(ma, mb, prm, stream);
-        case GEMM_QKV: return launch_tc_t<BN, GEMM_QKV>(ma, mb, prm, stream);
-        case GEMM_SWIGLU: return launch_tc_t<BN, GEMM_SWIGLU>(ma, mb, prm, stream);
-        case GEMM_ARGMAX: return launch_tc_t<BN, GEMM_ARGMAX>(ma, mb, prm, stream);
+        case GEMM_PLAIN: return launch_tc_t<BN, GEMM_PLAIN>(ma, mb, mo, prm, stream);
+        case GEMM_QKV: return launch_tc_t<BN, GEMM_QKV>(ma, mb, mo, prm, stream);
+        case GEMM_SWIGLU: return launch_tc_t<BN, GEMM_SWIGLU>(ma, mb, mo, prm, stream);
+        case GEMM_ARGMAX: return launch_tc_t<BN, GEMM_ARGMAX>(ma, mb, mo, prm, stream);
     }
     return TNSR_B200_ERR_INVALID_ARGUMENT;
 }
@@ -703,12 +752,28 @@ static int launch_gemm_impl(const bf16* a, const bf16* bt, void* out, uint32_t l
     }
     if (mode == GEMM_ARGMAX) P.ldc = prm.tiles_n;
     if (tiles_n_out) *tiles_n_out = prm.tiles_n;
+    // f32 result accumulated in place on the residual stream: let TMA do the read-add-write (see epilogue_block_reduce)
+    CUtensorMap mo = ma;   // placeholder when unused
+    prm.tma_reduce = 0;
+    if (mode == GEMM_PLAIN && ep.out_dtype == TNSR_B200_F32 && ep.residual && ep.residual == out && ep.ldr == ldc &&
+        ep.rows_per_session == 0 && !ep.round_bf16 && t_tma_reduce && ldc % 4 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) {
+        EncodeTiledFn fn = encode_fn();
+        cuuint64_t dims[2] = {n, m};
+        cuuint64_t strides[1] = {(cuuint64_t)ldc * 4};
+        cuuint32_t box[2] = {32, 32};
+        cuuint32_t estr[2] = {1, 1};
+        if (fn && fn(&mo, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+            prm.tma_reduce = 1;
+        else
+            mo = ma;
+    }
     prm.epi = P;
     switch (bn) {
-        case 256: return launch_tc_mode<256>(ma, mb, prm, mode, stream);
-        case 128: return launch_tc_mode<128>(ma, mb, prm, mode, stream);
-        case 64: return launch_tc_mode<64>(ma, mb, prm, mode, stream);
-        default: return launch_tc_mode<32>(ma, mb, prm, mode, stream);
+        case 256: return launch_tc_mode<256>(ma, mb, mo, prm, mode, stream);
+        case 128: return launch_tc_mode<128>(ma, mb, mo, prm, mode, stream);
+        case 64: return launch_tc_mode<64>(ma, mb, mo, prm, mode, stream);
+        default: return launch_tc_mode<32>(ma, mb, mo, prm, mode, stream);
     }
 }
 
