@@ -166,3 +166,34 @@ def test_config4_full_width_chunking_invariance_and_determinism():
     agree = (whole == split).all(axis=0)
     assert agree.mean() >= 0.5
     assert whole.min() >= 0 and whole.max() < cfg.vocab_size
+
+
+def test_config4_wide_tile_epilogues_agree_with_narrow_tile_epilogues():
+    """32 sessions x 96 tokens give the projections enough rows for 256-column tiles, whose QKV and SwiGLU epilogues run
+    sixteen warps and write through bulk tensor stores; 8 sessions take narrower tiles with per-lane stores.  The
+    accumulation order over K does not depend on the tile shape, so the first 8 sessions must come out bit-identical:
+    K/V rows of the first and the last layer and the greedy continuation."""
+    cfg = GptConfig(vocab_size=32000, max_sequence_length=2048, embed_dim=768, num_heads=12, feed_forward_dim=2048,
+                    num_layers=12, layer_norm_epsilon=1e-5, activation="swiglu", weight_dtype="bf16")
+    arrays = normal_model_arrays(cfg, seed=5, std=0.02)
+    prompt_len, steps = 96, 6
+    ids = np.random.default_rng(56).integers(0, cfg.vocab_size, size=(32, prompt_len)).astype(np.uint32)
+
+    def run(batch):
+        s = B200Session(cfg, batch, 128, logits_mode="none")
+        for i, a in enumerate(arrays):
+            s.refresh(i, a)
+        _, nxt = s.decode_full(ids[:batch], 0)
+        out = [nxt.copy()]
+        for step in range(steps):
+            _, nxt = s.decode_full(nxt.reshape(batch, 1), prompt_len + step)
+            out.append(nxt.copy())
+        caches = [s.read_cache(i) for i in (0, 1, 2 * cfg.num_layers - 2, 2 * cfg.num_layers - 1)]
+        s.close()
+        return np.stack(out), caches
+
+    wide_ids, wide = run(32)
+    narrow_ids, narrow = run(8)
+    for w, n in zip(wide, narrow):
+        assert np.array_equal(w[:8, :prompt_len].view(np.uint32), n[:, :prompt_len].view(np.uint32))
+    assert np.array_equal(wide_ids[:, :8], narrow_ids)

@@ -24,6 +24,8 @@
 namespace tb {
 
 int g_gemm_engine = 0;
+// measurement switch: TNSR_B200_TMA_STORE=0 keeps the bf16 epilogues on per-lane stores
+static bool t_tma_store = [] { const char* v = std::getenv("TNSR_B200_TMA_STORE"); return !(v && v[0] == '0'); }();
 // measurement switch: TNSR_B200_TMA_REDUCE=0 keeps the in-place residual update in the warps (read, add, store)
 static bool t_tma_reduce = [] { const char* v = std::getenv("TNSR_B200_TMA_REDUCE"); return !(v && v[0] == '0'); }();
 // measurement switch: TNSR_B200_EPI16=0 keeps every tcgen05 GEMM at 8 epilogue warps
@@ -217,6 +219,9 @@ struct TcParams {
     // 1: f32 output accumulated in place on the residual (out == residual): the epilogue hands each 32 x 32 block of
     // act(acc + bias) to a TMA reduce-add on `map_out` instead of reading, adding and storing the rows itself
     uint32_t tma_reduce;
+    // 1: bf16 destinations are written with bulk tensor stores of 32-row blocks (map_out; map_k / map_v for the caches
+    // of the QKV routing) instead of per-lane stores
+    uint32_t tma_store;
 };
 
 // Grouped tile order: 8 row-tiles share each column-tile before moving on, so a
@@ -302,6 +307,77 @@ __device__ __forceinline__ void epilogue_block_reduce(const EpiParams& P, const 
     if (lane == 0) {
         asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
                      ::"l"(map_out), "r"((int32_t)col0), "r"((int32_t)row0), "r"(smem_u32(stage)) : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+}
+
+// bf16 destinations through TMA: bias / activation / SwiGLU and the conversion happen on the accumulator row the lane
+// already holds; the 32-row block of bf16 goes into the warp's buffer in the swizzled layout of the store box (64-byte
+// rows, or 32-byte rows after SwiGLU) and one bulk tensor store writes it: no read-back pass, no per-lane stores.
+// The QKV routing stores a block either into q or, as rows pos + t of one session, into the K or V cache (blocks of
+// 32 rows never straddle sessions: the host checks chunk % 32 == 0).
+template <int MODE>
+__device__ __forceinline__ void epilogue_block_store(const EpiParams& P, const CUtensorMap* map_out, const CUtensorMap* map_k,
+                                                     const CUtensorMap* map_v, float* stage, uint32_t row0, uint32_t col0,
+                                                     const float* acc, uint32_t lane, uint32_t parity) {
+    // the 4 KB buffer holds two blocks; the store of the block before last must have been read out of its half
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+    __syncwarp();
+    stage += (parity & 1u) * 512;   // floats: 2 KB halves
+    float b[32];
+    if (P.ep.bias && (reinterpret_cast<uintptr_t>(P.ep.bias) & 15) == 0 && col0 + 32 <= P.n) {
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            const float4 t = __ldg(reinterpret_cast<const float4*>(P.ep.bias + col0 + 4 * g));
+            b[4 * g] = t.x; b[4 * g + 1] = t.y; b[4 * g + 2] = t.z; b[4 * g + 3] = t.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) b[i] = (P.ep.bias && col0 + i < P.n) ? P.ep.bias[col0 + i] : 0.0f;
+    }
+    uint4* st = reinterpret_cast<uint4*>(stage);
+    const uint32_t sm = smem_u32(stage);
+    if (MODE == GEMM_SWIGLU) {
+        uint32_t p[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            p[j] = pack_bf16x2(fast_silu(acc[2 * j] + b[2 * j]) * (acc[16 + 2 * j] + b[16 + 2 * j]),
+                               fast_silu(acc[2 * j + 1] + b[2 * j + 1]) * (acc[17 + 2 * j] + b[17 + 2 * j]));
+        // 32-byte rows, 32-byte swizzle: 16-byte chunk c of row r at c ^ ((r >> 2) & 1)
+        st[lane * 2 + (0 ^ ((lane >> 2) & 1))] = make_uint4(p[0], p[1], p[2], p[3]);
+        st[lane * 2 + (1 ^ ((lane >> 2) & 1))] = make_uint4(p[4], p[5], p[6], p[7]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                         ::"l"(map_out), "r"((int32_t)(col0 / 2)), "r"((int32_t)row0), "r"(sm) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        return;
+    }
+    const int act = MODE == GEMM_QKV ? ACT_NONE : P.ep.activation;
+    uint32_t p[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+        p[j] = pack_bf16x2(apply_activation(acc[2 * j] + b[2 * j], act), apply_activation(acc[2 * j + 1] + b[2 * j + 1], act));
+    // 64-byte rows, 64-byte swizzle: 16-byte chunk c of row r at c ^ ((r >> 1) & 3)
+#pragma unroll
+    for (uint32_t c = 0; c < 4; ++c)
+        st[lane * 4 + (c ^ ((lane >> 1) & 3))] = make_uint4(p[4 * c], p[4 * c + 1], p[4 * c + 2], p[4 * c + 3]);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) {
+        if (MODE == GEMM_QKV && col0 >= P.qkv.d) {
+            const uint32_t which = col0 / P.qkv.d, c = col0 % P.qkv.d;
+            const uint32_t pos = P.qkv.d_position ? *P.qkv.d_position : P.qkv.position;
+            const uint32_t session = row0 / P.qkv.chunk, t0 = row0 % P.qkv.chunk;
+            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+                         ::"l"(which == 1 ? map_k : map_v), "r"((int32_t)c), "r"((int32_t)(pos + t0)), "r"((int32_t)session), "r"(sm)
+                         : "memory");
+        } else {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                         ::"l"(map_out), "r"((int32_t)col0), "r"((int32_t)row0), "r"(sm) : "memory");
+        }
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
     }
 }
@@ -443,7 +519,8 @@ __device__ __forceinline__ void epilogue_block(const EpiParams& P, float* stage,
 template <int BN, int MODE, int EPI>
 __global__ void __launch_bounds__(64 + 32 * EPI, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ CUtensorMap map_out, TcParams prm) {
+               const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_k,
+               const __grid_constant__ CUtensorMap map_v, TcParams prm) {
     using S = TcShape<BN, EPI>;
     constexpr int PER_QUARTER = EPI / 4;             // epilogue warps per TMEM lane quarter
     constexpr uint32_t CHUNK_STRIDE = 32 * PER_QUARTER;
@@ -533,7 +610,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // 32-column chunks in turn (`half` = this warp's place among them).
         const uint32_t quarter = warp & 3, half = (warp - 2) >> 2;
         float* stage = stage_tiles + (warp - 2) * (TC_STAGE_TILE_BYTES / 4);
-        uint32_t it = 0;
+        uint32_t it = 0, store_parity = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
             const uint32_t ab = it & 1, aphase = (it >> 1) & 1;
@@ -585,6 +662,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t col0 = tn * BN + c;
                     if (reduce) {
                         if (row0 < prm.epi.m && col0 < prm.epi.n) epilogue_block_reduce(prm.epi, &map_out, stage, row0, col0, acc, lane);
+                    } else if (prm.tma_store) {
+                        if (row0 < prm.epi.m && col0 < prm.epi.n)
+                            epilogue_block_store<MODE>(prm.epi, &map_out, &map_k, &map_v, stage, row0, col0, acc, lane, store_parity++);
                     } else {
                         epilogue_block<MODE>(prm.epi, stage, row0, col0, acc, lane, (have_pre && c == half * 32) ? res_pre : nullptr);
                     }
@@ -595,7 +675,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (lane == 0) mbar_arrive(acc_empty + ab);
         }
         // bulk reduce operations of this warp must be complete before the CTA gives up its shared memory
-        if (MODE == GEMM_PLAIN && prm.tma_reduce && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (((MODE == GEMM_PLAIN && prm.tma_reduce) || prm.tma_store) && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
 
     // ---------------- teardown ----------------
@@ -642,7 +722,7 @@ static int sm_count() {
 }
 
 template <int BN, int MODE, int EPI>
-static int launch_tc_e(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const TcParams& prm, cudaStream_t stream) {
+static int launch_tc_e(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap* mo, const TcParams& prm, cudaStream_t stream) {
     using S = TcShape<BN, EPI>;
     static bool configured[64] = {};
     int dev = 0;
@@ -654,7 +734,7 @@ static int launch_tc_e(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
     }
     uint32_t tiles = prm.tiles_m * prm.tiles_n;
     uint32_t grid = tiles < (uint32_t)sm_count() ? tiles : (uint32_t)sm_count();
-    launch_kernel(gemm_tc_kernel<BN, MODE, EPI>, dim3(grid), dim3(S::THREADS), S::SMEM_BYTES, stream, ma, mb, mo, prm);
+    launch_kernel(gemm_tc_kernel<BN, MODE, EPI>, dim3(grid), dim3(S::THREADS), S::SMEM_BYTES, stream, ma, mb, mo[0], mo[1], mo[2], prm);
     count_launch();
     return check_launch("gemm_tc");
 }
@@ -663,14 +743,14 @@ static int launch_tc_e(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
 // 8 warps need to drain the previous accumulator, so these run 16 epilogue warps (and 3 ring stages instead of 4, which
 // is why longer K keeps 8: there the deeper ring is worth more).
 template <int BN, int MODE>
-static int launch_tc_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const TcParams& prm, cudaStream_t stream) {
+static int launch_tc_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap* mo, const TcParams& prm, cudaStream_t stream) {
     if (BN == 256 && (MODE == GEMM_QKV || MODE == GEMM_SWIGLU) && t_epi16 && prm.k <= 1024)
         return launch_tc_e<BN, MODE, (BN == 256 && (MODE == GEMM_QKV || MODE == GEMM_SWIGLU)) ? 16 : 8>(ma, mb, mo, prm, stream);
     return launch_tc_e<BN, MODE, 8>(ma, mb, mo, prm, stream);
 }
 
 template <int BN>
-static int launch_tc_mode(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const TcParams& prm, GemmMode mode, cudaStream_t stream) {
+static int launch_tc_mode(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap* mo, const TcParams& prm, GemmMode mode, cudaStream_t stream) {
     switch (mode) {
         case GEMM_PLAIN: return launch_tc_t<BN, GEMM_PLAIN>(ma, mb, mo, prm, stream);
         case GEMM_QKV: return launch_tc_t<BN, GEMM_QKV>(ma, mb, mo, prm, stream);
@@ -753,8 +833,9 @@ static int launch_gemm_impl(const bf16* a, const bf16* bt, void* out, uint32_t l
     if (mode == GEMM_ARGMAX) P.ldc = prm.tiles_n;
     if (tiles_n_out) *tiles_n_out = prm.tiles_n;
     // f32 result accumulated in place on the residual stream: let TMA do the read-add-write (see epilogue_block_reduce)
-    CUtensorMap mo = ma;   // placeholder when unused
+    CUtensorMap mo[3] = {ma, ma, ma};   // output map, K-cache map, V-cache map; placeholders when unused
     prm.tma_reduce = 0;
+    prm.tma_store = 0;
     if (mode == GEMM_PLAIN && ep.out_dtype == TNSR_B200_F32 && ep.residual && ep.residual == out && ep.ldr == ldc &&
         ep.rows_per_session == 0 && !ep.round_bf16 && t_tma_reduce && ldc % 4 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) {
         EncodeTiledFn fn = encode_fn();
@@ -762,11 +843,49 @@ static int launch_gemm_impl(const bf16* a, const bf16* bt, void* out, uint32_t l
         cuuint64_t strides[1] = {(cuuint64_t)ldc * 4};
         cuuint32_t box[2] = {32, 32};
         cuuint32_t estr[2] = {1, 1};
-        if (fn && fn(&mo, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        if (fn && fn(&mo[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
             prm.tma_reduce = 1;
         else
-            mo = ma;
+            mo[0] = ma;
+    }
+    // bf16 destinations: bulk tensor stores of 32-row blocks (see epilogue_block_store).  Measured: it pays where the
+    // epilogue is the bottleneck and sixteen warps share the work -- the QKV and SwiGLU epilogues of wide tiles with a
+    // short K (prefill 26.4 -> 25.8 ms) -- and costs 10 % on the plain bf16 epilogue with eight warps, which keeps
+    // per-lane stores.
+    if (t_tma_store && (mode == GEMM_QKV || mode == GEMM_SWIGLU) && bn == 256 && k <= 1024 && ep.rows_per_session == 0 &&
+        !ep.round_bf16) {
+        EncodeTiledFn fn = encode_fn();
+        auto bf16_map = [&](CUtensorMap* map, void* base, uint64_t cols, uint64_t rows, uint64_t ld, uint32_t box_cols,
+                            CUtensorMapSwizzle swz) {
+            if (!fn || !base || reinterpret_cast<uintptr_t>(base) % 16 != 0 || ld % 8 != 0) return false;
+            cuuint64_t dims[2] = {cols, rows};
+            cuuint64_t strides[1] = {ld * 2};
+            cuuint32_t box[2] = {box_cols, 32};
+            cuuint32_t estr[2] = {1, 1};
+            return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      swz, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+        };
+        bool okm = false;
+        if (mode == GEMM_PLAIN) {
+            okm = bf16_map(&mo[0], out, n, m, ldc, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+        } else if (mode == GEMM_SWIGLU) {
+            okm = bf16_map(&mo[0], out, n / 2, m, ldc, 16, CU_TENSOR_MAP_SWIZZLE_32B);
+        } else if (qkv && qkv->chunk % 32 == 0 && qkv->d % 32 == 0 && qkv->position_stride == 0 && m % qkv->chunk == 0) {
+            okm = bf16_map(&mo[0], qkv->q, qkv->d, m, qkv->d, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+            for (int which = 1; okm && which <= 2; ++which) {
+                void* base = which == 1 ? (void*)qkv->k_cache : (void*)qkv->v_cache;
+                if (!base || reinterpret_cast<uintptr_t>(base) % 16 != 0) { okm = false; break; }
+                cuuint64_t dims[3] = {qkv->d, qkv->capacity, m / qkv->chunk};
+                cuuint64_t strides[2] = {(cuuint64_t)qkv->d * 2, (cuuint64_t)qkv->capacity * qkv->d * 2};
+                cuuint32_t box[3] = {32, 32, 1};
+                cuuint32_t estr[3] = {1, 1, 1};
+                okm = fn(&mo[which], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+            }
+        }
+        if (okm) prm.tma_store = 1;
+        else mo[0] = mo[1] = mo[2] = ma;
     }
     prm.epi = P;
     switch (bn) {
