@@ -319,7 +319,7 @@ __device__ __forceinline__ void epilogue_block_reduce(const EpiParams& P, const 
 template <int MODE>
 __device__ __forceinline__ void epilogue_block_store(const EpiParams& P, const CUtensorMap* map_out, const CUtensorMap* map_k,
                                                      const CUtensorMap* map_v, float* stage, uint32_t row0, uint32_t col0,
-                                                     const float* acc, uint32_t lane, uint32_t parity) {
+                                                     const float* acc, uint32_t lane, uint32_t parity, uint32_t qkv_pos) {
     // the 4 KB buffer holds two blocks; the store of the block before last must have been read out of its half
     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
     __syncwarp();
@@ -369,7 +369,7 @@ __device__ __forceinline__ void epilogue_block_store(const EpiParams& P, const C
     if (lane == 0) {
         if (MODE == GEMM_QKV && col0 >= P.qkv.d) {
             const uint32_t which = col0 / P.qkv.d, c = col0 % P.qkv.d;
-            const uint32_t pos = P.qkv.d_position ? *P.qkv.d_position : P.qkv.position;
+            const uint32_t pos = qkv_pos;   // read once per warp, not once per block: a dependent global load on the store's path
             const uint32_t session = row0 / P.qkv.chunk, t0 = row0 % P.qkv.chunk;
             asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
                          ::"l"(which == 1 ? map_k : map_v), "r"((int32_t)c), "r"((int32_t)(pos + t0)), "r"((int32_t)session), "r"(sm)
@@ -611,6 +611,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t quarter = warp & 3, half = (warp - 2) >> 2;
         float* stage = stage_tiles + (warp - 2) * (TC_STAGE_TILE_BYTES / 4);
         uint32_t it = 0, store_parity = 0;
+        const uint32_t qkv_pos = (MODE == GEMM_QKV && prm.tma_store)
+                                     ? (prm.epi.qkv.d_position ? *prm.epi.qkv.d_position : prm.epi.qkv.position) : 0u;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
             const uint32_t ab = it & 1, aphase = (it >> 1) & 1;
@@ -664,7 +666,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         if (row0 < prm.epi.m && col0 < prm.epi.n) epilogue_block_reduce(prm.epi, &map_out, stage, row0, col0, acc, lane);
                     } else if (prm.tma_store) {
                         if (row0 < prm.epi.m && col0 < prm.epi.n)
-                            epilogue_block_store<MODE>(prm.epi, &map_out, &map_k, &map_v, stage, row0, col0, acc, lane, store_parity++);
+                            epilogue_block_store<MODE>(prm.epi, &map_out, &map_k, &map_v, stage, row0, col0, acc, lane, store_parity++, qkv_pos);
                     } else {
                         epilogue_block<MODE>(prm.epi, stage, row0, col0, acc, lane, (have_pre && c == half * 32) ? res_pre : nullptr);
                     }
