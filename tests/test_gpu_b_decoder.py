@@ -148,7 +148,7 @@ def oracle_model(oracle, cfg, arrays):
 
 @pytest.mark.parametrize("engine", [1, 0])
 @pytest.mark.parametrize("activation,d,heads,f", [("swiglu", 128, 2, 256), ("relu", 128, 2, 256), ("gelu", 96, 3, 104),
-                                                  ("swiglu", 64, 2, 40), ("swiglu", 72, 3, 36)])
+                                                  ("swiglu", 64, 2, 40), ("swiglu", 72, 3, 36), ("swiglu", 256, 2, 264)])
 def test_bf16_session_matches_checker_within_2e2(oracle, activation, d, heads, f, engine):
     """bf16 tensor-core path vs the f32 checker on bf16-rounded weights: <= 2e-2 relative."""
     from tnsr_b200 import _native
@@ -170,6 +170,26 @@ def test_bf16_session_matches_checker_within_2e2(oracle, activation, d, heads, f
             position += chunk
     finally:
         _native.lib().tnsr_b200_set_gemm_engine(0)
+
+
+@pytest.mark.parametrize("heads", [2, 1])
+def test_bf16_session_long_chunks_take_the_tcgen05_prefill_kernel(oracle, heads):
+    """Chunks of 32 rows and more at head width 64 (and 128: generic kernel) against the checker: the first at position 0,
+    the second on top of 41 cached rows, with a single-token step in between."""
+    cfg, model, rounded = small_bf16_model("swiglu", 128, heads, 256)
+    m = oracle_model(oracle, cfg, rounded)
+    rng = np.random.default_rng(8)
+    batch, total = 3, 74
+    ids = rng.integers(0, cfg.vocab_size, size=(batch, total)).astype(np.uint32)
+    full = m.forward(ids)
+    decoder = model.decoder(Backend.Cuda, batch)
+    position = 0
+    for chunk in (40, 1, 33):
+        tokens = ids[:, position:position + chunk].reshape(-1).tolist()
+        got = decoder.decode(tokens).reshape(batch, chunk, cfg.vocab_size)
+        assert np.all(np.isfinite(got))
+        assert rel_err(got, full[:, position:position + chunk]) <= 2e-2
+        position += chunk
 
 
 def test_bf16_session_logits_modes_argmax_and_device_loop(oracle):
