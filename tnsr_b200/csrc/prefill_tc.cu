@@ -36,6 +36,8 @@
 //
 // Every wait is bounded; a wait that gives up raises the CTA's abort flag, the
 // roles fall through to the common teardown and the status word is set.
+#include <algorithm>
+
 #include "tc_common.cuh"
 
 namespace tb {
@@ -64,7 +66,7 @@ __device__ __forceinline__ float pt_max4(const float* v) { return fmaxf(fmaxf(v[
 
 struct PtParams {
     bf16* out;
-    uint32_t chunk, position, heads, q_tiles;
+    uint32_t chunk, position, heads, q_tiles, sessions;
     float scale_log2;
     int* d_status;
 };
@@ -91,15 +93,26 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // the longest query tiles (most key blocks) are scheduled first
-    const uint32_t q_tile_index = prm.q_tiles - 1 - blockIdx.x;
-    const uint32_t q0 = q_tile_index * PT_BQ, h = blockIdx.y, s = blockIdx.z;
-    const uint32_t last_q = min(q0 + PT_BQ, prm.chunk) - 1;
-    const uint32_t total = prm.position + last_q + 1;              // keys visible to the tile's last query
-    const uint32_t n_blocks = (total + PT_BK - 1) / PT_BK;
+    uint64_t* q_empty = reinterpret_cast<uint64_t*>(tmem_slot + 2);   // [1]
+
+    // Work items = (query tile, head, session), the longest query tiles (most key blocks) first; CTA c takes items
+    // c, c + grid, c + 2 grid, ...  Every role walks the same list with the same counters, so the barrier phases
+    // (a running count of key blocks for the K/V ring, S, P and O; a running count of items for Q) stay in step.
+    const uint32_t per_tile = prm.heads * prm.sessions;
+    const uint32_t total_items = prm.q_tiles * per_tile;
+    auto item_coords = [&](uint32_t item, uint32_t& q0, uint32_t& h, uint32_t& s, uint32_t& n_blocks) {
+        const uint32_t q_tile_index = prm.q_tiles - 1 - item / per_tile, rem = item % per_tile;
+        q0 = q_tile_index * PT_BQ;
+        h = rem % prm.heads;
+        s = rem / prm.heads;
+        const uint32_t last_q = min(q0 + PT_BQ, prm.chunk) - 1;
+        const uint32_t total = prm.position + last_q + 1;          // keys visible to the tile's last query
+        n_blocks = (total + PT_BK - 1) / PT_BK;
+    };
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
+        mbar_init(q_empty, 1);
         for (int i = 0; i < PT_KV_STAGES; ++i) { mbar_init(kv_full + i, 1); mbar_init(kv_empty + i, 1); }
         mbar_init(s_full, 1);
         mbar_init(p_full, 8);
@@ -122,76 +135,84 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            mbar_expect_tx(q_full, PT_TILE_BYTES);
-            tma_load_3d(q_tile, &map_q, (int32_t)(h * PT_HD), (int32_t)q0, (int32_t)s, q_full);
-            uint32_t stage = 0, phase = 0;
-            for (uint32_t j = 0; j < n_blocks; ++j) {
-                if (!mbar_wait(kv_empty + stage, phase ^ 1, abort_flag)) break;
-                uint8_t* dst = kv_ring + stage * PT_KV_BYTES;
-                mbar_expect_tx(kv_full + stage, PT_KV_BYTES);
-                tma_load_3d(dst, &map_k, (int32_t)(h * PT_HD), (int32_t)(j * PT_BK), (int32_t)s, kv_full + stage);
-                tma_load_3d(dst + PT_TILE_BYTES, &map_v, (int32_t)(h * PT_HD), (int32_t)(j * PT_BK), (int32_t)s, kv_full + stage);
-                if (++stage == PT_KV_STAGES) { stage = 0; phase ^= 1; }
+            uint32_t g = 0, it = 0;     // key blocks and items so far
+            bool ok = true;
+            for (uint32_t item = blockIdx.x; ok && item < total_items; item += gridDim.x, ++it) {
+                uint32_t q0, h, s, n_blocks;
+                item_coords(item, q0, h, s, n_blocks);
+                // the Q tile is free once every S product of the previous item has been computed
+                if (it > 0 && !mbar_wait(q_empty, (it - 1) & 1, abort_flag)) break;
+                mbar_expect_tx(q_full, PT_TILE_BYTES);
+                tma_load_3d(q_tile, &map_q, (int32_t)(h * PT_HD), (int32_t)q0, (int32_t)s, q_full);
+                for (uint32_t j = 0; j < n_blocks; ++j, ++g) {
+                    const uint32_t stage = g % PT_KV_STAGES;
+                    if (!mbar_wait(kv_empty + stage, ((g / PT_KV_STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    uint8_t* dst = kv_ring + stage * PT_KV_BYTES;
+                    mbar_expect_tx(kv_full + stage, PT_KV_BYTES);
+                    tma_load_3d(dst, &map_k, (int32_t)(h * PT_HD), (int32_t)(j * PT_BK), (int32_t)s, kv_full + stage);
+                    tma_load_3d(dst + PT_TILE_BYTES, &map_v, (int32_t)(h * PT_HD), (int32_t)(j * PT_BK), (int32_t)s, kv_full + stage);
+                }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             const uint64_t qdesc = make_kmajor_sw128_desc(smem_u32(q_tile));
-            // S_j = Q K_j^T : four K steps of 16 dims, +32 bytes inside the swizzle row each
+            // S = Q K^T for the block in ring slot `stage`: four K steps of 16 dims, +32 bytes inside the swizzle row each
             auto issue_s = [&](uint32_t stage) {
                 const uint64_t kdesc = make_kmajor_sw128_desc(smem_u32(kv_ring + stage * PT_KV_BYTES));
 #pragma unroll
                 for (uint32_t kk = 0; kk < PT_HD / 16; ++kk) umma_bf16(tmem_base, qdesc + kk * 2, kdesc + kk * 2, PT_IDESC_S, kk != 0);
                 umma_commit(s_full);
             };
-            bool ok = mbar_wait(q_full, 0, abort_flag);
-            if (ok) ok = mbar_wait(kv_full + 0, 0, abort_flag);
-            if (ok) {
+            uint32_t g = 0, it = 0;
+            bool ok = true;
+            for (uint32_t item = blockIdx.x; ok && item < total_items; item += gridDim.x, ++it) {
+                uint32_t q0, h, s, n_blocks;
+                item_coords(item, q0, h, s, n_blocks);
+                if (!mbar_wait(q_full, it & 1, abort_flag)) break;
+                if (!mbar_wait(kv_full + g % PT_KV_STAGES, (g / PT_KV_STAGES) & 1, abort_flag)) break;
+                // the score buffer is free: its last reader signalled p_full of the previous block, which was waited for below
                 tc_fence_after();
-                issue_s(0);
-            }
-            for (uint32_t j = 0; ok && j < n_blocks; ++j) {
-                const uint32_t stage = j % PT_KV_STAGES;
-                // P_j is in place and the softmax warps are done with S_j
-                if (!mbar_wait(p_full, j & 1, abort_flag)) { ok = false; break; }
-                if (j + 1 < n_blocks) {
-                    const uint32_t next = (j + 1) % PT_KV_STAGES;
-                    if (!mbar_wait(kv_full + next, ((j + 1) / PT_KV_STAGES) & 1, abort_flag)) { ok = false; break; }
+                issue_s(g % PT_KV_STAGES);
+                if (n_blocks == 1) umma_commit(q_empty);
+                for (uint32_t j = 0; j < n_blocks; ++j) {
+                    const uint32_t b = g + j, stage = b % PT_KV_STAGES;
+                    // P_j is in place and the softmax warps are done with S_j
+                    if (!mbar_wait(p_full, b & 1, abort_flag)) { ok = false; break; }
+                    if (j + 1 < n_blocks) {
+                        const uint32_t next = (b + 1) % PT_KV_STAGES;
+                        if (!mbar_wait(kv_full + next, ((b + 1) / PT_KV_STAGES) & 1, abort_flag)) { ok = false; break; }
+                        tc_fence_after();
+                        issue_s(next);
+                        if (j + 2 == n_blocks) umma_commit(q_empty);   // that was the item's last S product
+                    }
                     tc_fence_after();
-                    issue_s(next);
-                }
-                tc_fence_after();
-                // O_j = P_j V_j : eight K steps of 16 keys.  P: K-major, keys 0-63 in the K slot of this stage, keys
-                // 64-127 in the upper tile; V: MN-major, 16 keys = two 8-key groups 1024 bytes apart, so each step
-                // starts 2048 bytes further on.
-                const uint32_t p_lower = smem_u32(kv_ring + stage * PT_KV_BYTES);
-                const uint32_t v_addr = p_lower + PT_TILE_BYTES;
+                    // O_j = P_j V_j : eight K steps of 16 keys.  P: K-major, keys 0-63 in the K slot of this stage, keys
+                    // 64-127 in the upper tile; V: MN-major, 16 keys = two 8-key groups 1024 bytes apart, so each step
+                    // starts 2048 bytes further on.
+                    const uint32_t p_lower = smem_u32(kv_ring + stage * PT_KV_BYTES);
+                    const uint32_t v_addr = p_lower + PT_TILE_BYTES;
 #pragma unroll
-                for (uint32_t kk = 0; kk < PT_BK / 16; ++kk) {
-                    const uint64_t pdesc = make_kmajor_sw128_desc(kk < 4 ? p_lower : smem_u32(p_upper)) + (kk & 3) * 2;
-                    const uint64_t vdesc = make_mnmajor_sw128_desc(v_addr + kk * 2048, PT_TILE_BYTES, 1024);
-                    umma_bf16(tmem_base + PT_O_COL, pdesc, vdesc, PT_IDESC_O, kk != 0);
+                    for (uint32_t kk = 0; kk < PT_BK / 16; ++kk) {
+                        const uint64_t pdesc = make_kmajor_sw128_desc(kk < 4 ? p_lower : smem_u32(p_upper)) + (kk & 3) * 2;
+                        const uint64_t vdesc = make_mnmajor_sw128_desc(v_addr + kk * 2048, PT_TILE_BYTES, 1024);
+                        umma_bf16(tmem_base + PT_O_COL, pdesc, vdesc, PT_IDESC_O, kk != 0);
+                    }
+                    umma_commit(o_full);
+                    umma_commit(kv_empty + stage);   // both products of this ring stage are done
                 }
-                umma_commit(o_full);
-                umma_commit(kv_empty + stage);   // both products of this ring stage are done
+                g += n_blocks;
             }
         }
     } else {
         // ---------------- softmax warps: two threads per query row ----------------
         const uint32_t quarter = warp & 3, half = (warp - 2) >> 2;
         const uint32_t row = quarter * 32 + lane;
-        const uint32_t q_idx = min(q0 + row, prm.chunk - 1);
-        const uint32_t limit = prm.position + q_idx;             // last visible key of this row
         const uint32_t lane_taddr = tmem_base + ((quarter * 32u) << 16);
         const float sl2 = prm.scale_log2;
-        float acc[32];                                           // output columns [32 half, 32 half + 32)
-#pragma unroll
-        for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
-        float m = -INFINITY, l = 0.0f, corr_pending = 0.0f;      // l: sum over this thread's key columns only
+        uint32_t pair_uses = 0, g = 0;
         bool ok = true;
-        uint32_t pair_uses = 0;
-
         // Both threads of a row publish a value and read the partner's.
         auto exchange = [&](float mine, float& other) -> bool {
             float* slot = xm + (pair_uses & 1) * 256;
@@ -203,97 +224,110 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             ++pair_uses;
             return true;
         };
-        // acc = acc * corr + O_b  (this thread's 32 outputs of block b)
-        auto fold = [&](uint32_t b, float corr) -> bool {
-            if (!mbar_wait(o_full, b & 1, abort_flag)) return false;
-            tc_fence_after();
-            float v[32];
-            tmem_ld32(lane_taddr + PT_O_COL + half * 32, v);
-            tmem_ld_wait();
+        for (uint32_t item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+            uint32_t q0, h, s, n_blocks;
+            item_coords(item, q0, h, s, n_blocks);
+            const uint32_t q_idx = min(q0 + row, prm.chunk - 1);
+            const uint32_t limit = prm.position + q_idx;             // last visible key of this row
+            float acc[32];                                           // output columns [32 half, 32 half + 32)
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[i] = fmaf(acc[i], corr, v[i]);
-            return true;
-        };
+            for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
+            float m = -INFINITY, l = 0.0f, corr_pending = 0.0f;      // l: sum over this thread's key columns only
+            // acc = acc * corr + O_b  (this thread's 32 outputs of block b, b counted over all items)
+            auto fold = [&](uint32_t b, float corr) -> bool {
+                if (!mbar_wait(o_full, b & 1, abort_flag)) return false;
+                tc_fence_after();
+                float v[32];
+                tmem_ld32(lane_taddr + PT_O_COL + half * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[i] = fmaf(acc[i], corr, v[i]);
+                return true;
+            };
 
-        for (uint32_t j = 0; j < n_blocks; ++j) {
-            if (!mbar_wait(s_full, j & 1, abort_flag)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t taddr = lane_taddr + half * 64;
-            const uint32_t kbase = j * PT_BK + half * 64;           // first key of this thread's columns
-            const bool need_mask = kbase + 63 > limit;
-            // pass 1: maximum of the raw scores of the own 64 columns (four independent chains)
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            for (uint32_t j = 0; j < n_blocks; ++j) {
+                const uint32_t b = g + j;
+                if (!mbar_wait(s_full, b & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t taddr = lane_taddr + half * 64;
+                const uint32_t kbase = j * PT_BK + half * 64;           // first key of this thread's columns
+                const bool need_mask = kbase + 63 > limit;
+                // pass 1: maximum of the raw scores of the own 64 columns (four independent chains)
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                float v[32];
-                tmem_ld32(taddr + c * 32, v);
-                tmem_ld_wait();
-                if (need_mask) {
+                for (int c = 0; c < 2; ++c) {
+                    float v[32];
+                    tmem_ld32(taddr + c * 32, v);
+                    tmem_ld_wait();
+                    if (need_mask) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) if (kbase + c * 32 + i > limit) v[i] = -INFINITY;
+                        for (int i = 0; i < 32; ++i) if (kbase + c * 32 + i > limit) v[i] = -INFINITY;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
                 }
+                float mx = pt_max4(mx4), other;
+                if (!exchange(mx, other)) { ok = false; break; }
+                mx = fmaxf(m, fmaxf(mx, other));
+                const float ms = (mx == -INFINITY) ? 0.0f : mx;
+                const float corr = pt_ex2((m - ms) * sl2);      // 0 for the first block
+                m = mx;
+                const float neg = -ms * sl2;
+                // the previous block's output; once it is complete the upper P tile may be overwritten
+                if (j > 0 && !fold(b - 1, corr_pending)) { ok = false; break; }
+                corr_pending = corr;
+                // pass 2: p = exp2(s * scale - m * scale) as bf16 into this thread's 128-byte row of the P tile
+                // (16-byte chunk c of row r at c ^ (r & 7))
+                uint8_t* p_row = (half ? p_upper : kv_ring + (b % PT_KV_STAGES) * PT_KV_BYTES) + row * 128u;
+                float rs4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-                for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
+                for (int c = 0; c < 2; ++c) {
+                    float v[32];
+                    tmem_ld32(taddr + c * 32, v);
+                    tmem_ld_wait();
+                    if (need_mask) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) if (kbase + c * 32 + i > limit) v[i] = -INFINITY;
+                    }
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float p0 = pt_ex2(fmaf(v[2 * i], sl2, neg)), p1 = pt_ex2(fmaf(v[2 * i + 1], sl2, neg));
+                        rs4[i & 3] += p0 + p1;
+                        packed[i] = pack_bf16x2(p0, p1);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t chunk16 = (uint32_t)(c * 4 + i);
+                        *reinterpret_cast<uint4*>(p_row + (((chunk16 ^ row) & 7u) << 4)) =
+                            make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                    }
+                }
+                l = l * corr + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
+                // scores consumed: the buffer may take the next S; P written: visible to the tensor core, then signal
+                tc_fence_before();
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_full);
             }
-            float mx = pt_max4(mx4), other;
-            if (!exchange(mx, other)) { ok = false; break; }
-            mx = fmaxf(m, fmaxf(mx, other));
-            const float ms = (mx == -INFINITY) ? 0.0f : mx;
-            const float corr = pt_ex2((m - ms) * sl2);      // 0 for the first block
-            m = mx;
-            const float neg = -ms * sl2;
-            // the previous block's output; once it is complete the upper P tile may be overwritten
-            if (j > 0 && !fold(j - 1, corr_pending)) { ok = false; break; }
-            corr_pending = corr;
-            // pass 2: p = exp2(s * scale - m * scale) as bf16 into this thread's 128-byte row of the P tile
-            // (16-byte chunk c of row r at c ^ (r & 7))
-            uint8_t* p_row = (half ? p_upper : kv_ring + (j % PT_KV_STAGES) * PT_KV_BYTES) + row * 128u;
-            float rs4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                float v[32];
-                tmem_ld32(taddr + c * 32, v);
-                tmem_ld_wait();
-                if (need_mask) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) if (kbase + c * 32 + i > limit) v[i] = -INFINITY;
-                }
-                uint32_t packed[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float p0 = pt_ex2(fmaf(v[2 * i], sl2, neg)), p1 = pt_ex2(fmaf(v[2 * i + 1], sl2, neg));
-                    rs4[i & 3] += p0 + p1;
-                    packed[i] = pack_bf16x2(p0, p1);
-                }
+            if (!ok) break;
+            ok = fold(g + n_blocks - 1, corr_pending);
+            float l_other = 0.0f;
+            if (ok) ok = exchange(l, l_other);
+            if (ok && q0 + row < prm.chunk) {
+                const float inv = 1.0f / (l + l_other);
+                bf16* og = prm.out + ((size_t)s * prm.chunk + q0 + row) * ((size_t)prm.heads * PT_HD) + (size_t)h * PT_HD + half * 32;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const uint32_t chunk16 = (uint32_t)(c * 4 + i);
-                    *reinterpret_cast<uint4*>(p_row + (((chunk16 ^ row) & 7u) << 4)) =
-                        make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                    uint4 w;
+                    w.x = pack_bf16x2(acc[8 * i] * inv, acc[8 * i + 1] * inv);
+                    w.y = pack_bf16x2(acc[8 * i + 2] * inv, acc[8 * i + 3] * inv);
+                    w.z = pack_bf16x2(acc[8 * i + 4] * inv, acc[8 * i + 5] * inv);
+                    w.w = pack_bf16x2(acc[8 * i + 6] * inv, acc[8 * i + 7] * inv);
+                    *reinterpret_cast<uint4*>(og + 8 * i) = w;
                 }
             }
-            l = l * corr + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
-            // scores consumed: the buffer may take S_{j+1}; P written: visible to the tensor core, then signal
-            tc_fence_before();
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
-        }
-        if (ok && n_blocks > 0) ok = fold(n_blocks - 1, corr_pending);
-        float l_other = 0.0f;
-        if (ok) ok = exchange(l, l_other);
-        if (ok && q0 + row < prm.chunk) {
-            const float inv = 1.0f / (l + l_other);
-            bf16* og = prm.out + ((size_t)s * prm.chunk + q0 + row) * ((size_t)prm.heads * PT_HD) + (size_t)h * PT_HD + half * 32;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                uint4 w;
-                w.x = pack_bf16x2(acc[8 * i] * inv, acc[8 * i + 1] * inv);
-                w.y = pack_bf16x2(acc[8 * i + 2] * inv, acc[8 * i + 3] * inv);
-                w.z = pack_bf16x2(acc[8 * i + 4] * inv, acc[8 * i + 5] * inv);
-                w.w = pack_bf16x2(acc[8 * i + 6] * inv, acc[8 * i + 7] * inv);
-                *reinterpret_cast<uint4*>(og + 8 * i) = w;
-            }
+            g += n_blocks;
         }
     }
 
@@ -368,7 +402,13 @@ int launch_prefill_attention_tc(const bf16* q, const bf16* k_cache, const bf16* 
     prm.q_tiles = ceil_div(chunk, (uint32_t)PT_BQ);
     prm.scale_log2 = (1.0f / sqrtf((float)PT_HD)) * 1.4426950408889634f;
     prm.d_status = d_status;
-    dim3 grid(prm.q_tiles, heads, sessions);
+    prm.sessions = sessions;
+    // persistent: two CTAs per SM walk the list of (query tile, head, session) items
+    int dev_sms = 0;
+    cudaDeviceGetAttribute(&dev_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (dev_sms <= 0) dev_sms = 148;
+    const uint64_t items = (uint64_t)prm.q_tiles * heads * sessions;
+    dim3 grid((unsigned)std::min<uint64_t>(items, 2ull * dev_sms));
     launch_kernel(prefill_attention_tc_kernel, grid, dim3(PT_THREADS), (size_t)PT_SMEM_BYTES, stream, mq, mk, mv, prm);
     count_launch();
     return check_launch("prefill_attention_tc");
