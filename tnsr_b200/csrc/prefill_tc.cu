@@ -3,12 +3,13 @@
 // (src/nn/kv_cache/prefill.rs:170-607): `chunk` new queries per session attend
 // keys 0 .. position + t of the cache that already holds their own rows.
 //
-// One CTA = 128 queries of one (session, head); the accumulator row of a query is
-// one TMEM lane.  Keys arrive in blocks of 128.  Two CTAs share an SM (about 100 KB
-// of shared memory and 256 TMEM columns each), so one CTA's loads, softmax and
-// hand-overs overlap the other's.
+// A work item = 128 queries of one (session, head); the accumulator row of a query
+// is one TMEM lane.  Keys arrive in blocks of 128.  The CTAs are persistent: two per
+// SM (about 100 KB of shared memory and 256 TMEM columns each, so one CTA's loads,
+// softmax and hand-overs overlap the other's) walk the item list, longest items
+// first, with TMEM and barriers set up once.
 //
-//   warp 0      TMA: the Q tile once, then K and V blocks into a two-stage ring
+//   warp 0      TMA: per item the Q tile, then K and V blocks into a two-stage ring
 //               (3-D tensor maps {width, live rows, sessions}: rows past
 //               position + chunk read as zeros, so stale cache rows never meet
 //               the arithmetic).
@@ -26,7 +27,8 @@
 //               complete, not reloaded before P_j V_j is), keys 64-127 to a tile of
 //               their own.
 //
-// Hand-overs (single-buffered, phase parity = block index & 1):
+// Hand-overs (single-buffered, phase parity = running block count & 1; q_full / q_empty count items: the Q tile
+// may be reloaded once the item's last S product is complete):
 //   s_full   S_j complete                      MMA commit  -> softmax
 //   pair     both halves of a row wrote their maximum      softmax <-> softmax (per lane quarter)
 //   p_full   P_j written, S_j no longer needed softmax     -> MMA (issues S_{j+1}, then P_j V_j)
