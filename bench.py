@@ -7,16 +7,20 @@ Workload ("c4"): the serving configuration -- 12 layers, d_model 768, 12 heads x
 64, SwiGLU 2048, vocab 32000, bf16 weights N(0, 0.02) seed 5; 256 independent
 sessions, each a 512-token prefill of uniform random ids followed by greedy
 decode steps.  Sessions are independent, so N GPUs hold disjoint shards and no
-collective runs on the data path.  With the default `--scaling weak` every GPU
-holds the configuration's 256 sessions (256 N in total: the per-GPU work is the
-1-GPU workload whatever N is); `--scaling strong` divides the same 256 sessions
-256/N per GPU, which is how the configuration words it.  A benchmark "step" is
-one decode step: one new token for every session of the rank.  The timed region is K steps starting
-at position 512 (the default K = 256 is the configuration's decode length), with
-token ids living on the device; `value` is total tokens/s over all ranks, timed
-with CUDA events on the session's stream, max over ranks.  `e2e` repeats the K
-steps through the host API (`tnsr_b200_decoder_decode`): ids go up from host
-memory and greedy ids come back every step.
+collective runs on the data path.  With the default `--scaling strong` the
+configuration's 256 sessions are divided 256/N per GPU, as the configuration
+words it (`weak_scaling` in the same line is the side measurement with all 256
+sessions on every GPU; `--scaling weak` makes that the headline instead).  A
+benchmark "step" is one decode step: one new token for every session of the
+rank.  The timed region is K steps starting at position 512 (the default K =
+256 is the configuration's decode length) with token ids living on the device,
+timed with CUDA events on the session's stream; it is repeated `--repeats`
+times from the same state, each repeat taken as the max over ranks, and
+`value` is total tokens/s at the median repeat (all samples are in `timing`).
+`e2e` repeats the K steps through the host API (`tnsr_b200_decoder_decode`):
+ids go up from host memory and greedy ids come back every step.  At N = 1 the
+line also carries `ops`: GEMM TFLOP/s, SwiGLU-MLP TFLOP/s and KV-attention GB/s
+of the operator configurations.
 
 `--workload c0|c1|c2|c3` measures the smaller configurations on one GPU (the f32
 4-layer model end to end, the GEMM sweep, the SwiGLU MLP, ragged decode attention),
@@ -48,10 +52,10 @@ DECODE_STEPS = 256
 FALLBACK_HBM_GBS = 6650.0
 
 # Per-launch DRAM traffic of decode_attention_kernel relative to its algorithmic
-# bytes, from the ncu capture summarised in profiles/decode_attention_c4_full_size.md
-# (dram__bytes_read.sum + dram__bytes_write.sum = 509.48 MB for 504.89 MB of live K/V
-# rows and q/out at 256 sessions x 641 live keys, the mean length of the timed steps;
-# traffic grows in proportion to the live keys, so the ratio is applied to every step).
+# bytes, from one ncu capture of the kernel at 256 sessions x 641 live keys (the mean
+# length of the timed steps): dram__bytes_read.sum + dram__bytes_write.sum = 509.48 MB
+# for 504.89 MB of live K/V rows and q/out.  Traffic grows in proportion to the live
+# keys, so the ratio is applied to every step.
 NCU_TRAFFIC_RATIO = 1.009
 
 
@@ -62,9 +66,13 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--sessions", type=int, default=TOTAL_SESSIONS,
-                    help="sessions per GPU (weak scaling) or in total (strong scaling)")
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
-                    help="weak: every GPU holds --sessions sessions; strong: --sessions are divided over the GPUs")
+                    help="sessions in total (strong scaling) or per GPU (weak scaling)")
+    ap.add_argument("--scaling", default="strong", choices=["weak", "strong"],
+                    help="strong (the configuration's wording): --sessions are divided over the GPUs, 256/N each; "
+                         "weak: every GPU holds --sessions sessions")
+    ap.add_argument("--repeats", type=int, default=10, help="timed passes of K steps; value is their median")
+    ap.add_argument("--no-weak", action="store_true", help="N > 1, strong scaling: skip the weak-scaling side measurement")
+    ap.add_argument("--no-ops", action="store_true", help="N = 1: skip the operator configurations (c1-c3 headline values)")
     ap.add_argument("--prefill", type=int, default=PREFILL)
     ap.add_argument("--layers", type=int, default=12)
     ap.add_argument("--vocab", type=int, default=32000)
@@ -154,7 +162,7 @@ def cpu_decode_rate(args, steps, warmup, threads=None, budget_s=None):
     The sessions start at position `prefill` on zeroed K/V rows: the arithmetic
     cost of a decode step does not depend on the cached values."""
     from oracle import oracle
-    from tests.workloads import normal_model_arrays
+    from tnsr_b200.synthetic import normal_model_arrays
     cfg = serving_config(args)
     threads = threads or oracle.max_threads()
     oracle.set_threads(threads)
@@ -215,15 +223,21 @@ def run_reference(args):
 
 
 def sessions_per_gpu(args, n_gpus):
-    return args.sessions if args.scaling == "weak" else args.sessions // n_gpus
+    """Per-rank session counts: the whole batch everywhere (weak) or contiguous shards of it (strong)."""
+    from tnsr_b200.sharding import shard_sessions
+    if args.scaling == "weak":
+        return [args.sessions] * n_gpus
+    return [shard_sessions(args.sessions, n_gpus, r)[1] for r in range(n_gpus)]
 
 
 def workload_config(args, n_gpus):
-    per_gpu = sessions_per_gpu(args, n_gpus)
+    shards = sessions_per_gpu(args, n_gpus)
+    per_gpu = shards[0] if len(set(shards)) == 1 else shards
     return {
         "workload": "c4: GPT 12x768 (12 heads x 64, SwiGLU 2048, vocab 32000, ctx 2048), "
-                    f"{per_gpu} sessions per GPU x ({args.prefill}-token prefill + greedy decode), 1 token/session/step",
-        "sessions_total": per_gpu * n_gpus, "sessions_per_gpu": per_gpu, "prefill": args.prefill,
+                    f"{sum(shards)} sessions ({per_gpu} per GPU) x ({args.prefill}-token prefill + greedy decode), "
+                    "1 token/session/step",
+        "sessions_total": sum(shards), "sessions_per_gpu": per_gpu, "prefill": args.prefill,
         "layers": args.layers, "vocab": args.vocab,
         "parallelism": f"independent sessions on {n_gpus} GPU(s), {args.scaling} scaling, no collective",
         "l2": "inputs larger than L2: each step streams the live K/V rows (GBs) and 222 MB of weights",
@@ -268,8 +282,9 @@ def run_ops(args):
     launches0 = lib.tnsr_b200_kernel_launches()
     rng = np.random.default_rng(2)
     if args.workload == "c0":
-        from tests.helpers import cpu_decoder
-        from tests.workloads import config0_model, config0_prompt, set_model_arrays
+        from oracle.oracle import OracleBackend
+        from tnsr_b200.nn import GptDecoder
+        from tnsr_b200.synthetic import config0_model, config0_prompt, set_model_arrays
         from tnsr_b200 import Backend, Gpt
         from tnsr_b200.nn import argmax_last
         cfg, arrays = config0_model("relu")
@@ -294,7 +309,8 @@ def run_ops(args):
         runs = [greedy(gpu_dec) for _ in range(max(5, args.samples // 2))]
         got = runs[-1][0]
         gpu_prefill_s, gpu_s = float(np.median([r[1] for r in runs])), float(np.median([r[2] for r in runs]))
-        cpu_dec = cpu_decoder(model, 1)
+        cpu_dec = GptDecoder(model, None, 1, cfg.max_sequence_length,
+                             backend_impl=OracleBackend(cfg, 1, cfg.max_sequence_length, attention_bf16=False))
         greedy(cpu_dec)
         cpu_runs = [greedy(cpu_dec) for _ in range(3)]
         want = cpu_runs[-1][0]
@@ -381,30 +397,19 @@ def run_ops(args):
 # ---------------------------------------------------------------------------
 # this library
 # ---------------------------------------------------------------------------
-def run_b200(args):
+def _percentile(xs, q):
+    return float(np.percentile(np.asarray(xs, dtype=np.float64), q))
+
+
+def measure_decode(args, cfg, sessions, rank, local_rank, world, barrier, reduce_max, full):
+    """Prefill `sessions` sessions on this rank, then time K greedy steps from position `prefill`, `--repeats` times
+    (every repeat starts over from the same position and ids).  Returns the per-repeat milliseconds (max over ranks)
+    and, when `full`, the attention-kernel profile and the end-to-end loop as well."""
     import torch
-    import torch.distributed as dist
-    from tests.workloads import normal_model_arrays
     from tnsr_b200 import _native
     from tnsr_b200.session import B200Session
+    from tnsr_b200.synthetic import normal_model_arrays
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.gpus > 1 and world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    cfg = serving_config(args)
-    sessions = sessions_per_gpu(args, world)
     K, W = args.steps, args.warmup
     capacity = min(cfg.max_sequence_length, args.prefill + max(K, W) + 1)
     # positions of the decode steps: prefill, prefill + 1, ...; a run longer than the context allows starts over at
@@ -416,18 +421,12 @@ def run_b200(args):
     def position_of(step):
         return args.prefill + step % span
     lib = _native.lib()
-
-    def make_session():
-        s = B200Session(cfg, sessions, capacity, device=local_rank, logits_mode="none")
-        for i, a in enumerate(arrays):
-            s.refresh(i, a)
-        return s
-
     arrays = normal_model_arrays(cfg, seed=5, std=0.02)
-    sess = make_session()
+    sess = B200Session(cfg, sessions, capacity, device=local_rank, logits_mode="none")
+    for i, a in enumerate(arrays):
+        sess.refresh(i, a)
     del arrays
     stream = torch.cuda.ExternalStream(sess.stream(), device=torch.device("cuda", local_rank))
-
     rng = np.random.default_rng(1000 + rank)
     prompt = rng.integers(0, cfg.vocab_size, size=(sessions, args.prefill)).astype(np.uint32)
 
@@ -459,108 +458,216 @@ def run_b200(args):
             sess.decode_device(cur.data_ptr(), 1, position_of(step), cur.data_ptr())
         return cur
 
-    # ---- warm-up, then the timed region ----
+    def timed_pass():
+        cur = fresh_ids()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        last = device_loop(K, cur)
+        e1.record(stream)
+        sess.synchronize()
+        return e0.elapsed_time(e1), last
+
+    # ---- warm-up: W steps, then whole untimed passes until two in a row agree to 2 % (clocks, caches, graph) ----
     device_loop(W, fresh_ids())
     sess.synchronize()
-    cur = fresh_ids()
+    warm_passes, prev = 0, None
+    t_warm = time.perf_counter()
+    while warm_passes < 12 and time.perf_counter() - t_warm < 5.0:
+        ms, _ = timed_pass()
+        warm_passes += 1
+        if prev is not None and abs(ms - prev) <= 0.02 * prev:
+            break
+        prev = ms
+
+    # ---- the timed region: `repeats` passes of exactly K steps, each between barriers ----
     sampler = ClockSampler(local_rank)
     sampler.start()
-    barrier()
-    launches0 = lib.tnsr_b200_kernel_launches()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    last = device_loop(K, cur)
-    e1.record(stream)
-    sess.synchronize()
-    launches = lib.tnsr_b200_kernel_launches() - launches0
-    barrier()
+    samples, launches = [], 0
+    last = None
+    for _ in range(args.repeats):
+        barrier()
+        launches0 = lib.tnsr_b200_kernel_launches()
+        ms, last = timed_pass()
+        launches = lib.tnsr_b200_kernel_launches() - launches0
+        barrier()
+        samples.append(ms)
     clocks = sampler.stop()
-    elapsed_ms = e0.elapsed_time(e1)
+    samples = [reduce_max(x) for x in samples]
     tokens_after_timed = last.cpu().numpy().astype(np.uint32)
+    out = {"sessions": sessions, "samples_ms": samples, "prefill_ms": reduce_max(prefill_ms), "launches": int(launches),
+           "clocks": clocks, "warm_passes": warm_passes, "position_of": position_of}
+    if not full:
+        sess.close()
+        return out
 
     # ---- instrumented replay of the same K steps: device time of the attention kernel ----
     sess.profile_attention(True)
     sess.attention_profile()
     device_loop(K, fresh_ids())
-    attn_ms, attn_launches = sess.attention_profile()
+    out["attn_ms"], out["attn_launches"] = sess.attention_profile()
     sess.profile_attention(False)
 
     # ---- end to end through the host API ----
-    e2e = None
     if not args.no_e2e:
         cur = first_host.copy()
         for step in range(min(W, K)):
             _, cur = sess.decode_full(cur.reshape(sessions, 1), position_of(step))
-        cur = first_host.copy()
-        barrier()
-        t0 = time.perf_counter()
-        for step in range(K):
-            _, cur = sess.decode_full(cur.reshape(sessions, 1), position_of(step))
-        torch.cuda.synchronize()
-        e2e_s = time.perf_counter() - t0
-        barrier()
-        e2e = {"seconds": e2e_s, "same_tokens_as_device_loop": bool(np.array_equal(cur, tokens_after_timed))}
+        e2e_samples = []
+        for _ in range(max(1, min(3, args.repeats))):
+            cur = first_host.copy()
+            barrier()
+            t0 = time.perf_counter()
+            for step in range(K):
+                _, cur = sess.decode_full(cur.reshape(sessions, 1), position_of(step))
+            torch.cuda.synchronize()
+            e2e_samples.append(time.perf_counter() - t0)
+            barrier()
+        out["e2e_samples_s"] = [reduce_max(x) for x in e2e_samples]
+        out["e2e_same_tokens"] = bool(np.array_equal(cur, tokens_after_timed))
+    sess.close()
+    return out
 
-    # ---- reduce over ranks ----
-    def max_over_ranks(x):
+
+def operator_summary(samples):
+    """Headline values of the operator configurations (GEMM TFLOP/s, SwiGLU MLP TFLOP/s, KV-attention GB/s), measured
+    through the C ABI by tnsr_b200.opbench on the current device."""
+    from tnsr_b200 import opbench
+    opbench.QUIET = True
+    del opbench.RESULTS[:]
+    opbench.bench_gemm(samples, shapes=[(8192, 8192, 8192), (1, 4096, 4096), (8, 4096, 4096), (64, 4096, 4096)],
+                       outs=("bf16",))
+    opbench.bench_mlp(samples)
+    opbench.bench_attention(samples)
+    ops = {}
+    for r in opbench.RESULTS:
+        if r["op"] == "gemm_bf16":
+            key = "c1_gemm_%dx%dx%d" % (r["m"], r["n"], r["k"])
+            if r["bound"] == "tensor":
+                ops[key] = {"tflops": r["tflops"], "frac_tensor": r["frac_tensor"], "ms": r["ms"]}
+            else:
+                ops[key] = {"us": r["ms"] * 1e3, "gbs": r["gbs"], "frac_hbm": r["frac_hbm"]}
+        elif r["op"] == "swiglu_mlp":
+            ops["c2_swiglu_mlp_4096x2048x5632"] = {"tflops": r["tflops"], "frac_tensor": r["frac_tensor"], "ms": r["ms"]}
+        elif r["op"] == "decode_attention":
+            ops["c3_decode_attention_64x16x64_ragged"] = {"gbs": r["gbs"], "frac_hbm": r["frac_hbm"], "ms": r["ms"]}
+    ops["peaks"] = opbench.RESULTS[-1]["peaks"] if opbench.RESULTS else None
+    return ops
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+    from tnsr_b200.sharding import shard_sessions
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus > 1 and world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def reduce_max(x):
         if world == 1:
-            return x
+            return float(x)
         t = torch.tensor([x], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    def sum_over_ranks(x):
+    def reduce_sum(x):
         if world == 1:
-            return x
+            return float(x)
         t = torch.tensor([x], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         return float(t.item())
 
-    elapsed_ms = max_over_ranks(elapsed_ms)
-    prefill_ms = max_over_ranks(prefill_ms)
-    total_launches = int(sum_over_ranks(float(launches)))
-    e2e_s = max_over_ranks(e2e["seconds"]) if e2e else None
-    total_sessions = sessions * world
+    cfg = serving_config(args)
+    K, W = args.steps, args.warmup
+    if args.scaling == "strong":
+        _, sessions = shard_sessions(args.sessions, world, rank)   # contiguous blocks, sizes differ by at most one
+        if sessions == 0:
+            raise SystemExit("more GPUs than sessions")
+    else:
+        sessions = args.sessions
+    main = measure_decode(args, cfg, sessions, rank, local_rank, world, barrier, reduce_max, full=True)
+    total_sessions = int(reduce_sum(sessions))
+    total_launches = int(reduce_sum(main["launches"]))
+    weak = None
+    if world > 1 and args.scaling == "strong" and not args.no_weak:
+        # the same job with the configuration's whole batch on every GPU: the per-GPU step of the 1-GPU run
+        weak = measure_decode(args, cfg, args.sessions, rank, local_rank, world, barrier, reduce_max, full=False)
 
     if rank == 0:
-        d, layers = cfg.embed_dim, cfg.num_layers
+        d, layers, f = cfg.embed_dim, cfg.num_layers, cfg.feed_forward_dim
         peak, peak_kind, peaks = measured_peaks()
+        position_of = main["position_of"]
+        elapsed_ms = float(np.median(main["samples_ms"]))
         # algorithmic bytes of one attention launch at decode step t: every session's live K and V rows
         # (prefill + t + 1 keys x d x 2 B x 2 tensors) plus q and out rows
         live = float(np.mean([position_of(t) + 1 for t in range(K)]))     # keys a step at position p attends: p + 1
         bytes_per_launch = sessions * (live * d * 2 * 2 + 2 * d * 2)
+        attn_ms, attn_launches = main["attn_ms"], main["attn_launches"]
         attn_avg_ms = attn_ms / max(attn_launches, 1)
         achieved = bytes_per_launch / (attn_avg_ms * 1e-3) / 1e9 if attn_launches else None
+        peak_source = f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s"
         roofline = {
             "kernel": "decode_attention_kernel<64,1> (split-KV live-prefix scan)", "bound": "hbm",
             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak if achieved else None,
-            "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
+            "peak_source": peak_source,
             "traffic": bytes_per_launch * NCU_TRAFFIC_RATIO if NCU_TRAFFIC_RATIO else None,
             "algorithmic_bytes_per_launch": bytes_per_launch, "avg_launch_ms": attn_avg_ms, "launches": attn_launches,
-            "share_of_step": attn_ms / (elapsed_ms if world == 1 else elapsed_ms) if attn_launches else None,
+            "share_of_step": attn_ms / elapsed_ms if attn_launches else None,
             "how": "CUDA events around every launch of the kernel on the session's stream, in a replay of the same K steps",
         }
+        # the whole step against the same roofline: live K/V of every layer plus every weight matrix once
+        weight_bytes = 2.0 * (layers * (4 * d * d + 3 * d * f) + d * cfg.vocab_size)
+        step_bytes = layers * bytes_per_launch + weight_bytes
+        step_gbs = step_bytes / (elapsed_ms / K * 1e-3) / 1e9
+        roofline_step = {"bound": "hbm", "achieved": step_gbs, "peak": peak, "unit": "GB/s", "frac": step_gbs / peak,
+                         "peak_source": peak_source, "algorithmic_bytes_per_step": step_bytes,
+                         "what": "rank 0's step: live K/V rows of all layers + every bf16 weight matrix once, over ms_per_step"}
         value = total_sessions * K / (elapsed_ms * 1e-3)
-        flops_per_token = 2.0 * (layers * (4 * d * d + 3 * d * cfg.feed_forward_dim)) + 2.0 * d * cfg.vocab_size
+        flops_per_token = 2.0 * (layers * (4 * d * d + 3 * d * f)) + 2.0 * d * cfg.vocab_size
         prefill_tokens = total_sessions * args.prefill
+        prefill_ms = main["prefill_ms"]
         line = {
             "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": elapsed_ms / K, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "config": workload_config(args, world),
-            "roofline": roofline,
+            "timing": {"repeats": len(main["samples_ms"]), "value_is": "median over repeats of K steps (max over ranks per repeat)",
+                       "samples_ms_per_step": [x / K for x in main["samples_ms"]],
+                       "p10_ms_per_step": _percentile(main["samples_ms"], 10) / K,
+                       "p90_ms_per_step": _percentile(main["samples_ms"], 90) / K,
+                       "untimed_warm_passes": main["warm_passes"]},
+            "roofline": roofline, "roofline_step": roofline_step,
             "gpu_launches": total_launches,
-            "clocks": clocks,
+            "clocks": main["clocks"],
             "prefill": {"tokens_per_s": prefill_tokens / (prefill_ms * 1e-3), "ms": prefill_ms,
-                        "gemm_tflops": prefill_tokens * (flops_per_token - 2.0 * d * cfg.vocab_size) / (prefill_ms * 1e-3) / 1e12,
-                        "note": "whole prefill step incl. attention and LayerNorm; GEMM flops / wall time"},
+                        "gemm_tflops": sessions * args.prefill * (flops_per_token - 2.0 * d * cfg.vocab_size) / (prefill_ms * 1e-3) / 1e12,
+                        "note": "whole prefill step incl. attention and LayerNorm; rank 0's GEMM flops / max-over-ranks time"},
         }
-        if e2e:
+        if "e2e_samples_s" in main:
+            e2e_s = float(np.median(main["e2e_samples_s"]))
             line["e2e"] = {"value": total_sessions * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 4 * sessions,
                            "d2h_bytes_per_step": 4 * sessions + 4, "ms_per_step": e2e_s / K * 1e3,
+                           "samples_ms_per_step": [x / K * 1e3 for x in main["e2e_samples_s"]],
                            "api": "tnsr_b200_decoder_decode, logits_mode NONE: ids up, greedy ids down, every step",
-                           "same_tokens_as_device_loop": e2e["same_tokens_as_device_loop"]}
+                           "same_tokens_as_device_loop": main["e2e_same_tokens"]}
+        if weak:
+            wms = float(np.median(weak["samples_ms"]))
+            line["weak_scaling"] = {"sessions_per_gpu": args.sessions, "value": args.sessions * world * K / (wms * 1e-3),
+                                    "unit": "tokens/s", "ms_per_step": wms / K,
+                                    "note": "side measurement: the configuration's whole batch on every GPU"}
+        if world == 1 and not args.no_ops:
+            line["ops"] = operator_summary(args.samples)
         if world == 1 and not args.no_cpu_baseline:
-            sess.close()
             r = cpu_decode_rate(args, steps=64, warmup=1, budget_s=20.0)
             line["cpu_baseline"] = {
                 "value": r["tokens_per_s"], "unit": "tokens/s", "cores": r["threads"], "kind": "port",

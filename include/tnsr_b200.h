@@ -255,7 +255,8 @@ TNSR_B200_API int tnsr_b200_gemm_bf16(const void* a, const void* bt, const float
  * tile is divided over several CTAs so that all SMs pull on HBM, and the CTA
  * that finishes last adds the partial tiles in a fixed order (results do not
  * depend on timing).  `workspace`: tnsr_b200_gemm_workspace() bytes, 16-byte
- * aligned, zeroed once before the first use (every launch leaves it zeroed);
+ * aligned, zeroed once before the first use (every launch that completes leaves
+ * it zeroed; zero it again if a launch was cut short by a device error);
  * launches that may overlap on the GPU must not share it. */
 TNSR_B200_API uint64_t tnsr_b200_gemm_workspace(void);
 TNSR_B200_API int tnsr_b200_gemm_bf16_ws(const void* a, const void* bt, const float* bias,
@@ -293,9 +294,13 @@ TNSR_B200_API int tnsr_b200_pack_gate_up(const void* w_gate, const void* w_up, c
  * bf16; k_cache, v_cache: [batch, capacity, heads*head_dim] bf16; lengths[b]
  * = live keys of session b including its newest row (1..capacity; 0 gives a
  * zero output row).  workspace: device scratch of at least
- * tnsr_b200_decode_attention_workspace(...) bytes; bytes 64..67 of it hold a
- * status word (0 = ok) once the stream has passed the call.  Scores are scaled by
- * 1/sqrt(head_dim); softmax statistics and accumulation are f32. */
+ * tnsr_b200_decode_attention_workspace(...) bytes (a smaller one is rejected
+ * before anything is written); bytes 64..67 of it hold a status word once the
+ * stream has passed the call: 0 = ok, 2 = a bounded wait inside the kernel gave
+ * up, 3 = a length beyond the capacity was clamped.  The call clears the word
+ * and the kernels re-arm their own counters at every launch, so a workspace can
+ * be reused after an error status without zeroing it again.  Scores are scaled
+ * by 1/sqrt(head_dim); softmax statistics and accumulation are f32. */
 TNSR_B200_API uint64_t tnsr_b200_decode_attention_workspace(uint32_t batch, uint32_t capacity,
                                                             uint32_t heads, uint32_t head_dim);
 TNSR_B200_API int tnsr_b200_decode_attention(const void* q, const void* k_cache, const void* v_cache,
@@ -316,8 +321,11 @@ TNSR_B200_API int tnsr_b200_decode_attention(const void* q, const void* k_cache,
  * not with capacity), otherwise TNSR_B200_ERR_UNSUPPORTED.  All calls
  * share the array, so calls that overlap on the GPU (different streams or host
  * threads) race: keep them on one stream.  The first call on each device looks
- * up the array's device address once; make that first call before any stream
- * capture.  d_status (optional device int) receives 0 or a device-side error
+ * up the array's device address once and keeps it for the life of the process;
+ * make that first call before any stream capture, and do not use this entry
+ * point after cudaDeviceReset or under a context other than the device's primary
+ * one (the remembered address belongs to the context that made the first call).
+ * d_status (optional device int) receives 0 or a device-side error
  * code when the stream reaches the end of the call.  Arguments otherwise as
  * tnsr_b200_decode_attention. */
 #define TNSR_B200_STATIC_SCRATCH_BYTES (32ull << 20)
@@ -336,14 +344,6 @@ TNSR_B200_API int tnsr_b200_prefill_attention(const void* q, const void* k_cache
                                               void* out, uint32_t batch, uint32_t chunk,
                                               uint32_t position, uint32_t capacity, uint32_t heads,
                                               uint32_t head_dim, void* stream);
-
-/* Measurement aid (no reference counterpart): one CTA per SM streams `bytes` of
- * `buffer` through a shared-memory ring of `stages` x `stage_bytes` with bulk
- * async copies and discards them -- the K/V ring of the decode-attention kernel
- * with the arithmetic taken out.  Timing it gives the read bandwidth that ring
- * can reach on this GPU.  *bytes_read receives the bytes one launch moves. */
-TNSR_B200_API int tnsr_b200_stream_read_probe(const void* buffer, uint64_t bytes, uint32_t stage_bytes,
-                                              uint32_t stages, uint64_t* bytes_read, void* stream);
 
 /* Greedy pick per row: the last index holding the maximum under IEEE
  * totalOrder (src/nn/kv_cache.rs:148-153). */

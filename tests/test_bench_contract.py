@@ -36,3 +36,22 @@ def test_reference_arm_only_rank_zero_works_under_a_multi_rank_launch():
     lines = run_bench("--impl", "reference", "--gpus", "2", "--steps", "1", "--warmup", "1", "--layers", "2", "--vocab", "2048",
                       env={"RANK": "1", "WORLD_SIZE": "2", "LOCAL_RANK": "1"})
     assert lines == []
+
+
+def test_strong_scaling_is_the_default_and_shards_cover_every_session():
+    sys.path.insert(0, ROOT)
+    import bench
+    old = sys.argv
+    sys.argv = ["bench.py"]
+    try:
+        args = bench.parse_args()
+    finally:
+        sys.argv = old
+    assert args.scaling == "strong" and args.sessions == 256 and args.repeats >= 10
+    for n in (1, 2, 3, 4, 8):
+        shards = bench.sessions_per_gpu(args, n)
+        assert sum(shards) == 256 and max(shards) - min(shards) <= 1
+        cfg = bench.workload_config(args, n)
+        assert cfg["sessions_total"] == 256 and "strong" in cfg["parallelism"]
+    args.scaling = "weak"
+    assert bench.sessions_per_gpu(args, 4) == [256] * 4

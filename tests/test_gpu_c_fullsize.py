@@ -69,6 +69,16 @@ def test_config2_swiglu_mlp_full_size_against_f32_matmuls():
     assert float((hidden.float() - h_ref).abs().max() / h_ref.abs().max()) <= 1 / 128
     ref = h_ref.to(torch.bfloat16).float() @ wd.float() + bd
     assert float((out.float() - ref).abs().max() / ref.abs().max()) <= 2e-2
+    # 64 rows of the block (the first and the last 32) against the CPU checker's composition
+    # down(silu(x.Wg + bg) * (x.Wu + bu)) + bd in f32, reference operation order, on the same bf16-valued operands
+    from oracle import oracle
+    oracle.set_threads(oracle.max_threads())
+    pick = torch.cat([torch.arange(0, 32), torch.arange(rows - 32, rows)]).cuda()
+    want = oracle.swiglu_mlp(x[pick].float().cpu().numpy(), wg.float().cpu().numpy(), bg.cpu().numpy(),
+                             wu.float().cpu().numpy(), bu.cpu().numpy(), wd.float().cpu().numpy(), bd.cpu().numpy())
+    oracle.set_threads(1)
+    got = out[pick].float().cpu().numpy()
+    assert np.max(np.abs(got - want)) / np.max(np.abs(want)) <= 2e-2
     # zero input rows give exactly the bias path: silu(bg) * bu . Wd + bd is the same for every row
     x.zero_()
     ok(lib().tnsr_b200_swiglu_mlp(ptr(x), ptr(packed_w), ptr(packed_b), ptr(wdt), ptr(bd), ptr(hidden), ptr(out), rows, d, f,
@@ -115,20 +125,26 @@ def test_config3_attention_full_size_invariants():
     # the split points of the key partition move with the session order, so the merge order of a session's
     # partial results changes: equal up to rounding, not bit for bit
     assert float((permuted.float() - base[perm].float()).abs().max()) <= max(1.0, float(base.float().abs().max())) / 128
-    # a reference over a few sessions in f64 (the whole batch would be slow in Python, not wrong)
-    for b in (0, 17, 63):
-        n = int(lengths[b])
-        qh = q[b].double().view(heads, hd)
-        kh = kc[b, :n].double().view(n, heads, hd)
-        vh = vc[b, :n].double().view(n, heads, hd)
-        w = torch.softmax(torch.einsum("hc,nhc->hn", qh, kh) / hd ** 0.5, dim=1)
-        ref = torch.einsum("hn,nhc->hc", w, vh).reshape(d)
-        assert float((base[b].double() - ref).abs().max()) <= max(1.0, float(ref.abs().max())) / 128
+    # every session against the CPU checker's live-prefix scan (f32, reference order) on the same bf16-valued rows;
+    # poisoned rows are cleared on the host copy only: the checker never reads them either, NaN * 0 aside
+    from oracle import oracle
+    oracle.set_threads(oracle.max_threads())
+    want = np.empty((batch, d), dtype=np.float32)
+    for b0 in range(0, batch, 16):
+        kh = torch.nan_to_num(kc[b0:b0 + 16].float(), nan=0.0).cpu().numpy()
+        vh = torch.nan_to_num(vc[b0:b0 + 16].float(), nan=0.0).cpu().numpy()
+        want[b0:b0 + 16] = oracle.decode_attention(q[b0:b0 + 16].float().cpu().numpy(), kh, vh, lengths[b0:b0 + 16], heads)
+    oracle.set_threads(1)
+    got = base.float().cpu().numpy()
+    per_session = np.max(np.abs(got - want), axis=1) / np.maximum(1.0, np.max(np.abs(want), axis=1))
+    assert per_session.max() <= 1 / 128, (int(per_session.argmax()), float(per_session.max()))
 
 
 def test_config4_full_width_chunking_invariance_and_determinism():
     """12 layers, d 768, 12 x 64, SwiGLU 2048, vocab 32000: prefilling 96 tokens at once or as 64 + 32 must give the
-    same greedy continuation and (to bf16 resolution) the same K/V rows; rerunning gives identical ids."""
+    same last-position logits to the bf16-path tolerance (2e-2 relative), the same greedy id wherever the top two
+    logits are further apart than that error, and (to bf16 resolution) the same K/V rows; rerunning gives identical
+    ids."""
     cfg = GptConfig(vocab_size=32000, max_sequence_length=2048, embed_dim=768, num_heads=12, feed_forward_dim=2048,
                     num_layers=12, layer_norm_epsilon=1e-5, activation="swiglu", weight_dtype="bf16")
     arrays = normal_model_arrays(cfg, seed=5, std=0.02)
@@ -136,16 +152,19 @@ def test_config4_full_width_chunking_invariance_and_determinism():
     ids = np.random.default_rng(55).integers(0, cfg.vocab_size, size=(batch, prompt_len)).astype(np.uint32)
 
     def session():
-        s = B200Session(cfg, batch, 160, logits_mode="none")
+        s = B200Session(cfg, batch, 160, logits_mode="last")
         for i, a in enumerate(arrays):
             s.refresh(i, a)
         return s
 
+    prefill_logits = []
+
     def greedy(s, chunks):
         position, nxt = 0, None
         for c in chunks:
-            _, nxt = s.decode_full(ids[:, position:position + c], position)
+            logits, nxt = s.decode_full(ids[:, position:position + c], position)
             position += c
+        prefill_logits.append(logits.reshape(batch, cfg.vocab_size).copy())
         out = [nxt.copy()]
         for step in range(steps):
             _, nxt = s.decode_full(nxt.reshape(batch, 1), prompt_len + step)
@@ -161,10 +180,16 @@ def test_config4_full_width_chunking_invariance_and_determinism():
     ka, kb = a.read_cache(0), b.read_cache(0)
     assert np.max(np.abs(ka[:, :prompt_len] - kb[:, :prompt_len])) <= np.max(np.abs(ka)) / 64
     assert np.all(ka[:, prompt_len + steps:] == 0)
-    # different chunking changes the order of bf16 roundings upstream, so ids may differ only where the top two
-    # logits are within rounding of each other; on this seed the continuations agree for most sessions
-    agree = (whole == split).all(axis=0)
-    assert agree.mean() >= 0.5
+    # different chunking changes which kernels (and which bf16 rounding points) produce the rows, so the logits agree
+    # to the tolerance of the bf16 path and the first greedy id may differ only where the top two are that close
+    lw, ls = prefill_logits[0], prefill_logits[1]
+    assert np.array_equal(lw, prefill_logits[2])
+    scale = float(np.max(np.abs(lw)))
+    err = np.max(np.abs(lw - ls), axis=1)
+    assert err.max() <= 2e-2 * scale, float(err.max() / scale)
+    top2 = np.sort(lw, axis=1)[:, -2:]
+    decided = (top2[:, 1] - top2[:, 0]) > 2 * err
+    assert np.array_equal(whole[0][decided], split[0][decided])
     assert whole.min() >= 0 and whole.max() < cfg.vocab_size
 
 
@@ -197,3 +222,61 @@ def test_config4_wide_tile_epilogues_agree_with_narrow_tile_epilogues():
     for w, n in zip(wide, narrow):
         assert np.array_equal(w[:8, :prompt_len].view(np.uint32), n[:, :prompt_len].view(np.uint32))
     assert np.array_equal(wide_ids[:, :8], narrow_ids)
+
+
+def test_config4_serving_shape_end_to_end_against_checker():
+    """The configuration the benchmark times, against the CPU checker: 12 layers, d 768, 12 x 64, SwiGLU 2048, vocab
+    32000, a 256-session handle, one 512-token prefill chunk (wide-tile QKV / SwiGLU epilogues with bulk tensor stores,
+    the in-place residual reduce-add, four key blocks of the tcgen05 prefill attention), then nine single-token steps
+    from position 512 (the first launched kernel by kernel, the rest replayed from the captured graph).  The checker
+    (f32, reference operation order, bf16-rounded matrices) follows two of the 256 sessions and is fed the ids the
+    library picked, so one close call does not fork the two histories.  Bar: last-position logits within 2e-2 of the
+    checker's (max-abs error over max-abs value) at every step, and the same greedy id wherever the checker's top two
+    logits are further apart than twice the error seen.  Mirrors tests/kv_cache.rs:29-69 (decode == full forward
+    across chunk splits) at serving size."""
+    from oracle import oracle
+    cfg = GptConfig(vocab_size=32000, max_sequence_length=2048, embed_dim=768, num_heads=12, feed_forward_dim=2048,
+                    num_layers=12, layer_norm_epsilon=1e-5, activation="swiglu", weight_dtype="bf16")
+    arrays = normal_model_arrays(cfg, seed=5, std=0.02)
+    batch, prefill, steps, capacity = 256, 512, 9, 528
+    watched = [5, 203]                       # one session from each 128-row tile of the decode GEMMs
+    ids = np.random.default_rng(57).integers(0, cfg.vocab_size, size=(batch, prefill)).astype(np.uint32)
+
+    def run(mode):
+        s = B200Session(cfg, batch, capacity, logits_mode=mode)
+        for i, a in enumerate(arrays):
+            s.refresh(i, a)
+        logits, nxt = s.decode_full(ids, 0)
+        rows = [None if logits is None else logits.reshape(batch, cfg.vocab_size)[watched].copy()]
+        picks = [nxt.copy()]
+        for step in range(steps):
+            logits, nxt = s.decode_full(nxt.reshape(batch, 1), prefill + step)
+            rows.append(None if logits is None else logits.reshape(batch, cfg.vocab_size)[watched].copy())
+            picks.append(nxt.copy())
+        s.close()
+        return rows, np.stack(picks)
+
+    got_logits, got_ids = run("last")
+    # the benchmark's mode: no logits leave the device, the greedy id comes out of the LM-head epilogue
+    _, fused_ids = run("none")
+    assert np.array_equal(fused_ids, got_ids)
+
+    oracle.set_threads(oracle.max_threads())
+    ref = oracle.OracleBackend(cfg, len(watched), capacity)
+    for i, a in enumerate(arrays):
+        ref.refresh(i, oracle.bf16_round_np(a) if a.ndim == 2 else a)
+    want = [ref.decode(ids[watched], 0).reshape(len(watched), prefill, cfg.vocab_size)[:, -1].copy()]
+    for step in range(steps):
+        fed = got_ids[step][watched].reshape(len(watched), 1)
+        want.append(ref.decode(fed, prefill + step).reshape(len(watched), cfg.vocab_size).copy())
+    oracle.set_threads(1)
+
+    for step, (g, w) in enumerate(zip(got_logits, want)):
+        assert np.all(np.isfinite(g))
+        err = np.max(np.abs(g - w), axis=1)
+        scale = np.max(np.abs(w), axis=1)
+        assert np.all(err <= 2e-2 * scale), (step, (err / scale).tolist())
+        top2 = np.sort(w, axis=1)[:, -2:]
+        for j, session in enumerate(watched):
+            if top2[j, 1] - top2[j, 0] > 2 * err[j]:
+                assert int(got_ids[step][session]) == oracle.argmax_last(w[j]), (step, session)

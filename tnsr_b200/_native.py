@@ -71,7 +71,6 @@ SIGNATURES = {
     "tnsr_b200_decode_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _u64, _u32, _u32, _u32, _u32, _vp]),
     "tnsr_b200_decode_attention_static": (_i, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _vp]),
     "tnsr_b200_prefill_attention": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _vp]),
-    "tnsr_b200_stream_read_probe": (_i, [_vp, _u64, _u32, _u32, C.POINTER(C.c_uint64), _vp]),
     "tnsr_b200_argmax": (_i, [_vp, _vp, _u32, _u32, _vp]),
 }
 

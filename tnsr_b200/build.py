@@ -10,6 +10,7 @@ entry points of ``include/tnsr_b200.h``.  ``strict.cu`` is compiled with
 from __future__ import annotations
 
 import argparse
+import glob
 import os
 import shutil
 import subprocess
@@ -22,7 +23,7 @@ OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(CSRC, "libtnsr_b200.so")
 
 SOURCES = ["decoder.cu", "ops_api.cu", "elementwise.cu", "strict.cu", "gemm.cu", "gemm_skinny.cu", "attention.cu", "prefill.cu", "prefill_tc.cu",
-           "decode_attention_static.cu", "probe.cu"]
+           "decode_attention_static.cu"]
 EXTRA = {"strict.cu": ["--fmad=false"]}
 
 BASE_FLAGS = [
@@ -48,7 +49,8 @@ def _stale(target: str, deps) -> bool:
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
     sources = list(SOURCES)
-    headers = [os.path.join(CSRC, "common.cuh"), os.path.join(HERE, "..", "include", "tnsr_b200.h")]
+    # every object depends on every header of the library: editing any .cuh (or the public header) rebuilds all
+    headers = sorted(glob.glob(os.path.join(CSRC, "*.cuh"))) + [os.path.join(HERE, "..", "include", "tnsr_b200.h")]
     jobs = []
     for src in sources:
         obj = os.path.join(OBJ, src.replace(".cu", ".o"))

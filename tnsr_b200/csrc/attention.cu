@@ -678,8 +678,6 @@ int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v
         // partial results, no merge) or an even split of every session.  That is worth more than the SMs left idle:
         // 256 sessions on 128 CTAs take 81 us per launch against 86 us on 148 (measured), as long as at least three
         // quarters of the SMs stay in use.
-        static int env_ctas = -1;   // measurement switch: TNSR_B200_DA_CTAS=n forces the grid
-        if (env_ctas < 0) { const char* v = std::getenv("TNSR_B200_DA_CTAS"); env_ctas = v ? atoi(v) : 0; }
         uint32_t aligned = 0;
         if (batch >= grid) {
             for (uint32_t g = grid; g >= 1 && 4 * g >= 3 * grid; --g)
@@ -689,7 +687,6 @@ int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v
             if (4 * aligned < 3 * grid) aligned = 0;
         }
         if (aligned) grid = aligned;
-        if (env_ctas > 0 && (uint32_t)env_ctas <= DA_MAX_CTAS) grid = (uint32_t)env_ctas;
     }
     if (plan) {
         launch_kernel(da_plan_kernel, dim3(1), dim3(1024), 0, stream, d_lengths, d_position, extra, batch, heads, capacity, grid,

@@ -20,7 +20,10 @@
 //    once per device with cudaGetSymbolAddress (below, under a lock, with that
 //    device current) and that address is what the kernels receive.  The first
 //    call on a device performs this look-up; make that first call before any
-//    stream capture begins.
+//    stream capture begins.  The address is remembered per device ordinal for the
+//    life of the process, so it is tied to the device's primary context: after
+//    cudaDeviceReset, or under another context on the same ordinal, it is stale and
+//    this entry point must not be used.
 //  * Shapes whose workspace (tnsr_b200_decode_attention_workspace) exceeds the array are rejected with
 //    TNSR_B200_ERR_UNSUPPORTED and a message that states both sizes.
 //  * Every call reuses the same bytes and finds the previous call's contents in

@@ -24,13 +24,6 @@
 namespace tb {
 
 int g_gemm_engine = 0;
-// measurement switch: TNSR_B200_TMA_STORE=0 keeps the bf16 epilogues on per-lane stores
-static bool t_tma_store = [] { const char* v = std::getenv("TNSR_B200_TMA_STORE"); return !(v && v[0] == '0'); }();
-// measurement switch: TNSR_B200_TMA_REDUCE=0 keeps the in-place residual update in the warps (read, add, store)
-static bool t_tma_reduce = [] { const char* v = std::getenv("TNSR_B200_TMA_REDUCE"); return !(v && v[0] == '0'); }();
-// measurement switch: TNSR_B200_EPI16=0 keeps every tcgen05 GEMM at 8 epilogue warps
-static bool t_epi16 = [] { const char* v = std::getenv("TNSR_B200_EPI16"); return !(v && v[0] == '0'); }();
-
 struct EpiParams {
     GemmEpilogue ep;
     GemmQkvTargets qkv;
@@ -746,7 +739,7 @@ static int launch_tc_e(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
 // is why longer K keeps 8: there the deeper ring is worth more).
 template <int BN, int MODE>
 static int launch_tc_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap* mo, const TcParams& prm, cudaStream_t stream) {
-    if (BN == 256 && (MODE == GEMM_QKV || MODE == GEMM_SWIGLU) && t_epi16 && prm.k <= 1024)
+    if (BN == 256 && (MODE == GEMM_QKV || MODE == GEMM_SWIGLU) && prm.k <= 1024)
         return launch_tc_e<BN, MODE, (BN == 256 && (MODE == GEMM_QKV || MODE == GEMM_SWIGLU)) ? 16 : 8>(ma, mb, mo, prm, stream);
     return launch_tc_e<BN, MODE, 8>(ma, mb, mo, prm, stream);
 }
@@ -839,7 +832,7 @@ static int launch_gemm_impl(const bf16* a, const bf16* bt, void* out, uint32_t l
     prm.tma_reduce = 0;
     prm.tma_store = 0;
     if (mode == GEMM_PLAIN && ep.out_dtype == TNSR_B200_F32 && ep.residual && ep.residual == out && ep.ldr == ldc &&
-        ep.rows_per_session == 0 && !ep.round_bf16 && t_tma_reduce && ldc % 4 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) {
+        ep.rows_per_session == 0 && !ep.round_bf16 && ldc % 4 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) {
         EncodeTiledFn fn = encode_fn();
         cuuint64_t dims[2] = {n, m};
         cuuint64_t strides[1] = {(cuuint64_t)ldc * 4};
@@ -855,7 +848,7 @@ static int launch_gemm_impl(const bf16* a, const bf16* bt, void* out, uint32_t l
     // epilogue is the bottleneck and sixteen warps share the work -- the QKV and SwiGLU epilogues of wide tiles with a
     // short K (prefill 26.4 -> 25.8 ms) -- and costs 10 % on the plain bf16 epilogue with eight warps, which keeps
     // per-lane stores.
-    if (t_tma_store && (mode == GEMM_QKV || mode == GEMM_SWIGLU) && bn == 256 && k <= 1024 && ep.rows_per_session == 0 &&
+    if ((mode == GEMM_QKV || mode == GEMM_SWIGLU) && bn == 256 && k <= 1024 && ep.rows_per_session == 0 &&
         !ep.round_bf16) {
         EncodeTiledFn fn = encode_fn();
         auto bf16_map = [&](CUtensorMap* map, void* base, uint64_t cols, uint64_t rows, uint64_t ld, uint32_t box_cols,

@@ -116,7 +116,10 @@ int tnsr_b200_decode_attention(const void* q, const void* k_cache, const void* v
                                void* workspace, uint64_t workspace_bytes, uint32_t batch, uint32_t capacity, uint32_t heads,
                                uint32_t head_dim, void* stream) {
     if (!q || !k_cache || !v_cache || !lengths || !out || !workspace) return bad("decode_attention: null pointer");
-    // the first 16 bytes past the header words hold the kernel's status word
+    // nothing may be written before the size is known to fit (the status word below lives inside the workspace)
+    if (workspace_bytes < decode_attention_workspace_bytes(batch, capacity, heads, head_dim) || workspace_bytes < 256)
+        return bad("decode_attention: workspace smaller than tnsr_b200_decode_attention_workspace() asks for");
+    // bytes 64..67 of the workspace hold the kernel's status word
     int* d_status = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(workspace) + 64);
     cudaError_t e = cudaMemsetAsync(d_status, 0, 4, as_stream(stream));
     if (e != cudaSuccess) {

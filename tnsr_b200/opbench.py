@@ -5,7 +5,6 @@
     python -m tnsr_b200.opbench mlp         # configuration 2: fused SwiGLU MLP 4096 x 2048 -> 5632 -> 2048
     python -m tnsr_b200.opbench attention   # configuration 3: 64 sessions x 16 heads x 64, ragged lengths <= 4096
     python -m tnsr_b200.opbench serving_attention  # configuration 4's decode attention: 256 x 12 x 64, 641 live keys
-    python -m tnsr_b200.opbench stream_read # read-bandwidth ceiling of the bulk-copy K/V ring
     python -m tnsr_b200.opbench elementwise # LayerNorm, SwiGLU, embedding, greedy pick
     python -m tnsr_b200.opbench prefill_attention  # configuration 4's prefill attention on both engines
     python -m tnsr_b200.opbench all
@@ -116,12 +115,15 @@ def emit(**kw):
         print(json.dumps(kw), flush=True)
 
 
-def bench_gemm(samples):
+def bench_gemm(samples, shapes=None, outs=("bf16", "f32")):
     hbm, tf, kind = peaks()
-    shapes = [(n, n, n) for n in (1024, 2048, 4096, 8192)] + [(m, 4096, 4096) for m in (1, 8, 64)]
+    if shapes is None:
+        shapes = [(n, n, n) for n in (1024, 2048, 4096, 8192)] + [(m, 4096, 4096) for m in (1, 8, 64)]
     g = torch.Generator(device="cuda").manual_seed(2)
     for m, n, k in shapes:
         for out_dtype, name in ((1, "bf16"), (0, "f32")):
+            if name not in outs:
+                continue
             osz = 2 if out_dtype else 4
             per_set = 2 * (m * k + n * k) + osz * m * n
             sets = copies_for(per_set)
@@ -267,19 +269,6 @@ def bench_prefill_attention(samples, sessions=64):
     emit(op="prefill_attention", max_abs_difference_between_engines=float((results["tcgen05"] - results["mma.sync"]).abs().max()))
 
 
-def bench_stream_read(samples):
-    """Ceiling of the bulk-copy K/V ring: stream 505 MB (one decode-attention launch of configuration 4) and discard."""
-    hbm, _, kind = peaks()
-    buf = torch.randint(0, 255, (505 << 20,), dtype=torch.uint8, device="cuda")
-    moved = C.c_uint64()
-    for stage_bytes, stages in ((16384, 4), (32768, 4), (49152, 4), (65536, 2), (65536, 3)):
-        def launch(_):
-            ok(lib().tnsr_b200_stream_read_probe(ptr(buf), buf.numel(), stage_bytes, stages, C.byref(moved), stream()))
-        ms, _ = timed(launch, 1, samples)
-        emit(op="stream_read_probe", stage_bytes=stage_bytes, stages=stages, ms=ms, gbs=moved.value / ms / 1e6,
-             frac_hbm=moved.value / ms / 1e6 / hbm, peaks=kind)
-
-
 def bench_elementwise(samples):
     hbm, _, kind = peaks()
     rows, d = 131072, 768
@@ -305,16 +294,16 @@ def bench_elementwise(samples):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "serving_gemms", "mlp", "attention", "serving_attention", "stream_read", "elementwise", "prefill_attention", "all"])
+    ap.add_argument("what", choices=["gemm", "serving_gemms", "mlp", "attention", "serving_attention", "elementwise", "prefill_attention", "all"])
     ap.add_argument("--samples", type=int, default=20)
     args = ap.parse_args()
     if not torch.cuda.is_available():
         sys.exit("opbench needs a CUDA device")
-    todo = (["gemm", "serving_gemms", "mlp", "attention", "serving_attention", "stream_read", "elementwise", "prefill_attention"]
+    todo = (["gemm", "serving_gemms", "mlp", "attention", "serving_attention", "elementwise", "prefill_attention"]
             if args.what == "all" else [args.what])
     for name in todo:
         {"gemm": bench_gemm, "serving_gemms": bench_serving_gemms, "mlp": bench_mlp, "attention": bench_attention,
-         "serving_attention": lambda n: bench_attention(n, serving=True), "stream_read": bench_stream_read,
+         "serving_attention": lambda n: bench_attention(n, serving=True),
          "elementwise": bench_elementwise, "prefill_attention": bench_prefill_attention}[name](args.samples)
 
 
