@@ -71,6 +71,16 @@ typedef enum tnsr_b200_logits_mode {
     TNSR_B200_LOGITS_NONE = 2  /* no logits leave the device, argmax ids only         */
 } tnsr_b200_logits_mode;
 
+/* `GptPrefillMode` (src/nn/kv_cache.rs:28-34).  AUTO lets multi-token chunks run
+ * on the tiled tensor-core attention kernels; SCALAR keeps them on the
+ * non-tiled scan (one warp per query and head, keys in order), which the
+ * reference describes as "useful as a precision-matched reference".  It only
+ * matters with bf16 weights: the strict f32 path has a single attention kernel. */
+typedef enum tnsr_b200_prefill_mode {
+    TNSR_B200_PREFILL_AUTO = 0,
+    TNSR_B200_PREFILL_SCALAR = 1
+} tnsr_b200_prefill_mode;
+
 /* Session configuration: the seven `GptConfig` fields (src/nn.rs:543-552),
  * the `GptDecoder::new` arguments (src/nn/kv_cache.rs:161-167) and the
  * precision choices.
@@ -96,6 +106,7 @@ typedef struct tnsr_b200_config {
     uint32_t capacity;     /* K/V rows per session, <= max_sequence_length         */
     int32_t device;        /* CUDA ordinal (the reference always uses 0)           */
     uint32_t logits_mode;  /* tnsr_b200_logits_mode */
+    uint32_t prefill_mode; /* tnsr_b200_prefill_mode */
 } tnsr_b200_config;
 
 typedef struct tnsr_b200_decoder tnsr_b200_decoder;
@@ -119,6 +130,20 @@ TNSR_B200_API uint64_t tnsr_b200_kernel_launches(void);
  * also keeps prefill attention off tcgen05 (the warp-level mma.sync kernel
  * runs), which is how tests compare the two. */
 TNSR_B200_API int tnsr_b200_set_gemm_engine(int engine);
+/* Every wait inside a kernel (a producer/consumer barrier between the copy, MMA
+ * and epilogue roles) is bounded: when it lasts longer than this limit the
+ * kernel stops waiting, lets copies in flight land, releases what it holds and
+ * records TNSR_B200_ERR_TIMEOUT in the caller's status word; a session then
+ * enters the failed state until reset, like the `failed` flag of
+ * src/nn/kv_cache.rs:262-265,331,387.  Default 2 s; accepted range 1 us .. 60 s.
+ * Process-wide; it applies to kernels launched (or captured) afterwards. */
+TNSR_B200_API int tnsr_b200_set_wait_limit_ns(uint64_t ns);
+/* Test hook (no reference counterpart): the next tcgen05 GEMM launched from
+ * the calling thread leaves out the operand copies of k-block `k_block` of its
+ * first tile.  Nothing faults: the MMA role's bounded wait for that stage runs
+ * out after the wait limit and the kernel returns through its time-out path,
+ * which is the only way to exercise that path on healthy hardware. */
+TNSR_B200_API int tnsr_b200_test_lose_gemm_stage(uint32_t k_block);
 
 /* ---- session: replaces cuda::CudaDecoder -------------------------------- */
 

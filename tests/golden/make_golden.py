@@ -12,6 +12,9 @@ and there is no toolchain for it); the vectors are the literals of
   tests/indexed_ops.rs:25-36          embedding gather
   tests/transformer.rs:86-103         batched matmul
   src/graph/mixed.rs:126-135          bf16 narrowing
+It also copies the reference's own data fixtures of the forty_five example (examples/forty_five/fixtures/{tiny,
+tiny-separate}: the parameter archive `manifest.json` + `weights.f32`, and `reference.json`, the inputs and expected
+outputs its tests check the encoder against) into forty_five/ byte for byte.
 The second half derives fixtures from this repository's own CPU checker
 (oracle/), so the GPU tests can run where neither tnsr nor the generator is
 present: greedy token ids and logits of configuration 0.
@@ -94,10 +97,22 @@ def config0(activation):
     }
 
 
+def copy_forty_five_fixtures(ref):
+    import shutil
+    for variant in ("tiny", "tiny-separate"):
+        src = os.path.join(ref, "examples/forty_five/fixtures", variant)
+        dst = os.path.join(HERE, "forty_five", variant)
+        os.makedirs(dst, exist_ok=True)
+        for name in ("manifest.json", "weights.f32", "reference.json"):
+            if os.path.exists(os.path.join(src, name)):
+                shutil.copyfile(os.path.join(src, name), os.path.join(dst, name))
+
+
 def main():
     if len(sys.argv) != 2:
         sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of tninesling/tnsr>")
     ref = sys.argv[1]
+    copy_forty_five_fixtures(ref)
     data = literal_vectors()
     data["activations"] = activation_vectors(ref)
     with open(os.path.join(HERE, "reference_vectors.json"), "w") as f:

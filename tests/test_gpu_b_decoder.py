@@ -438,3 +438,74 @@ def test_full_context_forward_and_uncached_generate_on_the_gpu():
     from tnsr_b200.nn import TnsrError
     with pytest.raises(TnsrError):
         model.forward(Backend.Cuda, [list(range(10))])
+
+
+def test_a_wait_that_runs_out_fails_the_session_until_reset():
+    """The `failed` flag of src/nn/kv_cache.rs:262-265,331,387 on the device side: every producer/consumer wait
+    inside the tensor-core kernels is bounded, and when one runs out the kernel returns (nothing traps, nothing spins
+    for ever), the step reports ERR_TIMEOUT, the handle refuses further steps until `reset`, and after `reset` it
+    computes what a fresh handle computes.  The wait is made to run out on healthy hardware by the library's test
+    hook: the next GEMM's copy role leaves one stage of its ring unfilled, so the MMA role waits for data that never
+    arrives; the wait limit is lowered to 2 ms for the duration of the test."""
+    from tnsr_b200 import _native
+    lib = _native.lib()
+    cfg = GptConfig(vocab_size=512, max_sequence_length=64, embed_dim=256, num_heads=4, feed_forward_dim=512,
+                    num_layers=2, layer_norm_epsilon=1e-5, activation="swiglu", weight_dtype="bf16")
+    arrays = normal_model_arrays(cfg, seed=31, std=0.05)
+    ids = np.random.default_rng(32).integers(0, cfg.vocab_size, size=(2, 12)).astype(np.uint32)
+
+    def session():
+        s = B200Session(cfg, 2, 32)
+        for i, a in enumerate(arrays):
+            s.refresh(i, a)
+        return s
+
+    fresh = session()
+    want, _ = fresh.decode_full(ids, 0)
+    fresh.close()
+
+    s = session()
+    assert lib.tnsr_b200_set_wait_limit_ns(10) == -1            # below the accepted range
+    assert lib.tnsr_b200_set_wait_limit_ns(2_000_000) == 0
+    try:
+        assert lib.tnsr_b200_test_lose_gemm_stage(2) == 0       # k-block 2 of the first projection's first tile
+        u32p = _native.C.POINTER(_native.C.c_uint32)
+        fp = _native.C.POINTER(_native.C.c_float)
+        logits = np.empty(2 * 12 * cfg.vocab_size, dtype=np.float32)
+        code = lib.tnsr_b200_decoder_decode(s.handle, ids.ctypes.data_as(u32p), 12, 0, logits.ctypes.data_as(fp), None)
+        assert code == -7, _native.STATUS.get(code, code)       # TNSR_B200_ERR_TIMEOUT
+        assert "timed out" in _native.last_error(s.handle)
+        code = lib.tnsr_b200_decoder_decode(s.handle, ids.ctypes.data_as(u32p), 12, 0, logits.ctypes.data_as(fp), None)
+        assert code == -6                                       # TNSR_B200_ERR_FAILED_STATE
+        assert "reset the cache before reuse" in _native.last_error(s.handle)
+    finally:
+        assert lib.tnsr_b200_set_wait_limit_ns(2_000_000_000) == 0
+    s.reset()
+    got, _ = s.decode_full(ids, 0)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    s.close()
+
+
+def test_prefill_mode_scalar_keeps_multi_token_chunks_off_the_tiled_kernels():
+    """`GptPrefillMode::Scalar` (src/nn/kv_cache.rs:28-34) with bf16 weights: chunks run on the non-tiled scan instead
+    of the tensor-core prefill kernels.  Both modes must meet the bf16 tolerance against the checker, and they must
+    actually take different kernels (the logits differ in the last bits somewhere)."""
+    cfg = GptConfig(vocab_size=640, max_sequence_length=192, embed_dim=256, num_heads=4, feed_forward_dim=512,
+                    num_layers=2, layer_norm_epsilon=1e-5, activation="gelu", weight_dtype="bf16")
+    arrays = normal_model_arrays(cfg, seed=41, std=0.05)
+    model = Gpt(cfg)
+    set_model_arrays(model, arrays)
+    ids = np.random.default_rng(42).integers(0, cfg.vocab_size, size=(3, 150)).astype(np.uint32)
+    from oracle import oracle
+    ref = oracle.OracleModel(cfg.vocab_size, cfg.max_sequence_length, cfg.embed_dim, cfg.num_heads, cfg.feed_forward_dim,
+                             cfg.num_layers, cfg.layer_norm_epsilon, "gelu")
+    ref.set_params([oracle.bf16_round_np(a) if a.ndim == 2 else a for a in arrays])
+    want = ref.forward(ids)
+    outs = {}
+    for mode in (GptPrefillMode.Auto, GptPrefillMode.Scalar):
+        dec = gpu_decoder(model, 3, 192, GptDecoderOptions(prefill=mode))
+        first = dec.decode(ids[:, :96].reshape(-1).tolist()).reshape(3, 96, cfg.vocab_size)
+        second = dec.decode(ids[:, 96:].reshape(-1).tolist()).reshape(3, 54, cfg.vocab_size)
+        outs[mode] = np.concatenate([first, second], axis=1)
+        assert rel_err(outs[mode], want) <= 2e-2
+    assert not np.array_equal(outs[GptPrefillMode.Auto], outs[GptPrefillMode.Scalar])

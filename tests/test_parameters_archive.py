@@ -80,3 +80,16 @@ def test_gpt_archive_roundtrip(tmp_path, activation):
     config["num_layers"] = 3
     with pytest.raises(TnsrError):
         gpt_from_named(named, config)
+
+
+@pytest.mark.parametrize("variant", ["tiny", "tiny-separate"])
+def test_reference_written_archives_reload_and_resave_byte_for_byte(tmp_path, variant):
+    """The archives tnsr's own forty_five example ships (examples/forty_five/fixtures/*, written by the Rust
+    `NamedParameters::save`, src/parameters.rs:100-210): loading one and saving it again must reproduce both files
+    exactly -- same tensor order, offsets, JSON layout and f32 bytes -- so archives pass between the two sides."""
+    src = os.path.join(os.path.dirname(__file__), "golden", "forty_five", variant)
+    named, config = NamedParameters.load(src)
+    assert config["token_dim"] == 8 and config["use_swiglu"] is True
+    named.save(str(tmp_path), config)
+    for name in ("manifest.json", "weights.f32"):
+        assert (tmp_path / name).read_bytes() == open(os.path.join(src, name), "rb").read(), name

@@ -20,6 +20,7 @@ STATUS = {
 ACT = {"relu": 0, "gelu": 1, "swiglu": 2}
 DTYPE = {"f32": 0, "bf16": 1}
 LOGITS = {"all": 0, "last": 1, "none": 2}
+PREFILL = {"auto": 0, "scalar": 1}
 
 
 class Config(C.Structure):
@@ -28,7 +29,7 @@ class Config(C.Structure):
         ("num_heads", C.c_uint32), ("feed_forward_dim", C.c_uint32), ("num_layers", C.c_uint32),
         ("layer_norm_epsilon", C.c_float), ("activation", C.c_uint32), ("weight_dtype", C.c_uint32),
         ("kv_dtype", C.c_uint32), ("batch", C.c_uint32), ("capacity", C.c_uint32), ("device", C.c_int32),
-        ("logits_mode", C.c_uint32),
+        ("logits_mode", C.c_uint32), ("prefill_mode", C.c_uint32),
     ]
 
 
@@ -42,6 +43,8 @@ SIGNATURES = {
     "tnsr_b200_last_error": (C.c_char_p, [_vp]),
     "tnsr_b200_kernel_launches": (_u64, []),
     "tnsr_b200_set_gemm_engine": (_i, [_i]),
+    "tnsr_b200_set_wait_limit_ns": (_i, [_u64]),
+    "tnsr_b200_test_lose_gemm_stage": (_i, [_u32]),
     "tnsr_b200_decoder_create": (_i, [C.POINTER(Config), C.POINTER(_vp)]),
     "tnsr_b200_decoder_destroy": (None, [_vp]),
     "tnsr_b200_decoder_param_count": (_u32, [_vp]),

@@ -117,7 +117,6 @@ int launch_attention_generic(const bf16* q, const bf16* k_cache, const bf16* v_c
 constexpr uint32_t DA_KS = 16;             // keys per ring stage
 constexpr uint32_t DA_MAX_STAGES = 8;
 constexpr uint32_t DA_SMEM_BUDGET = 200 * 1024;
-constexpr uint64_t DA_WAIT_LIMIT_NS = 2000000000ull;
 constexpr uint32_t DA_MAX_CTAS = 256;      // upper bound on the grid (one CTA per SM)
 
 // A work item: keys [key0, key0 + nkeys) of one session, all heads.  `slot` is the index of its
@@ -308,14 +307,14 @@ __device__ __forceinline__ uint64_t da_timer_ns() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ bool da_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool da_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint64_t limit_ns) {
     if (da_mbar_try_wait(bar, parity)) return true;
     const uint64_t start = da_timer_ns();
     for (uint32_t it = 1;; ++it) {
         if (da_mbar_try_wait(bar, parity)) return true;
         if ((it & 63u) == 0) {
             if (*abort_flag) return false;
-            if (da_timer_ns() - start > DA_WAIT_LIMIT_NS) {
+            if (da_timer_ns() - start > limit_ns) {
                 *abort_flag = 1;
                 return false;
             }
@@ -354,6 +353,7 @@ struct DaParams {
     uint32_t stages;
     float scale_log2;
     int* d_status;
+    uint64_t wait_limit_ns;   // bound of every mbarrier wait (tnsr_b200_set_wait_limit_ns)
 };
 
 // HD: head width; LPK = HD / 8 lanes share one (key, head) row slice, each lane
@@ -401,7 +401,7 @@ decode_attention_kernel(DaParams P) {
                 const size_t base = ((size_t)it.session * P.capacity + it.key0) * d;
                 const uint32_t n_stages = (it.nkeys + DA_KS - 1) / DA_KS;
                 for (uint32_t s = 0; s < n_stages; ++s) {
-                    if (!da_mbar_wait(empty_bar + stage, phase ^ 1, abort_flag)) { ok = false; break; }
+                    if (!da_mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, P.wait_limit_ns)) { ok = false; break; }
                     const uint32_t nk = min(DA_KS, it.nkeys - s * DA_KS);
                     uint8_t* sk = ring + (size_t)stage * stage_bytes;
                     DaStageMeta mt;
@@ -430,7 +430,7 @@ decode_attention_kernel(DaParams P) {
         bool ok = true;
         for (uint32_t item = item_begin; ok && item < item_end; ++item) {
             for (;;) {
-                if (!da_mbar_wait(full_bar + stage, phase, abort_flag)) { ok = false; break; }
+                if (!da_mbar_wait(full_bar + stage, phase, abort_flag, P.wait_limit_ns)) { ok = false; break; }
                 const DaStageMeta mt = meta[stage];
                 const uint8_t* sk = ring + (size_t)stage * stage_bytes;
                 const uint8_t* sv = sk + k_bytes;
@@ -709,6 +709,7 @@ int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v
     P.batch = batch; P.capacity = capacity; P.heads = heads; P.stages = stages;
     P.scale_log2 = (1.0f / sqrtf((float)head_dim)) * 1.4426950408889634f;
     P.d_status = d_status;
+    P.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
     const uint32_t threads = (consumers + 1) * 32;
     if (hpw == 1) {
         return head_dim == 32 ? launch_da_t<32, 1>(P, threads, smem, grid, stream)

@@ -18,6 +18,10 @@ typedef __nv_bfloat16 bf16;
 // ---- host-side plumbing ----------------------------------------------------
 
 extern std::atomic<uint64_t> g_launches;       // kernels launched by this library
+extern std::atomic<uint64_t> g_wait_limit_ns;  // bound of every device-side barrier wait; launchers copy it into kernel parameters
+// Test hook: when non-zero, the next tcgen05 GEMM launched from this thread loses the copies of k-block (value - 1) of
+// its first tile, so a bounded wait runs out and the kernel reports DEV_TIMEOUT; the launcher clears it.
+extern thread_local uint32_t t_lose_gemm_stage;
 void set_thread_error(const std::string& msg);  // message for calls without a handle
 const char* thread_error();
 

@@ -12,6 +12,7 @@
 
 namespace tb {
 std::atomic<uint64_t> g_launches{0};
+std::atomic<uint64_t> g_wait_limit_ns{2000000000ull};
 static thread_local std::string t_error;
 void set_thread_error(const std::string& msg) { t_error = msg; }
 const char* thread_error() { return t_error.c_str(); }
@@ -402,7 +403,7 @@ int step_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, 
                                                 d_position ? 1 : position + 1, att, dec->attn_ws, dec->attn_ws_bytes, B,
                                                 c.capacity, H, hd, !planned, dec->d_status, st));
             planned = true;
-        } else if (chunk > 1 && prefill_attention_supported(hd)) {
+        } else if (chunk > 1 && prefill_attention_supported(hd) && c.prefill_mode != TNSR_B200_PREFILL_SCALAR) {
             RUN(dec, launch_prefill_attention(q, (const bf16*)L.kcache, (const bf16*)L.vcache, att, B, chunk, position, d_position,
                                               c.capacity, H, hd, dec->d_status, st));
         } else {
@@ -535,7 +536,7 @@ int validate_config(const tnsr_b200_config* c, std::string& why) {
         return TNSR_B200_ERR_INVALID_ARGUMENT;
     }
     if (c->activation > TNSR_B200_ACT_SWIGLU || c->weight_dtype > TNSR_B200_BF16 || c->kv_dtype > TNSR_B200_BF16 ||
-        c->logits_mode > TNSR_B200_LOGITS_NONE) {
+        c->logits_mode > TNSR_B200_LOGITS_NONE || c->prefill_mode > TNSR_B200_PREFILL_SCALAR) {
         why = "invalid enum value in configuration";
         return TNSR_B200_ERR_INVALID_ARGUMENT;
     }
@@ -580,6 +581,17 @@ int tnsr_b200_device_count(void) {
 const char* tnsr_b200_last_error(const tnsr_b200_decoder* dec) { return dec ? dec->error.c_str() : thread_error(); }
 
 uint64_t tnsr_b200_kernel_launches(void) { return g_launches.load(); }
+
+int tnsr_b200_set_wait_limit_ns(uint64_t ns) {
+    if (ns < 1000ull || ns > 60000000000ull) return fail(nullptr, TNSR_B200_ERR_INVALID_ARGUMENT, "wait limit must lie between 1 us and 60 s");
+    g_wait_limit_ns.store(ns);
+    return TNSR_B200_OK;
+}
+
+int tnsr_b200_test_lose_gemm_stage(uint32_t k_block) {
+    t_lose_gemm_stage = k_block + 1;
+    return TNSR_B200_OK;
+}
 
 int tnsr_b200_set_gemm_engine(int engine) {
     if (engine < 0 || engine > 3) return TNSR_B200_ERR_INVALID_ARGUMENT;

@@ -24,6 +24,7 @@
 namespace tb {
 
 int g_gemm_engine = 0;
+thread_local uint32_t t_lose_gemm_stage = 0;
 struct EpiParams {
     GemmEpilogue ep;
     GemmQkvTargets qkv;
@@ -215,6 +216,10 @@ struct TcParams {
     // 1: bf16 destinations are written with bulk tensor stores of 32-row blocks (map_out; map_k / map_v for the caches
     // of the QKV routing) instead of per-lane stores
     uint32_t tma_store;
+    uint64_t wait_limit_ns;   // bound of every mbarrier wait (tnsr_b200_set_wait_limit_ns)
+    // Test hook (0 = off): the producer of CTA 0 leaves out the copies of k-block `lose_kb - 1` of its first tile, so
+    // the MMA warp's wait for that stage runs out and the kernel leaves through its abort path.
+    uint32_t lose_kb;
 };
 
 // Grouped tile order: 8 row-tiles share each column-tile before moving on, so a
@@ -560,11 +565,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 uint32_t tm, tn;
                 tile_coords(tile, prm.tiles_m, prm.tiles_n, tm, tn);
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait(empty_bar + stage, phase ^ 1, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, prm.wait_limit_ns)) { ok = false; break; }
                     uint8_t* sa = smem + stage * S::STAGE_BYTES;
-                    mbar_expect_tx(full_bar + stage, S::STAGE_BYTES);
-                    tma_load_2d(sa, &map_a, (int32_t)(kb * BK), (int32_t)(tm * BM), full_bar + stage);
-                    tma_load_2d(sa + S::A_BYTES, &map_b, (int32_t)(kb * BK), (int32_t)(tn * BN), full_bar + stage);
+                    const bool lost = prm.lose_kb && blockIdx.x == 0 && tile == blockIdx.x && kb + 1 == prm.lose_kb;
+                    if (!lost) {   // a lost stage is never filled: its full barrier stays where it is
+                        mbar_expect_tx(full_bar + stage, S::STAGE_BYTES);
+                        tma_load_2d(sa, &map_a, (int32_t)(kb * BK), (int32_t)(tm * BM), full_bar + stage);
+                        tma_load_2d(sa + S::A_BYTES, &map_b, (int32_t)(kb * BK), (int32_t)(tn * BN), full_bar + stage);
+                    }
                     if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -577,11 +585,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             bool ok = true;
             for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
                 const uint32_t ab = it & 1, aphase = (it >> 1) & 1;
-                if (!mbar_wait(acc_empty + ab, aphase ^ 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(acc_empty + ab, aphase ^ 1, abort_flag, prm.wait_limit_ns)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + ab * BN;
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait(full_bar + stage, phase, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(full_bar + stage, phase, abort_flag, prm.wait_limit_ns)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + stage * S::STAGE_BYTES);
                     const uint64_t adesc = make_kmajor_sw128_desc(sa);
@@ -624,7 +632,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     have_pre = true;
                 }
             }
-            if (!mbar_wait(acc_full + ab, aphase, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(acc_full + ab, aphase, abort_flag, prm.wait_limit_ns)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + ab * BN;
             if (MODE == GEMM_ARGMAX) {
@@ -817,6 +825,9 @@ static int launch_gemm_impl(const bf16* a, const bf16* bt, void* out, uint32_t l
     prm.tiles_m = tiles_m;
     prm.tiles_n = ceil_div(n, bn);
     prm.d_status = d_status;
+    prm.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
+    prm.lose_kb = t_lose_gemm_stage;   // one-shot test hook, see TcParams
+    t_lose_gemm_stage = 0;
     CUtensorMap ma, mb;
     if (!make_map(&ma, a, m, k, lda, BM) || !make_map(&mb, bt, n, k, k, bn)) {
         if (g_gemm_engine == 2) {

@@ -56,6 +56,7 @@ struct SkParams {
     float* partials;       // [tile][split][MP][128]
     uint32_t* counters;    // [tile][4]
     int* d_status;
+    uint64_t wait_limit_ns;
 };
 
 __device__ __forceinline__ void sk_store(const SkParams& P, uint32_t row, uint32_t col, float acc) {
@@ -127,7 +128,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             for (uint32_t kb = kb_begin; kb < kb_end; ++kb) {
-                if (!mbar_wait(empty_bar + stage, phase ^ 1, abort_flag)) break;
+                if (!mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, prm.wait_limit_ns)) break;
                 uint8_t* sw = smem + stage * S::STAGE_BYTES;
                 mbar_expect_tx(full_bar + stage, S::STAGE_BYTES);
                 tma_load_2d(sw, &map_w, (int32_t)(kb * SK_BK), (int32_t)(tile * SK_ROWS), full_bar + stage);
@@ -140,7 +141,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (uint32_t kb = kb_begin; kb < kb_end; ++kb) {
-                if (!mbar_wait(full_bar + stage, phase, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(full_bar + stage, phase, abort_flag, prm.wait_limit_ns)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t sw = smem_u32(smem + stage * S::STAGE_BYTES);
                 const uint64_t wdesc = make_kmajor_sw128_desc(sw);
@@ -157,7 +158,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         // ---------------- epilogue: lane = output column, registers = rows ----------------
         const uint32_t quarter = warp & 3;
         const uint32_t col = tile * SK_ROWS + quarter * 32 + lane;
-        if (kb_end > kb_begin ? mbar_wait(acc_full, 0, abort_flag) : true) {
+        if (kb_end > kb_begin ? mbar_wait(acc_full, 0, abort_flag, prm.wait_limit_ns) : true) {
             tc_fence_after();
             constexpr int LOADS = MP <= 32 ? 1 : MP / 32;
             float acc[LOADS * 32];
@@ -294,6 +295,7 @@ int launch_gemm_skinny(const bf16* a, const bf16* bt, void* out, uint32_t ldc, u
     prm.partials = nullptr;
     prm.counters = nullptr;
     prm.d_status = d_status;
+    prm.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
     if (scratch && reinterpret_cast<uintptr_t>(scratch) % 16 == 0 && scratch_bytes >= gemm_skinny_workspace_bytes() &&
         tiles < (uint32_t)sk_sm_count() && (uint64_t)tiles * 16 <= SK_COUNTER_BYTES) {
         uint32_t splits = std::min(std::min((uint32_t)sk_sm_count() / tiles, num_kb / 2), SK_MAX_SPLITS);

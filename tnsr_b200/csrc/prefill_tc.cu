@@ -71,6 +71,7 @@ struct PtParams {
     uint32_t chunk, position, heads, q_tiles, sessions;
     float scale_log2;
     int* d_status;
+    uint64_t wait_limit_ns;
 };
 
 __global__ void __launch_bounds__(PT_THREADS, 2)
@@ -143,12 +144,12 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 uint32_t q0, h, s, n_blocks;
                 item_coords(item, q0, h, s, n_blocks);
                 // the Q tile is free once every S product of the previous item has been computed
-                if (it > 0 && !mbar_wait(q_empty, (it - 1) & 1, abort_flag)) break;
+                if (it > 0 && !mbar_wait(q_empty, (it - 1) & 1, abort_flag, prm.wait_limit_ns)) break;
                 mbar_expect_tx(q_full, PT_TILE_BYTES);
                 tma_load_3d(q_tile, &map_q, (int32_t)(h * PT_HD), (int32_t)q0, (int32_t)s, q_full);
                 for (uint32_t j = 0; j < n_blocks; ++j, ++g) {
                     const uint32_t stage = g % PT_KV_STAGES;
-                    if (!mbar_wait(kv_empty + stage, ((g / PT_KV_STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(kv_empty + stage, ((g / PT_KV_STAGES) & 1) ^ 1, abort_flag, prm.wait_limit_ns)) { ok = false; break; }
                     uint8_t* dst = kv_ring + stage * PT_KV_BYTES;
                     mbar_expect_tx(kv_full + stage, PT_KV_BYTES);
                     tma_load_3d(dst, &map_k, (int32_t)(h * PT_HD), (int32_t)(j * PT_BK), (int32_t)s, kv_full + stage);
@@ -172,8 +173,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (uint32_t item = blockIdx.x; ok && item < total_items; item += gridDim.x, ++it) {
                 uint32_t q0, h, s, n_blocks;
                 item_coords(item, q0, h, s, n_blocks);
-                if (!mbar_wait(q_full, it & 1, abort_flag)) break;
-                if (!mbar_wait(kv_full + g % PT_KV_STAGES, (g / PT_KV_STAGES) & 1, abort_flag)) break;
+                if (!mbar_wait(q_full, it & 1, abort_flag, prm.wait_limit_ns)) break;
+                if (!mbar_wait(kv_full + g % PT_KV_STAGES, (g / PT_KV_STAGES) & 1, abort_flag, prm.wait_limit_ns)) break;
                 // the score buffer is free: its last reader signalled p_full of the previous block, which was waited for below
                 tc_fence_after();
                 issue_s(g % PT_KV_STAGES);
@@ -181,10 +182,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 for (uint32_t j = 0; j < n_blocks; ++j) {
                     const uint32_t b = g + j, stage = b % PT_KV_STAGES;
                     // P_j is in place and the softmax warps are done with S_j
-                    if (!mbar_wait(p_full, b & 1, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(p_full, b & 1, abort_flag, prm.wait_limit_ns)) { ok = false; break; }
                     if (j + 1 < n_blocks) {
                         const uint32_t next = (b + 1) % PT_KV_STAGES;
-                        if (!mbar_wait(kv_full + next, ((b + 1) / PT_KV_STAGES) & 1, abort_flag)) { ok = false; break; }
+                        if (!mbar_wait(kv_full + next, ((b + 1) / PT_KV_STAGES) & 1, abort_flag, prm.wait_limit_ns)) { ok = false; break; }
                         tc_fence_after();
                         issue_s(next);
                         if (j + 2 == n_blocks) umma_commit(q_empty);   // that was the item's last S product
@@ -221,7 +222,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             slot[half * 128 + row] = mine;
             __syncwarp();
             if (lane == 0) mbar_arrive(pair + quarter);
-            if (!mbar_wait(pair + quarter, pair_uses & 1, abort_flag)) return false;
+            if (!mbar_wait(pair + quarter, pair_uses & 1, abort_flag, prm.wait_limit_ns)) return false;
             other = slot[(half ^ 1) * 128 + row];
             ++pair_uses;
             return true;
@@ -237,7 +238,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             float m = -INFINITY, l = 0.0f, corr_pending = 0.0f;      // l: sum over this thread's key columns only
             // acc = acc * corr + O_b  (this thread's 32 outputs of block b, b counted over all items)
             auto fold = [&](uint32_t b, float corr) -> bool {
-                if (!mbar_wait(o_full, b & 1, abort_flag)) return false;
+                if (!mbar_wait(o_full, b & 1, abort_flag, prm.wait_limit_ns)) return false;
                 tc_fence_after();
                 float v[32];
                 tmem_ld32(lane_taddr + PT_O_COL + half * 32, v);
@@ -249,7 +250,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
             for (uint32_t j = 0; j < n_blocks; ++j) {
                 const uint32_t b = g + j;
-                if (!mbar_wait(s_full, b & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(s_full, b & 1, abort_flag, prm.wait_limit_ns)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t taddr = lane_taddr + half * 64;
                 const uint32_t kbase = j * PT_BK + half * 64;           // first key of this thread's columns
@@ -404,6 +405,7 @@ int launch_prefill_attention_tc(const bf16* q, const bf16* k_cache, const bf16* 
     prm.q_tiles = ceil_div(chunk, (uint32_t)PT_BQ);
     prm.scale_log2 = (1.0f / sqrtf((float)PT_HD)) * 1.4426950408889634f;
     prm.d_status = d_status;
+    prm.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
     prm.sessions = sessions;
     // persistent: two CTAs per SM walk the list of (query tile, head, session) items
     int dev_sms = 0;

@@ -12,7 +12,7 @@
 
 namespace tb {
 
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // a wait that lasts 2 s gives up
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // default of tnsr_b200_set_wait_limit_ns: a wait that lasts 2 s gives up
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -42,15 +42,16 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     return t;
 }
 // Bounded wait: returns false (and raises the CTA-wide abort flag) if the
-// barrier does not flip within WAIT_LIMIT_NS or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+// barrier does not flip within `limit_ns` (the launcher's copy of the process-wide
+// wait limit) or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t start = global_timer_ns();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 63u) == 0) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - start > WAIT_LIMIT_NS) {
+            if (global_timer_ns() - start > limit_ns) {
                 *abort_flag = 1;
                 return false;
             }

@@ -8,7 +8,7 @@ import ctypes as C
 import numpy as np
 
 from . import _native
-from ._native import ACT, DTYPE, LOGITS, Config, NativeError, check, lib
+from ._native import ACT, DTYPE, LOGITS, PREFILL, Config, NativeError, check, lib
 
 
 class B200Session:
@@ -22,7 +22,8 @@ class B200Session:
         self.cfg = Config(config.vocab_size, config.max_sequence_length, config.embed_dim, config.num_heads,
                           config.feed_forward_dim, config.num_layers, config.layer_norm_epsilon,
                           ACT[getattr(config, "activation", "relu")], DTYPE[weight_dtype], DTYPE[kv], batch,
-                          capacity, device, LOGITS[logits_mode])
+                          capacity, device, LOGITS[logits_mode],
+                          PREFILL[options.prefill.value] if options is not None else PREFILL["auto"])
         self.handle = C.c_void_p()
         self.batch, self.capacity, self.vocab = batch, capacity, config.vocab_size
         self.embed_dim = config.embed_dim
