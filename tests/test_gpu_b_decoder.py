@@ -509,3 +509,44 @@ def test_prefill_mode_scalar_keeps_multi_token_chunks_off_the_tiled_kernels():
         outs[mode] = np.concatenate([first, second], axis=1)
         assert rel_err(outs[mode], want) <= 2e-2
     assert not np.array_equal(outs[GptPrefillMode.Auto], outs[GptPrefillMode.Scalar])
+
+
+def test_divided_single_token_step_matches_the_undivided_one(monkeypatch):
+    """Handles of 64 or more sessions run a single-token step as two half-batches on two streams (lean kernel forms,
+    own attention scratch per half).  Sessions are independent, so this must give what the undivided step gives up to
+    the rounding of a different softmax grouping; TNSR_B200_NO_SPLIT=1 at creation keeps a handle undivided.  An odd
+    batch makes the halves unequal; the ragged form goes through the same division."""
+    cfg = GptConfig(vocab_size=640, max_sequence_length=96, embed_dim=256, num_heads=4, feed_forward_dim=512,
+                    num_layers=3, layer_norm_epsilon=1e-5, activation="swiglu", weight_dtype="bf16")
+    arrays = normal_model_arrays(cfg, seed=43, std=0.05)
+    batch, prompt_len, steps = 71, 20, 6
+    ids = np.random.default_rng(44).integers(0, cfg.vocab_size, size=(batch, prompt_len + steps)).astype(np.uint32)
+
+    def run(no_split):
+        if no_split:
+            monkeypatch.setenv("TNSR_B200_NO_SPLIT", "1")
+        else:
+            monkeypatch.delenv("TNSR_B200_NO_SPLIT", raising=False)
+        s = B200Session(cfg, batch, 64, logits_mode="last")
+        for i, a in enumerate(arrays):
+            s.refresh(i, a)
+        s.decode_full(ids[:, :prompt_len], 0)
+        out = []
+        for t in range(steps):        # the first step is launched kernel by kernel, the others replay the captured graph
+            logits, _ = s.decode_full(ids[:, prompt_len + t:prompt_len + t + 1], prompt_len + t)
+            out.append(logits.reshape(batch, cfg.vocab_size).copy())
+        positions = np.arange(batch, dtype=np.uint32) % 7 + prompt_len + steps - 6   # rows that exist in every session
+        ragged, _ = s.decode_ragged(ids[:, 0], positions)
+        out.append(ragged.reshape(batch, cfg.vocab_size).copy())
+        caches = [s.read_cache(i) for i in (0, 2 * cfg.num_layers - 1)]
+        s.close()
+        return np.stack(out), caches
+
+    divided, caches_a = run(False)
+    whole, caches_b = run(True)
+    assert np.all(np.isfinite(divided))
+    assert rel_err(divided, whole) <= 1e-2
+    for a, b in zip(caches_a, caches_b):
+        assert np.max(np.abs(a - b)) <= max(1.0, float(np.max(np.abs(b)))) / 64
+    # the first layer's keys do not depend on attention at all: identical bits in both forms
+    assert np.array_equal(caches_a[0].view(np.uint32), caches_b[0].view(np.uint32))

@@ -114,9 +114,13 @@ int launch_attention_generic(const bf16* q, const bf16* k_cache, const bf16* v_c
 // ===========================================================================
 // Split-KV decode attention
 // ===========================================================================
-constexpr uint32_t DA_KS = 16;             // keys per ring stage
+constexpr uint32_t DA_KS = 16;             // keys per ring stage (8 in the lean form, see launch_decode_attention_ex)
 constexpr uint32_t DA_MAX_STAGES = 8;
 constexpr uint32_t DA_SMEM_BUDGET = 200 * 1024;
+// Lean form: half the shared memory, so that a CTA of another kernel (the projections of the other half of the batch)
+// fits on the same SM while this one streams K/V.
+constexpr uint32_t DA_KS_LEAN = 8;
+constexpr uint32_t DA_SMEM_BUDGET_LEAN = 106 * 1024;
 constexpr uint32_t DA_MAX_CTAS = 256;      // upper bound on the grid (one CTA per SM)
 
 // A work item: keys [key0, key0 + nkeys) of one session, all heads.  `slot` is the index of its
@@ -180,7 +184,7 @@ bool decode_attention_supported(uint32_t heads, uint32_t head_dim) {
 // Session b has lengths[b] + extra keys; lengths == nullptr means (d_position ? *d_position : 0) + extra for all.
 __global__ void __launch_bounds__(1024)
 da_plan_kernel(const uint32_t* __restrict__ lengths, const uint32_t* __restrict__ d_position, uint32_t extra,
-               uint32_t batch, uint32_t heads, uint32_t capacity, uint32_t grid, uint32_t* __restrict__ header,
+               uint32_t batch, uint32_t heads, uint32_t capacity, uint32_t grid, uint32_t ks, uint32_t* __restrict__ header,
                uint32_t* __restrict__ first, uint32_t* __restrict__ count, uint32_t* __restrict__ done,
                uint32_t* __restrict__ sstart, uint32_t* __restrict__ cta_begin, DaItem* __restrict__ items,
                int* __restrict__ d_status) {
@@ -223,7 +227,7 @@ da_plan_kernel(const uint32_t* __restrict__ lengths, const uint32_t* __restrict_
     // the merge counters must be zero when the attention kernel starts
     for (uint32_t i = tid; i < batch * heads; i += blockDim.x) done[i] = 0;
     // 1. global stage offsets of the sessions
-    const uint32_t total = scan([&](uint32_t b) { return (len_of(b) + DA_KS - 1) / DA_KS; }, sstart);
+    const uint32_t total = scan([&](uint32_t b) { return (len_of(b) + ks - 1) / ks; }, sstart);
     if (tid == 0) {
         sstart[batch] = total;
         const uint32_t ctas = total < grid ? (total ? total : 1) : grid;
@@ -235,13 +239,13 @@ da_plan_kernel(const uint32_t* __restrict__ lengths, const uint32_t* __restrict_
     const uint32_t quota = s_quota;
     // 2. pieces per session = CTAs its stage range touches; slots by exclusive scan
     auto pieces = [&](uint32_t b) -> uint32_t {
-        const uint32_t s0 = sstart[b], n = (len_of(b) + DA_KS - 1) / DA_KS;
+        const uint32_t s0 = sstart[b], n = (len_of(b) + ks - 1) / ks;
         return n ? (s0 + n - 1) / quota - s0 / quota + 1 : 0;
     };
     const uint32_t n_items = scan(pieces, first);
     // 3. items, one thread per session
     for (uint32_t b = tid; b < batch; b += blockDim.x) {
-        const uint32_t L = len_of(b), s0 = sstart[b], n = (L + DA_KS - 1) / DA_KS;
+        const uint32_t L = len_of(b), s0 = sstart[b], n = (L + ks - 1) / ks;
         const uint32_t c = pieces(b), f = first[b];
         count[b] = c;
         const uint32_t cta0 = s0 / quota;
@@ -249,8 +253,8 @@ da_plan_kernel(const uint32_t* __restrict__ lengths, const uint32_t* __restrict_
             const uint32_t lo = max(s0, (cta0 + j) * quota), hi = min(s0 + n, (cta0 + j + 1) * quota);
             DaItem it;
             it.session = b;
-            it.key0 = (lo - s0) * DA_KS;
-            it.nkeys = min(L, (hi - s0) * DA_KS) - it.key0;
+            it.key0 = (lo - s0) * ks;
+            it.nkeys = min(L, (hi - s0) * ks) - it.key0;
             it.slot = c == 1 ? DA_DIRECT : f + j;
             it.n_parts = c;
             it.first_slot = f;
@@ -359,14 +363,14 @@ struct DaParams {
 // HD: head width; LPK = HD / 8 lanes share one (key, head) row slice, each lane
 // owning 8 consecutive dims (one 16-byte shared-memory load); KPW = 32 / LPK keys
 // are processed side by side in a warp.  HPW: heads per consumer warp.
-template <int HD, int HPW>
+template <int HD, int HPW, int KS>
 __global__ void __launch_bounds__(576, 1)
 decode_attention_kernel(DaParams P) {
-    constexpr uint32_t LPK = HD / 8, KPW = 32 / LPK, ITERS = DA_KS / KPW;
-    static_assert(DA_KS % KPW == 0, "stage must hold whole key groups");
+    constexpr uint32_t LPK = HD / 8, KPW = 32 / LPK, ITERS = KS / KPW;
+    static_assert(KS % KPW == 0, "stage must hold whole key groups");
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t d = P.heads * HD, row_bytes = d * 2;
-    const uint32_t k_bytes = DA_KS * row_bytes;
+    const uint32_t k_bytes = KS * row_bytes;
     const uint32_t stage_bytes = 2 * k_bytes + row_bytes;  // K slab, V slab, q row
     uint8_t* ring = smem;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)P.stages * stage_bytes);
@@ -399,10 +403,10 @@ decode_attention_kernel(DaParams P) {
                 const DaItem it = nxt;
                 if (item + 1 < item_end) nxt = P.items[item + 1];
                 const size_t base = ((size_t)it.session * P.capacity + it.key0) * d;
-                const uint32_t n_stages = (it.nkeys + DA_KS - 1) / DA_KS;
+                const uint32_t n_stages = (it.nkeys + KS - 1) / KS;
                 for (uint32_t s = 0; s < n_stages; ++s) {
                     if (!da_mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, P.wait_limit_ns)) { ok = false; break; }
-                    const uint32_t nk = min(DA_KS, it.nkeys - s * DA_KS);
+                    const uint32_t nk = min((uint32_t)KS, it.nkeys - s * KS);
                     uint8_t* sk = ring + (size_t)stage * stage_bytes;
                     DaStageMeta mt;
                     mt.slot = it.slot;
@@ -414,8 +418,8 @@ decode_attention_kernel(DaParams P) {
                     meta[stage] = mt;
                     const uint32_t bytes = nk * row_bytes;
                     da_mbar_expect_tx(full_bar + stage, 2 * bytes + (s == 0 ? row_bytes : 0));
-                    da_bulk_load(sk, P.kc + base + (size_t)s * DA_KS * d, bytes, full_bar + stage);
-                    da_bulk_load(sk + k_bytes, P.vc + base + (size_t)s * DA_KS * d, bytes, full_bar + stage);
+                    da_bulk_load(sk, P.kc + base + (size_t)s * KS * d, bytes, full_bar + stage);
+                    da_bulk_load(sk + k_bytes, P.vc + base + (size_t)s * KS * d, bytes, full_bar + stage);
                     if (s == 0) da_bulk_load(sk + 2 * k_bytes, P.q + (size_t)it.session * d, row_bytes, full_bar + stage);
                     if (++stage == P.stages) { stage = 0; phase ^= 1; }
                 }
@@ -599,13 +603,13 @@ decode_attention_kernel(DaParams P) {
     }
 }
 
-template <int HD, int HPW>
+template <int HD, int HPW, int KS>
 static int launch_da_t(const DaParams& P, uint32_t threads, size_t smem, uint32_t grid, cudaStream_t stream) {
     static size_t configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || configured[dev] < smem) {
-        if (cudaFuncSetAttribute(decode_attention_kernel<HD, HPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(decode_attention_kernel<HD, HPW, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return check_launch("decode_attention attribute");
         if (dev >= 0 && dev < 64) configured[dev] = smem;
     }
@@ -624,7 +628,7 @@ static int launch_da_t(const DaParams& P, uint32_t threads, size_t smem, uint32_
         timer->used += 2;
         cudaEventRecord(start, stream);
     }
-    launch_kernel(decode_attention_kernel<HD, HPW>, dim3(grid), dim3(threads), smem, stream, P);
+    launch_kernel(decode_attention_kernel<HD, HPW, KS>, dim3(grid), dim3(threads), smem, stream, P);
     if (timer) cudaEventRecord(stop, stream);
     count_launch();
     return check_launch("decode_attention");
@@ -645,7 +649,7 @@ static int da_sm_count() {
 int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v_cache, const uint32_t* d_lengths,
                                const uint32_t* d_position, uint32_t extra, bf16* out, void* workspace,
                                uint64_t workspace_bytes, uint32_t batch, uint32_t capacity, uint32_t heads,
-                               uint32_t head_dim, bool plan, int* d_status, cudaStream_t stream) {
+                               uint32_t head_dim, bool plan, int* d_status, cudaStream_t stream, bool lean) {
     if (batch == 0) return TNSR_B200_OK;
     if (!decode_attention_supported(heads, head_dim)) {
         set_thread_error("decode attention: head_dim must be 32, 64 or 128 and heads <= 32");
@@ -672,6 +676,10 @@ int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v
     float* partial = reinterpret_cast<float*>(ws + L.partial);
     uint32_t grid = (uint32_t)da_sm_count();
     if (grid > DA_MAX_CTAS) grid = DA_MAX_CTAS;
+    // keys per ring stage: 8 in the lean form if two such stages (the least a ring needs) fit its budget
+    const uint32_t d = heads * head_dim, row_bytes = d * 2;
+    if (lean && 2 * (2 * DA_KS_LEAN * row_bytes + row_bytes) > DA_SMEM_BUDGET_LEAN) lean = false;
+    const uint32_t ks = lean ? DA_KS_LEAN : DA_KS;
     if (!d_lengths) {
         // Every session has the same length (the decoder's own steps).  If the grid divides the batch, or the batch
         // divides the grid, the equal key ranges of the CTAs line up with the sessions: whole sessions per CTA (no
@@ -690,14 +698,13 @@ int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v
     }
     if (plan) {
         launch_kernel(da_plan_kernel, dim3(1), dim3(1024), 0, stream, d_lengths, d_position, extra, batch, heads, capacity, grid,
-                      header, first, count, done, sstart, cta_begin, items, d_status);
+                      ks, header, first, count, done, sstart, cta_begin, items, d_status);
         count_launch();
         int rc = check_launch("decode_attention plan");
         if (rc) return rc;
     }
-    const uint32_t d = heads * head_dim, row_bytes = d * 2;
-    const uint32_t stage_bytes = 2 * DA_KS * row_bytes + row_bytes;
-    uint32_t stages = DA_SMEM_BUDGET / stage_bytes;
+    const uint32_t stage_bytes = 2 * ks * row_bytes + row_bytes;
+    uint32_t stages = (lean ? DA_SMEM_BUDGET_LEAN : DA_SMEM_BUDGET) / stage_bytes;
     if (stages > DA_MAX_STAGES) stages = DA_MAX_STAGES;
     const size_t smem = (size_t)stages * stage_bytes + 2 * DA_MAX_STAGES * 8 + DA_MAX_STAGES * sizeof(DaStageMeta) + 16;
     const uint32_t hpw = heads > 16 ? 2 : 1;
@@ -711,14 +718,24 @@ int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v
     P.d_status = d_status;
     P.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
     const uint32_t threads = (consumers + 1) * 32;
-    if (hpw == 1) {
-        return head_dim == 32 ? launch_da_t<32, 1>(P, threads, smem, grid, stream)
-             : head_dim == 64 ? launch_da_t<64, 1>(P, threads, smem, grid, stream)
-                              : launch_da_t<128, 1>(P, threads, smem, grid, stream);
+    if (lean) {
+        if (hpw == 1) {
+            return head_dim == 32 ? launch_da_t<32, 1, DA_KS_LEAN>(P, threads, smem, grid, stream)
+                 : head_dim == 64 ? launch_da_t<64, 1, DA_KS_LEAN>(P, threads, smem, grid, stream)
+                                  : launch_da_t<128, 1, DA_KS_LEAN>(P, threads, smem, grid, stream);
+        }
+        return head_dim == 32 ? launch_da_t<32, 2, DA_KS_LEAN>(P, threads, smem, grid, stream)
+             : head_dim == 64 ? launch_da_t<64, 2, DA_KS_LEAN>(P, threads, smem, grid, stream)
+                              : launch_da_t<128, 2, DA_KS_LEAN>(P, threads, smem, grid, stream);
     }
-    return head_dim == 32 ? launch_da_t<32, 2>(P, threads, smem, grid, stream)
-         : head_dim == 64 ? launch_da_t<64, 2>(P, threads, smem, grid, stream)
-                          : launch_da_t<128, 2>(P, threads, smem, grid, stream);
+    if (hpw == 1) {
+        return head_dim == 32 ? launch_da_t<32, 1, DA_KS>(P, threads, smem, grid, stream)
+             : head_dim == 64 ? launch_da_t<64, 1, DA_KS>(P, threads, smem, grid, stream)
+                              : launch_da_t<128, 1, DA_KS>(P, threads, smem, grid, stream);
+    }
+    return head_dim == 32 ? launch_da_t<32, 2, DA_KS>(P, threads, smem, grid, stream)
+         : head_dim == 64 ? launch_da_t<64, 2, DA_KS>(P, threads, smem, grid, stream)
+                          : launch_da_t<128, 2, DA_KS>(P, threads, smem, grid, stream);
 }
 
 int launch_decode_attention(const bf16* q, const bf16* k_cache, const bf16* v_cache, const uint32_t* d_lengths,
@@ -726,7 +743,7 @@ int launch_decode_attention(const bf16* q, const bf16* k_cache, const bf16* v_ca
                             uint32_t capacity, uint32_t heads, uint32_t head_dim, int* d_status,
                             cudaStream_t stream) {
     return launch_decode_attention_ex(q, k_cache, v_cache, d_lengths, nullptr, 0, out, workspace, workspace_bytes, batch,
-                                      capacity, heads, head_dim, true, d_status, stream);
+                                      capacity, heads, head_dim, true, d_status, stream, false);
 }
 
 }  // namespace tb

@@ -55,8 +55,15 @@ extern thread_local KernelTimer* t_attention_timer;
 // predecessor has completed and its writes are visible, so only launch latency overlaps, never data.
 extern thread_local bool t_pdl;
 
+// Asks (once per kernel and device) for the largest shared-memory carve-out whenever `kernel` runs.  The split between
+// L1 and shared memory is a per-SM setting that can only change while the SM is empty, so two kernels can share an SM
+// only if they agree on it; with every kernel of the library on the same setting, a CTA of one stream's kernel can
+// move in beside a CTA of another stream's kernel as soon as threads, registers and shared memory allow.
+void prefer_max_shared_carveout(const void* kernel);
+
 template <typename... KArgs, typename... Args>
 inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    prefer_max_shared_carveout(reinterpret_cast<const void*>(kernel));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -170,7 +177,7 @@ int launch_swiglu_strict(const float* gate, const float* up, float* out, size_t 
 int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v_cache, const uint32_t* d_lengths,
                                const uint32_t* d_position, uint32_t extra, bf16* out, void* workspace,
                                uint64_t workspace_bytes, uint32_t batch, uint32_t capacity, uint32_t heads,
-                               uint32_t head_dim, bool plan, int* d_status, cudaStream_t stream);
+                               uint32_t head_dim, bool plan, int* d_status, cudaStream_t stream, bool lean = false);
 int launch_pack_gate_up(const bf16* wg, const bf16* wu, const float* bg, const float* bu, bf16* w_out,
                         float* b_out, uint32_t d, uint32_t f, cudaStream_t stream);
 int launch_fill_u32(uint32_t* p, uint32_t value, uint32_t n, cudaStream_t stream);

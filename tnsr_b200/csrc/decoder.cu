@@ -6,6 +6,8 @@
 // cache to evict.
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
+#include <unordered_set>
 #include <vector>
 
 #include "common.cuh"
@@ -16,6 +18,17 @@ std::atomic<uint64_t> g_wait_limit_ns{2000000000ull};
 static thread_local std::string t_error;
 void set_thread_error(const std::string& msg) { t_error = msg; }
 const char* thread_error() { return t_error.c_str(); }
+void prefer_max_shared_carveout(const void* kernel) {
+    static std::mutex lock;
+    static std::unordered_set<uint64_t> done;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const uint64_t key = (uint64_t)reinterpret_cast<uintptr_t>(kernel) ^ ((uint64_t)(uint32_t)dev << 56);
+    std::lock_guard<std::mutex> guard(lock);
+    if (!done.insert(key).second) return;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
+        cudaGetLastError();   // a hint only: the launch itself does not depend on it
+}
 bool debug_sync_enabled() {
     static const bool on = [] {
         const char* v = std::getenv("TNSR_B200_DEBUG_SYNC");
@@ -88,7 +101,11 @@ struct tnsr_b200_decoder {
     uint32_t* d_argmax = nullptr;
     int* d_status = nullptr;
     void* attn_ws = nullptr;
+    void* attn_ws2 = nullptr;          // scratch of the second half-batch when a step is divided over two streams
     uint64_t attn_ws_bytes = 0;
+    cudaStream_t stream2 = nullptr;    // the second half-batch's stream; forked from and joined to `stream` by events
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    bool split_step = true;
     uint32_t* d_positions = nullptr;   // [batch] per-session positions of a ragged step
     uint32_t* h_positions = nullptr;   // pinned staging for them
     // pinned staging
@@ -368,52 +385,60 @@ int step_strict(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk
 }
 
 // ---- one step on the bf16 tensor-core path -----------------------------------
+// The part of a step that belongs to a range of sessions [s0, s0 + ns): embedding and all layers, on stream `st`.
+// Nothing in it couples two sessions, so disjoint ranges may run on different streams at the same time.
 // `d_position` (optional): the position as a device scalar, so that a captured graph of the step can be replayed
-// while the position advances.  `fused_ids` (optional): greedy ids come straight out of the LM-head GEMM and no
-// logits are written (only when the logits mode is NONE).
-// `ragged`: d_position is an array with one position per session (single-token steps only).
-int step_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, uint32_t position,
-              const uint32_t* d_position, uint32_t logit_rows, uint32_t* fused_ids, bool ragged = false) {
+// while the position advances.  `ragged`: d_position is an array with one position per session (single-token steps).
+// `ws`: decode-attention scratch of this range.  `lean`: take the decode-attention form that leaves room on every SM
+// for the other range's projection kernels.
+int layers_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, uint32_t position,
+                const uint32_t* d_position, bool ragged, uint32_t s0, uint32_t ns, void* ws, bool lean, cudaStream_t st) {
     const tnsr_b200_config& c = dec->cfg;
-    const uint32_t d = c.embed_dim, f = c.feed_forward_dim, H = c.num_heads, hd = d / H, B = c.batch, rows = B * chunk;
-    cudaStream_t st = dec->stream;
-    bf16* n = (bf16*)dec->n; bf16* q = (bf16*)dec->q; bf16* att = (bf16*)dec->att; bf16* ff = (bf16*)dec->ff;
-    RUN(dec, launch_embedding(dec->tok, dec->pos, d_tokens, dec->h, rows, chunk, position, d_position, c.vocab_size, d,
+    const uint32_t d = c.embed_dim, f = c.feed_forward_dim, H = c.num_heads, hd = d / H;
+    const uint32_t rows = ns * chunk;
+    const size_t r0 = (size_t)s0 * chunk;                       // first activation row of the range
+    const size_t cache0 = (size_t)s0 * c.capacity * d;          // first cache element of the range
+    float* h = dec->h + r0 * d;
+    bf16* n = (bf16*)dec->n + r0 * d; bf16* q = (bf16*)dec->q + r0 * d; bf16* att = (bf16*)dec->att + r0 * d;
+    bf16* ff = (bf16*)dec->ff + r0 * f;
+    bf16* ff2 = dec->ff2 ? (bf16*)dec->ff2 + r0 * f : nullptr;
+    const uint32_t* pos_arg = ragged ? d_position + s0 : d_position;
+    RUN(dec, launch_embedding(dec->tok, dec->pos, d_tokens + r0, h, rows, chunk, position, pos_arg, c.vocab_size, d,
                               TNSR_B200_BF16, dec->d_status, st, ragged ? 1u : 0u));
-    const bool fast_decode = chunk == 1 && dec->attn_ws && decode_attention_supported(H, hd);
+    const bool fast_decode = chunk == 1 && ws && decode_attention_supported(H, hd);
     if (ragged && !fast_decode) return fail(dec, TNSR_B200_ERR_UNSUPPORTED, "ragged decode needs the split-KV attention kernel (head width 32, 64 or 128)");
     bool planned = false;
     for (Layer& L : dec->layers) {
-        RUN(dec, launch_layernorm(dec->h, L.ln1w, L.ln1b, n, rows, d, c.layer_norm_epsilon, TNSR_B200_BF16, false, st));
+        bf16* kcache = (bf16*)L.kcache + cache0;
+        bf16* vcache = (bf16*)L.vcache + cache0;
+        RUN(dec, launch_layernorm(h, L.ln1w, L.ln1b, n, rows, d, c.layer_norm_epsilon, TNSR_B200_BF16, false, st));
         GemmEpilogue eq;
         eq.bias = L.bqkv;
         GemmQkvTargets tg;
-        tg.q = q; tg.k_cache = (bf16*)L.kcache; tg.v_cache = (bf16*)L.vcache;
-        tg.d = d; tg.chunk = chunk; tg.capacity = c.capacity; tg.position = position; tg.d_position = d_position;
+        tg.q = q; tg.k_cache = kcache; tg.v_cache = vcache;
+        tg.d = d; tg.chunk = chunk; tg.capacity = c.capacity; tg.position = position; tg.d_position = pos_arg;
         tg.position_stride = ragged ? 1u : 0u;
         RUN(dec, launch_gemm_bf16(n, L.wqkv, nullptr, 0, rows, 3 * d, d, GEMM_QKV, eq, &tg, dec->d_status, st));
         if (fast_decode) {
             // every session holds position + 1 keys; the item list is the same for all layers of this step
             if (ragged)   // session b holds d_position[b] + 1 keys
-                RUN(dec, launch_decode_attention_ex(q, (const bf16*)L.kcache, (const bf16*)L.vcache, d_position, nullptr, 1, att,
-                                                    dec->attn_ws, dec->attn_ws_bytes, B, c.capacity, H, hd, !planned,
-                                                    dec->d_status, st));
+                RUN(dec, launch_decode_attention_ex(q, kcache, vcache, pos_arg, nullptr, 1, att, ws, dec->attn_ws_bytes, ns,
+                                                    c.capacity, H, hd, !planned, dec->d_status, st, lean));
             else
-            RUN(dec, launch_decode_attention_ex(q, (const bf16*)L.kcache, (const bf16*)L.vcache, nullptr, d_position,
-                                                d_position ? 1 : position + 1, att, dec->attn_ws, dec->attn_ws_bytes, B,
-                                                c.capacity, H, hd, !planned, dec->d_status, st));
+                RUN(dec, launch_decode_attention_ex(q, kcache, vcache, nullptr, d_position, d_position ? 1 : position + 1, att,
+                                                    ws, dec->attn_ws_bytes, ns, c.capacity, H, hd, !planned, dec->d_status,
+                                                    st, lean));
             planned = true;
         } else if (chunk > 1 && prefill_attention_supported(hd) && c.prefill_mode != TNSR_B200_PREFILL_SCALAR) {
-            RUN(dec, launch_prefill_attention(q, (const bf16*)L.kcache, (const bf16*)L.vcache, att, B, chunk, position, d_position,
-                                              c.capacity, H, hd, dec->d_status, st));
+            RUN(dec, launch_prefill_attention(q, kcache, vcache, att, ns, chunk, position, d_position, c.capacity, H, hd,
+                                              dec->d_status, st));
         } else {
-            RUN(dec, launch_attention_generic(q, (const bf16*)L.kcache, (const bf16*)L.vcache, att, B, chunk, position, d_position,
-                                              c.capacity, H, hd, st));
+            RUN(dec, launch_attention_generic(q, kcache, vcache, att, ns, chunk, position, d_position, c.capacity, H, hd, st));
         }
         GemmEpilogue eo;
-        eo.bias = L.bo; eo.residual = dec->h; eo.ldr = d; eo.out_dtype = TNSR_B200_F32;
-        RUN(dec, launch_gemm_bf16(att, (const bf16*)L.wo, dec->h, d, rows, d, d, GEMM_PLAIN, eo, nullptr, dec->d_status, st));
-        RUN(dec, launch_layernorm(dec->h, L.ln2w, L.ln2b, n, rows, d, c.layer_norm_epsilon, TNSR_B200_BF16, false, st));
+        eo.bias = L.bo; eo.residual = h; eo.ldr = d; eo.out_dtype = TNSR_B200_F32;
+        RUN(dec, launch_gemm_bf16(att, (const bf16*)L.wo, h, d, rows, d, d, GEMM_PLAIN, eo, nullptr, dec->d_status, st));
+        RUN(dec, launch_layernorm(h, L.ln2w, L.ln2b, n, rows, d, c.layer_norm_epsilon, TNSR_B200_BF16, false, st));
         if (dec->swiglu) {
             if (dec->fused_gu) {
                 GemmEpilogue eg; eg.bias = L.bgu; eg.out_dtype = TNSR_B200_BF16;
@@ -422,17 +447,56 @@ int step_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, 
                 GemmEpilogue eg; eg.bias = L.b_gate; eg.out_dtype = TNSR_B200_BF16;
                 RUN(dec, launch_gemm_bf16(n, (const bf16*)L.w_gate, ff, f, rows, f, d, GEMM_PLAIN, eg, nullptr, dec->d_status, st));
                 GemmEpilogue eu; eu.bias = L.b_up; eu.out_dtype = TNSR_B200_BF16;
-                RUN(dec, launch_gemm_bf16(n, (const bf16*)L.w_up, dec->ff2, f, rows, f, d, GEMM_PLAIN, eu, nullptr, dec->d_status, st));
-                RUN(dec, launch_swiglu(ff, (const bf16*)dec->ff2, ff, (uint64_t)rows * f, st));
+                RUN(dec, launch_gemm_bf16(n, (const bf16*)L.w_up, ff2, f, rows, f, d, GEMM_PLAIN, eu, nullptr, dec->d_status, st));
+                RUN(dec, launch_swiglu(ff, ff2, ff, (uint64_t)rows * f, st));
             }
         } else {
             GemmEpilogue ei; ei.bias = L.b_in; ei.out_dtype = TNSR_B200_BF16;
             ei.activation = c.activation == TNSR_B200_ACT_GELU ? ACT_GELU : ACT_RELU;
             RUN(dec, launch_gemm_bf16(n, (const bf16*)L.w_in, ff, f, rows, f, d, GEMM_PLAIN, ei, nullptr, dec->d_status, st));
         }
-        GemmEpilogue ef; ef.bias = L.b_out; ef.residual = dec->h; ef.ldr = d; ef.out_dtype = TNSR_B200_F32;
-        RUN(dec, launch_gemm_bf16(ff, (const bf16*)L.w_out, dec->h, d, rows, d, f, GEMM_PLAIN, ef, nullptr, dec->d_status, st));
+        GemmEpilogue ef; ef.bias = L.b_out; ef.residual = h; ef.ldr = d; ef.out_dtype = TNSR_B200_F32;
+        RUN(dec, launch_gemm_bf16(ff, (const bf16*)L.w_out, h, d, rows, d, f, GEMM_PLAIN, ef, nullptr, dec->d_status, st));
     }
+    return TNSR_B200_OK;
+}
+
+// Smallest batch whose single-token step is divided over two streams (see step_bf16).
+constexpr uint32_t kSplitMinSessions = 64;
+
+// One whole step.  `fused_ids` (optional): greedy ids come straight out of the LM-head GEMM and no logits are written
+// (only when the logits mode is NONE).
+//
+// Single-token steps of at least kSplitMinSessions sessions run as two half-batches on two streams.  Inside one half
+// the step is a chain of short, latency-bound kernels (LayerNorm, the four projections) around one long,
+// bandwidth-bound kernel per layer (decode attention); sessions are independent, so while one half streams its K/V
+// rows the other half's short kernels run beside it on the same SMs (the lean kernel forms leave room for that) and
+// their latency is hidden instead of added.  The halves fork after the ids are in place and join before the final
+// LayerNorm and the LM head, which read the token table once for the whole batch.
+int step_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, uint32_t position,
+              const uint32_t* d_position, uint32_t logit_rows, uint32_t* fused_ids, bool ragged = false) {
+    const tnsr_b200_config& c = dec->cfg;
+    const uint32_t d = c.embed_dim, H = c.num_heads, hd = d / H, B = c.batch, rows = B * chunk;
+    cudaStream_t st = dec->stream;
+    const bool split = chunk == 1 && B >= kSplitMinSessions && dec->split_step && dec->attn_ws2 && dec->stream2 &&
+                       !dec->profile_attention && decode_attention_supported(H, hd) && !debug_sync_enabled();
+    if (split) {
+        const uint32_t first_half = (B + 1) / 2;
+        CU(dec, cudaEventRecord(dec->ev_fork, st));
+        CU(dec, cudaStreamWaitEvent(dec->stream2, dec->ev_fork, 0));
+        int rc = layers_bf16(dec, d_tokens, chunk, position, d_position, ragged, first_half, B - first_half, dec->attn_ws2, true,
+                             dec->stream2);
+        cudaError_t e = cudaEventRecord(dec->ev_join, dec->stream2);   // the fork is always joined, also on failure
+        int rc1 = layers_bf16(dec, d_tokens, chunk, position, d_position, ragged, 0, first_half, dec->attn_ws, true, st);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(st, dec->ev_join, 0);
+        if (rc) return rc;
+        if (rc1) return rc1;
+        if (e != cudaSuccess) return cuda_fail(dec, e, "joining the two halves of the step");
+    } else {
+        int rc = layers_bf16(dec, d_tokens, chunk, position, d_position, ragged, 0, B, dec->attn_ws, false, st);
+        if (rc) return rc;
+    }
+    bf16* n = (bf16*)dec->n;
     const float* src = dec->h;
     if (logit_rows != rows) {
         RUN(dec, launch_gather_last_rows(dec->h, dec->hl, B, chunk, d, st));
@@ -648,6 +712,8 @@ int tnsr_b200_decoder_create(const tnsr_b200_config* config, tnsr_b200_decoder**
         if (v && v[0] == '1') dec->use_graphs = false;
         v = std::getenv("TNSR_B200_NO_PDL");
         if (v && v[0] == '1') dec->use_pdl = false;
+        v = std::getenv("TNSR_B200_NO_SPLIT");
+        if (v && v[0] == '1') dec->split_step = false;
     }
     if (cudaMallocHost((void**)&dec->h_argmax, (size_t)config->batch * 4) != cudaSuccess ||
         cudaMallocHost((void**)&dec->h_status, 16) != cudaSuccess)
@@ -657,6 +723,13 @@ int tnsr_b200_decoder_create(const tnsr_b200_config* config, tnsr_b200_decoder**
         dec->attn_ws_bytes = decode_attention_workspace_bytes(config->batch, config->capacity, config->num_heads,
                                                               config->embed_dim / config->num_heads);
         if ((rc = dev_alloc(dec, &dec->attn_ws, dec->attn_ws_bytes, true))) return bail(rc);
+        if (config->batch >= kSplitMinSessions) {
+            if ((rc = dev_alloc(dec, &dec->attn_ws2, dec->attn_ws_bytes, true))) return bail(rc);
+            if (cudaStreamCreateWithFlags(&dec->stream2, cudaStreamNonBlocking) != cudaSuccess ||
+                cudaEventCreateWithFlags(&dec->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&dec->ev_join, cudaEventDisableTiming) != cudaSuccess)
+                return bail(cuda_fail(dec, cudaGetLastError(), "second stream of the divided step"));
+        }
     }
     if (dec->bf16_path) {
         dec->host_bqkv.assign((size_t)config->num_layers * 3 * d, 0.0f);
@@ -679,6 +752,9 @@ void tnsr_b200_decoder_destroy(tnsr_b200_decoder* dec) {
     if (dec->h_status) cudaFreeHost(dec->h_status);
     if (dec->h_stage) cudaFreeHost(dec->h_stage);
     drop_graphs(dec);
+    if (dec->stream2) { cudaStreamSynchronize(dec->stream2); cudaStreamDestroy(dec->stream2); }
+    if (dec->ev_fork) cudaEventDestroy(dec->ev_fork);
+    if (dec->ev_join) cudaEventDestroy(dec->ev_join);
     for (cudaEvent_t e : dec->attention_timer.events) cudaEventDestroy(e);
     if (dec->stream) cudaStreamDestroy(dec->stream);
     cudaGetLastError();

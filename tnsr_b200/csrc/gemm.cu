@@ -189,8 +189,11 @@ constexpr uint32_t TC_STAGE_TILE_BYTES = 32 * 32 * 4;  // per-warp transpose buf
 template <int BN, int EPI>
 struct TcShape {
     static constexpr int THREADS = 64 + 32 * EPI;
-    // 4 stages of 48 KB at BN 256 with 8 epilogue warps; 3 with 16 (their transpose buffers take 64 KB)
-    static constexpr int STAGES = BN >= 256 ? (EPI > 8 ? 3 : 4) : (BN >= 128 ? 6 : 8);
+    // 4 stages of 48 KB at BN 256 with 8 epilogue warps; 3 with 16 (their transpose buffers take 64 KB).
+    // EPI 4 is the lean form of the narrow tiles (few rows, one tile per CTA: the decode step): half the shared memory
+    // (about 115 KB) and at most 112 registers x 192 threads, so that a CTA of it fits on an SM beside a CTA of the lean
+    // decode-attention kernel that works on the other half of the batch.
+    static constexpr int STAGES = BN >= 256 ? (EPI > 8 ? 3 : 4) : (BN >= 128 ? 6 : (EPI == 4 ? (BN >= 64 ? 4 : 5) : 8));
     static constexpr uint32_t A_BYTES = BM * BK * 2;
     static constexpr uint32_t B_BYTES = BN * BK * 2;
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -515,7 +518,7 @@ __device__ __forceinline__ void epilogue_block(const EpiParams& P, float* stage,
 }
 
 template <int BN, int MODE, int EPI>
-__global__ void __launch_bounds__(64 + 32 * EPI, 1)
+__global__ void __launch_bounds__(64 + 32 * EPI, EPI == 4 ? 3 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, TcParams prm) {
@@ -749,6 +752,8 @@ template <int BN, int MODE>
 static int launch_tc_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap* mo, const TcParams& prm, cudaStream_t stream) {
     if (BN == 256 && (MODE == GEMM_QKV || MODE == GEMM_SWIGLU) && prm.k <= 1024)
         return launch_tc_e<BN, MODE, (BN == 256 && (MODE == GEMM_QKV || MODE == GEMM_SWIGLU)) ? 16 : 8>(ma, mb, mo, prm, stream);
+    // narrow tiles: one epilogue warp per TMEM lane quarter is all a 32- or 64-column tile can use
+    if (BN <= 64 && MODE != GEMM_ARGMAX) return launch_tc_e<BN, MODE, BN <= 64 ? 4 : 8>(ma, mb, mo, prm, stream);
     return launch_tc_e<BN, MODE, 8>(ma, mb, mo, prm, stream);
 }
 
