@@ -107,6 +107,13 @@ typedef struct tnsr_b200_config {
     int32_t device;        /* CUDA ordinal (the reference always uses 0)           */
     uint32_t logits_mode;  /* tnsr_b200_logits_mode */
     uint32_t prefill_mode; /* tnsr_b200_prefill_mode */
+    /* How many independent session ranges a single-token step of the bf16 path
+     * is divided into, each on its own stream so that one range's short
+     * projection kernels run while another range streams its K/V rows (no
+     * reference counterpart; results differ from the undivided step only by
+     * rounding).  0 = automatic (2 from 192 sessions up, else 1), 1 = never
+     * divide, 2..4 = that many parts. */
+    uint32_t step_parts;
 } tnsr_b200_config;
 
 typedef struct tnsr_b200_decoder tnsr_b200_decoder;

@@ -511,23 +511,20 @@ def test_prefill_mode_scalar_keeps_multi_token_chunks_off_the_tiled_kernels():
     assert not np.array_equal(outs[GptPrefillMode.Auto], outs[GptPrefillMode.Scalar])
 
 
-def test_divided_single_token_step_matches_the_undivided_one(monkeypatch):
-    """Handles of 64 or more sessions run a single-token step as two half-batches on two streams (lean kernel forms,
-    own attention scratch per half).  Sessions are independent, so this must give what the undivided step gives up to
-    the rounding of a different softmax grouping; TNSR_B200_NO_SPLIT=1 at creation keeps a handle undivided.  An odd
-    batch makes the halves unequal; the ragged form goes through the same division."""
+@pytest.mark.parametrize("parts", [2, 3])
+def test_divided_single_token_step_matches_the_undivided_one(parts):
+    """Large handles (or `step_parts` in the configuration) run a single-token step as independent session ranges on
+    separate streams (lean kernel forms, own attention scratch per range).  Sessions are independent, so this must
+    give what the undivided step gives up to the rounding of a different softmax grouping.  An odd batch makes the
+    ranges unequal; the ragged form goes through the same division."""
     cfg = GptConfig(vocab_size=640, max_sequence_length=96, embed_dim=256, num_heads=4, feed_forward_dim=512,
                     num_layers=3, layer_norm_epsilon=1e-5, activation="swiglu", weight_dtype="bf16")
     arrays = normal_model_arrays(cfg, seed=43, std=0.05)
     batch, prompt_len, steps = 71, 20, 6
     ids = np.random.default_rng(44).integers(0, cfg.vocab_size, size=(batch, prompt_len + steps)).astype(np.uint32)
 
-    def run(no_split):
-        if no_split:
-            monkeypatch.setenv("TNSR_B200_NO_SPLIT", "1")
-        else:
-            monkeypatch.delenv("TNSR_B200_NO_SPLIT", raising=False)
-        s = B200Session(cfg, batch, 64, logits_mode="last")
+    def run(step_parts):
+        s = B200Session(cfg, batch, 64, logits_mode="last", step_parts=step_parts)
         for i, a in enumerate(arrays):
             s.refresh(i, a)
         s.decode_full(ids[:, :prompt_len], 0)
@@ -542,8 +539,8 @@ def test_divided_single_token_step_matches_the_undivided_one(monkeypatch):
         s.close()
         return np.stack(out), caches
 
-    divided, caches_a = run(False)
-    whole, caches_b = run(True)
+    divided, caches_a = run(parts)
+    whole, caches_b = run(1)
     assert np.all(np.isfinite(divided))
     assert rel_err(divided, whole) <= 1e-2
     for a, b in zip(caches_a, caches_b):

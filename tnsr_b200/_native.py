@@ -29,7 +29,7 @@ class Config(C.Structure):
         ("num_heads", C.c_uint32), ("feed_forward_dim", C.c_uint32), ("num_layers", C.c_uint32),
         ("layer_norm_epsilon", C.c_float), ("activation", C.c_uint32), ("weight_dtype", C.c_uint32),
         ("kv_dtype", C.c_uint32), ("batch", C.c_uint32), ("capacity", C.c_uint32), ("device", C.c_int32),
-        ("logits_mode", C.c_uint32), ("prefill_mode", C.c_uint32),
+        ("logits_mode", C.c_uint32), ("prefill_mode", C.c_uint32), ("step_parts", C.c_uint32),
     ]
 
 

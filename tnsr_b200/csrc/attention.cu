@@ -332,6 +332,14 @@ __device__ __forceinline__ void da_bulk_load(void* dst, const void* src, uint32_
                  : "memory");
 }
 
+// The same copy for data that is read exactly once (K/V rows): evict-first in L2, so that a long scan does not push out
+// what other kernels keep there.
+__device__ __forceinline__ void da_bulk_load_once(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(da_smem_u32(dst)), "l"(src), "r"(bytes), "r"(da_smem_u32(bar)), "l"(policy)
+                 : "memory");
+}
+
 struct DaStageMeta {
     uint32_t slot;        // partial slot of the item, or DA_DIRECT
     uint32_t nk;          // valid keys in this stage (1..DA_KS)
@@ -395,6 +403,8 @@ decode_attention_kernel(DaParams P) {
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            uint64_t once;
+            asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(once));
             // item records and the per-session piece counts are fetched one item ahead, so their latency
             // hides behind the copies of the current item
             DaItem nxt = {};
@@ -418,8 +428,8 @@ decode_attention_kernel(DaParams P) {
                     meta[stage] = mt;
                     const uint32_t bytes = nk * row_bytes;
                     da_mbar_expect_tx(full_bar + stage, 2 * bytes + (s == 0 ? row_bytes : 0));
-                    da_bulk_load(sk, P.kc + base + (size_t)s * KS * d, bytes, full_bar + stage);
-                    da_bulk_load(sk + k_bytes, P.vc + base + (size_t)s * KS * d, bytes, full_bar + stage);
+                    da_bulk_load_once(sk, P.kc + base + (size_t)s * KS * d, bytes, full_bar + stage, once);
+                    da_bulk_load_once(sk + k_bytes, P.vc + base + (size_t)s * KS * d, bytes, full_bar + stage, once);
                     if (s == 0) da_bulk_load(sk + 2 * k_bytes, P.q + (size_t)it.session * d, row_bytes, full_bar + stage);
                     if (++stage == P.stages) { stage = 0; phase ^= 1; }
                 }

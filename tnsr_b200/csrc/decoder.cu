@@ -101,11 +101,13 @@ struct tnsr_b200_decoder {
     uint32_t* d_argmax = nullptr;
     int* d_status = nullptr;
     void* attn_ws = nullptr;
-    void* attn_ws2 = nullptr;          // scratch of the second half-batch when a step is divided over two streams
+    // a single-token step may be divided into up to kMaxParts session ranges on as many streams (see step_bf16):
+    // range 0 runs on `stream` with `attn_ws`, range i > 0 on side_stream[i - 1] with side_ws[i - 1]
+    void* side_ws[3] = {nullptr, nullptr, nullptr};
     uint64_t attn_ws_bytes = 0;
-    cudaStream_t stream2 = nullptr;    // the second half-batch's stream; forked from and joined to `stream` by events
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
-    bool split_step = true;
+    cudaStream_t side_stream[3] = {nullptr, nullptr, nullptr};   // forked from and joined to `stream` by events
+    cudaEvent_t ev_fork = nullptr, ev_join[3] = {nullptr, nullptr, nullptr};
+    uint32_t parts = 1;
     uint32_t* d_positions = nullptr;   // [batch] per-session positions of a ragged step
     uint32_t* h_positions = nullptr;   // pinned staging for them
     // pinned staging
@@ -461,13 +463,17 @@ int layers_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk
     return TNSR_B200_OK;
 }
 
-// Smallest batch whose single-token step is divided over two streams (see step_bf16).
-constexpr uint32_t kSplitMinSessions = 64;
+// Smallest batch whose single-token step is divided over two streams unless the configuration says otherwise (see
+// step_bf16).  Measured on B200 with the 12-layer d768 model: 256 sessions 1.35 ms per step divided in two against
+// 1.48 ms undivided (three parts 1.46, four 1.53); at 128 sessions 1.02 against 1.01 and at 64 sessions 0.88 against
+// 0.83, because a half batch no longer keeps every SM streaming during its attention.
+constexpr uint32_t kSplitMinSessions = 192;
 
 // One whole step.  `fused_ids` (optional): greedy ids come straight out of the LM-head GEMM and no logits are written
 // (only when the logits mode is NONE).
 //
-// Single-token steps of at least kSplitMinSessions sessions run as two half-batches on two streams.  Inside one half
+// Single-token steps of at least kSplitMinSessions sessions (or as many parts as the configuration's step_parts asks
+// for) run as two half-batches on two streams.  Inside one half
 // the step is a chain of short, latency-bound kernels (LayerNorm, the four projections) around one long,
 // bandwidth-bound kernel per layer (decode attention); sessions are independent, so while one half streams its K/V
 // rows the other half's short kernels run beside it on the same SMs (the lean kernel forms leave room for that) and
@@ -478,20 +484,31 @@ int step_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, 
     const tnsr_b200_config& c = dec->cfg;
     const uint32_t d = c.embed_dim, H = c.num_heads, hd = d / H, B = c.batch, rows = B * chunk;
     cudaStream_t st = dec->stream;
-    const bool split = chunk == 1 && B >= kSplitMinSessions && dec->split_step && dec->attn_ws2 && dec->stream2 &&
-                       !dec->profile_attention && decode_attention_supported(H, hd) && !debug_sync_enabled();
+    const bool split = chunk == 1 && dec->parts > 1 && !dec->profile_attention && decode_attention_supported(H, hd) &&
+                       !debug_sync_enabled();
     if (split) {
-        const uint32_t first_half = (B + 1) / 2;
+        const uint32_t parts = dec->parts;
         CU(dec, cudaEventRecord(dec->ev_fork, st));
-        CU(dec, cudaStreamWaitEvent(dec->stream2, dec->ev_fork, 0));
-        int rc = layers_bf16(dec, d_tokens, chunk, position, d_position, ragged, first_half, B - first_half, dec->attn_ws2, true,
-                             dec->stream2);
-        cudaError_t e = cudaEventRecord(dec->ev_join, dec->stream2);   // the fork is always joined, also on failure
-        int rc1 = layers_bf16(dec, d_tokens, chunk, position, d_position, ragged, 0, first_half, dec->attn_ws, true, st);
-        if (e == cudaSuccess) e = cudaStreamWaitEvent(st, dec->ev_join, 0);
+        int rc = TNSR_B200_OK;
+        cudaError_t e = cudaSuccess;
+        for (uint32_t p = 1; p < parts; ++p) {
+            const uint32_t s0 = (uint32_t)((uint64_t)B * p / parts), s1 = (uint32_t)((uint64_t)B * (p + 1) / parts);
+            cudaStream_t side = dec->side_stream[p - 1];
+            CU(dec, cudaStreamWaitEvent(side, dec->ev_fork, 0));
+            int r = layers_bf16(dec, d_tokens, chunk, position, d_position, ragged, s0, s1 - s0, dec->side_ws[p - 1], true, side);
+            cudaError_t er = cudaEventRecord(dec->ev_join[p - 1], side);   // every fork is joined, also after a failure
+            if (r && !rc) rc = r;
+            if (er != cudaSuccess && e == cudaSuccess) e = er;
+        }
+        int r0 = layers_bf16(dec, d_tokens, chunk, position, d_position, ragged, 0, (uint32_t)((uint64_t)B / parts), dec->attn_ws,
+                             true, st);
+        for (uint32_t p = 1; p < parts; ++p) {
+            cudaError_t er = cudaStreamWaitEvent(st, dec->ev_join[p - 1], 0);
+            if (er != cudaSuccess && e == cudaSuccess) e = er;
+        }
         if (rc) return rc;
-        if (rc1) return rc1;
-        if (e != cudaSuccess) return cuda_fail(dec, e, "joining the two halves of the step");
+        if (r0) return r0;
+        if (e != cudaSuccess) return cuda_fail(dec, e, "joining the parts of the step");
     } else {
         int rc = layers_bf16(dec, d_tokens, chunk, position, d_position, ragged, 0, B, dec->attn_ws, false, st);
         if (rc) return rc;
@@ -600,7 +617,7 @@ int validate_config(const tnsr_b200_config* c, std::string& why) {
         return TNSR_B200_ERR_INVALID_ARGUMENT;
     }
     if (c->activation > TNSR_B200_ACT_SWIGLU || c->weight_dtype > TNSR_B200_BF16 || c->kv_dtype > TNSR_B200_BF16 ||
-        c->logits_mode > TNSR_B200_LOGITS_NONE || c->prefill_mode > TNSR_B200_PREFILL_SCALAR) {
+        c->logits_mode > TNSR_B200_LOGITS_NONE || c->prefill_mode > TNSR_B200_PREFILL_SCALAR || c->step_parts > 4) {
         why = "invalid enum value in configuration";
         return TNSR_B200_ERR_INVALID_ARGUMENT;
     }
@@ -712,8 +729,7 @@ int tnsr_b200_decoder_create(const tnsr_b200_config* config, tnsr_b200_decoder**
         if (v && v[0] == '1') dec->use_graphs = false;
         v = std::getenv("TNSR_B200_NO_PDL");
         if (v && v[0] == '1') dec->use_pdl = false;
-        v = std::getenv("TNSR_B200_NO_SPLIT");
-        if (v && v[0] == '1') dec->split_step = false;
+
     }
     if (cudaMallocHost((void**)&dec->h_argmax, (size_t)config->batch * 4) != cudaSuccess ||
         cudaMallocHost((void**)&dec->h_status, 16) != cudaSuccess)
@@ -723,13 +739,17 @@ int tnsr_b200_decoder_create(const tnsr_b200_config* config, tnsr_b200_decoder**
         dec->attn_ws_bytes = decode_attention_workspace_bytes(config->batch, config->capacity, config->num_heads,
                                                               config->embed_dim / config->num_heads);
         if ((rc = dev_alloc(dec, &dec->attn_ws, dec->attn_ws_bytes, true))) return bail(rc);
-        if (config->batch >= kSplitMinSessions) {
-            if ((rc = dev_alloc(dec, &dec->attn_ws2, dec->attn_ws_bytes, true))) return bail(rc);
-            if (cudaStreamCreateWithFlags(&dec->stream2, cudaStreamNonBlocking) != cudaSuccess ||
-                cudaEventCreateWithFlags(&dec->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
-                cudaEventCreateWithFlags(&dec->ev_join, cudaEventDisableTiming) != cudaSuccess)
-                return bail(cuda_fail(dec, cudaGetLastError(), "second stream of the divided step"));
+        uint32_t parts = config->step_parts ? config->step_parts : (config->batch >= kSplitMinSessions ? 2 : 1);
+        if (parts > config->batch) parts = config->batch;
+        if (parts > 1 && cudaEventCreateWithFlags(&dec->ev_fork, cudaEventDisableTiming) != cudaSuccess)
+            return bail(cuda_fail(dec, cudaGetLastError(), "fork event of the divided step"));
+        for (uint32_t p = 1; p < parts; ++p) {
+            if ((rc = dev_alloc(dec, &dec->side_ws[p - 1], dec->attn_ws_bytes, true))) return bail(rc);
+            if (cudaStreamCreateWithFlags(&dec->side_stream[p - 1], cudaStreamNonBlocking) != cudaSuccess ||
+                cudaEventCreateWithFlags(&dec->ev_join[p - 1], cudaEventDisableTiming) != cudaSuccess)
+                return bail(cuda_fail(dec, cudaGetLastError(), "side stream of the divided step"));
         }
+        dec->parts = parts;
     }
     if (dec->bf16_path) {
         dec->host_bqkv.assign((size_t)config->num_layers * 3 * d, 0.0f);
@@ -752,9 +772,11 @@ void tnsr_b200_decoder_destroy(tnsr_b200_decoder* dec) {
     if (dec->h_status) cudaFreeHost(dec->h_status);
     if (dec->h_stage) cudaFreeHost(dec->h_stage);
     drop_graphs(dec);
-    if (dec->stream2) { cudaStreamSynchronize(dec->stream2); cudaStreamDestroy(dec->stream2); }
+    for (int i = 0; i < 3; ++i) {
+        if (dec->side_stream[i]) { cudaStreamSynchronize(dec->side_stream[i]); cudaStreamDestroy(dec->side_stream[i]); }
+        if (dec->ev_join[i]) cudaEventDestroy(dec->ev_join[i]);
+    }
     if (dec->ev_fork) cudaEventDestroy(dec->ev_fork);
-    if (dec->ev_join) cudaEventDestroy(dec->ev_join);
     for (cudaEvent_t e : dec->attention_timer.events) cudaEventDestroy(e);
     if (dec->stream) cudaStreamDestroy(dec->stream);
     cudaGetLastError();
