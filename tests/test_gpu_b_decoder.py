@@ -547,3 +547,28 @@ def test_divided_single_token_step_matches_the_undivided_one(parts):
         assert np.max(np.abs(a - b)) <= max(1.0, float(np.max(np.abs(b)))) / 64
     # the first layer's keys do not depend on attention at all: identical bits in both forms
     assert np.array_equal(caches_a[0].view(np.uint32), caches_b[0].view(np.uint32))
+
+
+@pytest.mark.parametrize("weight_dtype", ["f32", "bf16"])
+def test_gpu_decoder_state_round_trips_through_the_archive(tmp_path, weight_dtype):
+    """Serialised decoder state on the device: K/V rows read back through the C ABI, written as a tensor archive,
+    restored into a fresh session (bf16 rows are exactly representable in the archive's f32), which then continues
+    with the same bits as the session that was never interrupted."""
+    cfg = GptConfig(vocab_size=320, max_sequence_length=96, embed_dim=128, num_heads=2, feed_forward_dim=256,
+                    num_layers=2, layer_norm_epsilon=1e-5, activation="gelu", weight_dtype=weight_dtype)
+    model = Gpt(cfg)
+    set_model_arrays(model, normal_model_arrays(cfg, seed=51, std=0.05))
+    ids = np.random.default_rng(52).integers(0, cfg.vocab_size, size=(3, 40)).astype(np.uint32)
+    flat = lambda lo, hi: ids[:, lo:hi].reshape(-1).tolist()
+    straight = gpu_decoder(model, 3, 96)
+    straight.decode(flat(0, 33))
+    want = [straight.decode(flat(33 + i, 34 + i)) for i in range(4)]
+    first = gpu_decoder(model, 3, 96)
+    first.decode(flat(0, 33))
+    first.save_state(str(tmp_path))
+    second = gpu_decoder(model, 3, 64)              # a different capacity is fine as long as the rows fit
+    second.load_state(str(tmp_path))
+    assert second.len() == 33
+    for i in range(4):
+        got = second.decode(flat(33 + i, 34 + i))
+        assert np.array_equal(got.view(np.uint32), want[i].view(np.uint32))

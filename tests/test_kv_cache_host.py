@@ -1,6 +1,8 @@
 """tnsr's tests/kv_cache.rs, CPU half, over the shared GptDecoder wrapper and
 the CPU checker: session guards, chunk splits vs full forward, cached vs
 uncached greedy generation, bf16 attention storage."""
+import json
+
 import numpy as np
 import pytest
 
@@ -264,3 +266,43 @@ def test_threads_do_not_change_results(oracle):
     finally:
         oracle.set_threads(1)
     assert np.array_equal(one.view(np.uint32), many.view(np.uint32))
+
+
+def test_decoder_state_round_trips_through_the_archive(tmp_path):
+    """Serialised decoder state (what docs/kv-cache.md:94-95 leaves outside the reference's API): a session saved after
+    a prefix and restored into a fresh session continues exactly as the uninterrupted one; mismatched shapes and
+    foreign archives are refused and leave the target usable."""
+    from tnsr_b200.parameters import save_gpt
+    model = kv_model(16)
+    rows = kv_test_tokens(2, 11)
+    flat = lambda lo, hi: [t for r in rows for t in r[lo:hi]]
+    straight = cpu_decoder(model, 2)
+    straight.decode(flat(0, 7))
+    expected = straight.decode(flat(7, 11))
+
+    first = cpu_decoder(model, 2)
+    first.decode(flat(0, 7))
+    first.save_state(str(tmp_path / "state"))
+    manifest = json.load(open(tmp_path / "state" / "manifest.json"))
+    assert manifest["config"]["length"] == 7 and manifest["tensors"][0]["shape"] == [2, 7, 8]
+    assert [t["name"] for t in manifest["tensors"]][:2] == ["cache.0000.key", "cache.0000.value"]
+
+    second = cpu_decoder(model, 2)
+    second.decode(flat(0, 3))                      # previous contents are discarded by the load
+    second.load_state(str(tmp_path / "state"))
+    assert second.len() == 7
+    assert np.array_equal(second.decode(flat(7, 11)).view(np.uint32), expected.view(np.uint32))
+
+    empty = cpu_decoder(model, 2)
+    empty.save_state(str(tmp_path / "empty"))
+    second.load_state(str(tmp_path / "empty"))
+    assert second.is_empty()
+
+    with pytest.raises(TnsrError):
+        cpu_decoder(model, 3).load_state(str(tmp_path / "state"))          # other batch
+    with pytest.raises(TnsrError):
+        cpu_decoder(model, 2, 5).load_state(str(tmp_path / "state"))       # 7 rows do not fit 5
+    save_gpt(model, str(tmp_path / "weights"))
+    with pytest.raises(TnsrError):
+        second.load_state(str(tmp_path / "weights"))                       # a parameter archive, not a state
+    second.decode(flat(0, 2))                                              # still usable

@@ -369,6 +369,15 @@ class GptDecoder:
         self._backend.reset()
         self._failed = False
 
+    def save_state(self, directory: str) -> None:
+        """K/V rows and length into a tensor archive (see ``parameters.save_decoder_state``)."""
+        from .parameters import save_decoder_state
+        save_decoder_state(self, directory)
+
+    def load_state(self, directory: str) -> None:
+        from .parameters import load_decoder_state
+        load_decoder_state(self, directory)
+
     def decode(self, tokens: Sequence[int]) -> np.ndarray:
         if self._failed:
             raise TnsrError("decoder execution failed; reset the cache before reuse")

@@ -184,3 +184,62 @@ def save_gpt(model: Gpt, directory: str) -> None:
 def load_gpt(directory: str) -> Gpt:
     named, config = NamedParameters.load(directory)
     return gpt_from_named(named, config)
+
+
+# ---- serialised decoder state -------------------------------------------------------------------
+# tnsr lists "serialized decoder state" as outside its decoder API (docs/kv-cache.md:94-95).  Here a session's
+# state -- the live rows of its 2 * layers K/V tensors and its length -- travels in the same archive format as
+# parameters: tensors `cache.<layer>.key` / `cache.<layer>.value` of shape [batch, length, embed_dim] (only the live
+# prefix; rows past `length` are zero in a session by construction, src/nn/kv_cache.rs:238-257), group
+# "decoder_state", and a config object that pins the shape the state belongs to.
+
+def decoder_state_config(decoder) -> dict:
+    c = decoder._model.config()
+    return dict(kind="gpt_decoder_state", batch=decoder.batch_size(), capacity=decoder.capacity(), length=decoder.len(),
+                num_layers=c.num_layers, embed_dim=c.embed_dim, num_heads=c.num_heads,
+                attention_precision=decoder._options.attention_precision.value, weight_dtype=c.weight_dtype)
+
+
+def save_decoder_state(decoder, directory: str) -> None:
+    """Writes the K/V rows [0, len) of every layer and the length of `decoder` (a ``GptDecoder``) to `directory`."""
+    if decoder._failed:
+        raise TnsrError("decoder execution failed; reset the cache before reuse")
+    config = decoder_state_config(decoder)
+    named = NamedParameters()
+    length = decoder.len()
+    if length:
+        for layer in range(config["num_layers"]):
+            for which, name in enumerate(("key", "value")):
+                rows = decoder._backend.read_cache(2 * layer + which)[:, :length, :]
+                named.insert(f"cache.{layer:04d}.{name}", rows, rows.shape, "decoder_state")
+    named.save(directory, config)
+
+
+def load_decoder_state(decoder, directory: str) -> None:
+    """Restores a state written by ``save_decoder_state`` into `decoder`, which must have the same batch, layer count,
+    width and precision and enough capacity; its previous contents are discarded.  The weights are the caller's
+    business, exactly as with a live session: a state only continues correctly under the weights that produced it."""
+    named, config = NamedParameters.load(directory)
+    if not isinstance(config, dict) or config.get("kind") != "gpt_decoder_state":
+        raise TnsrError("archive does not hold a decoder state")
+    mine = decoder_state_config(decoder)
+    for key in ("batch", "num_layers", "embed_dim", "num_heads", "attention_precision", "weight_dtype"):
+        if config.get(key) != mine[key]:
+            raise TnsrError(f"decoder state mismatch: {key} is {config.get(key)!r}, this decoder has {mine[key]!r}")
+    length = config.get("length")
+    if not isinstance(length, int) or length < 0 or length > decoder.capacity():
+        raise TnsrError("decoder context capacity exceeded")
+    names = {f"cache.{layer:04d}.{name}" for layer in range(mine["num_layers"]) for name in ("key", "value")} if length else set()
+    named.validate_names(names)
+    decoder.reset()
+    shape = [mine["batch"], length, mine["embed_dim"]]
+    decoder._failed = True
+    for layer in range(mine["num_layers"]) if length else ():
+        for which, name in enumerate(("key", "value")):
+            rows = named.get(f"cache.{layer:04d}.{name}", shape).values().reshape(shape)
+            full = np.zeros((mine["batch"], decoder.capacity(), mine["embed_dim"]), dtype=np.float32)
+            full[:, :length, :] = rows
+            decoder._backend.write_cache(2 * layer + which, full)
+    decoder._length = length
+    decoder._revisions = [p.revision() for p in decoder._parameters]
+    decoder._failed = False
