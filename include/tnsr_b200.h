@@ -218,6 +218,14 @@ TNSR_B200_API int tnsr_b200_decoder_decode_ragged(tnsr_b200_decoder* dec, const 
 TNSR_B200_API int tnsr_b200_decoder_decode_device(tnsr_b200_decoder* dec, const uint32_t* d_tokens,
                                                   uint32_t chunk, uint32_t position,
                                                   uint32_t* d_argmax_out);
+/* Replaces the greedy pick of `argmax_out` / `d_argmax_out` by
+ * tnsr_b200_sample_top_k on the last position's logits: session b at a step
+ * that ends at position p (its new token will sit at p) draws with counter
+ * (p, 0, b, 0), so a run is reproducible from (seed, ids) whatever the chunking.
+ * temperature <= 0 switches back to greedy.  Logits are materialised on the
+ * device while a sampler is set, also with LOGITS_NONE. */
+TNSR_B200_API int tnsr_b200_decoder_set_sampler(tnsr_b200_decoder* dec, float temperature, uint32_t top_k,
+                                                uint64_t seed);
 /* Waits for the session's stream and reports any deferred device-side error. */
 TNSR_B200_API int tnsr_b200_decoder_synchronize(tnsr_b200_decoder* dec);
 /* The session's private stream as a cudaStream_t (for event timing). */
@@ -376,6 +384,20 @@ TNSR_B200_API int tnsr_b200_prefill_attention(const void* q, const void* k_cache
                                               void* out, uint32_t batch, uint32_t chunk,
                                               uint32_t position, uint32_t capacity, uint32_t heads,
                                               uint32_t head_dim, void* stream);
+
+/* Next-token sampling on the device (no reference counterpart: tnsr's decode
+ * loop is greedy, src/nn/kv_cache.rs:121-157).  Per row: the top_k entries
+ * under IEEE totalOrder with ties towards the larger index (so top_k = 1 is
+ * exactly tnsr_b200_argmax); walked in index order with weights
+ * w_j = (float)exp((double)((l_j - l_max) / temperature)) summed in f32; one
+ * uniform u = (x >> 8) * 2^-24 from Philox4x32-10 with counter (step, 0,
+ * first_session + row, 0) and key (seed & 0xffffffff, seed >> 32); the pick is
+ * the first candidate whose running sum exceeds u * sum.  temperature > 0,
+ * 1 <= top_k <= 256.  The rule is stated operation by operation so that a CPU
+ * restatement reproduces the ids exactly. */
+TNSR_B200_API int tnsr_b200_sample_top_k(const float* logits, uint32_t* out, uint32_t rows, uint32_t vocab,
+                                         float temperature, uint32_t top_k, uint64_t seed, uint32_t step,
+                                         uint32_t first_session, void* stream);
 
 /* Greedy pick per row: the last index holding the maximum under IEEE
  * totalOrder (src/nn/kv_cache.rs:148-153). */

@@ -478,3 +478,32 @@ def test_argmax_prefers_the_last_maximum(oracle):
     ok(lib().tnsr_b200_argmax(ptr(dev(small)), ptr(out), 1, 4, stream()))
     torch.cuda.synchronize()
     assert int(out[0]) == 2
+
+
+@pytest.mark.parametrize("vocab,top_k,temperature", [(32000, 40, 0.8), (32000, 256, 1.3), (1000, 5, 0.5), (97, 1, 1.0),
+                                                     (50, 256, 2.0)])
+def test_sample_top_k_matches_the_cpu_restatement(vocab, top_k, temperature):
+    """Device sampling against oracle/sampler.py on the same logits: same candidates (ties towards the larger index),
+    same f32 weights and running sums, same Philox draw -> the same id for every row."""
+    from oracle import sampler
+    rng = np.random.default_rng(vocab + top_k)
+    rows = 48
+    logits = (rng.standard_normal((rows, vocab)) * 3).astype(np.float32)
+    logits[1, ::7] = logits[1].max()                       # many ties at the top
+    logits[2, :] = 0.25                                    # all equal: the candidates are the last top_k indices
+    logits[3, 5] = -0.0
+    logits[4, : vocab // 2] = -np.inf
+    d_logits = dev(logits)
+    out = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    ok(lib().tnsr_b200_sample_top_k(ptr(d_logits), ptr(out), rows, vocab, temperature, top_k, 0x1234567890ABCDEF, 77, 9,
+                                    stream()))
+    torch.cuda.synchronize()
+    want = sampler.sample(logits, temperature, top_k, 0x1234567890ABCDEF, 77, first_session=9)
+    assert np.array_equal(out.cpu().numpy().astype(np.uint32), want)
+    if top_k == 1:
+        greedy = torch.zeros(rows, dtype=torch.int32, device="cuda")
+        ok(lib().tnsr_b200_argmax(ptr(d_logits), ptr(greedy), rows, vocab, stream()))
+        torch.cuda.synchronize()
+        assert torch.equal(out, greedy)
+    assert lib().tnsr_b200_sample_top_k(ptr(d_logits), ptr(out), rows, vocab, 0.0, top_k, 1, 0, 0, stream()) == -1
+    assert lib().tnsr_b200_sample_top_k(ptr(d_logits), ptr(out), rows, vocab, 1.0, 257, 1, 0, 0, stream()) == -1

@@ -17,6 +17,7 @@ from tests.test_kv_cache_host import chunks_match, validate_inputs_and_weights  
 from tests.workloads import (config0_model, config0_prompt, kv_test_tokens, normal_model_arrays,  # noqa: E402
                              set_model_arrays)
 from tnsr_b200.nn import (Backend, Gpt, GptAttentionPrecision, GptConfig, GptDecoder, GptDecoderOptions,  # noqa: E402
+                          argmax_last,
                           GptPrefillMode, model_parameters)
 from tnsr_b200.session import B200Session  # noqa: E402
 
@@ -572,3 +573,41 @@ def test_gpu_decoder_state_round_trips_through_the_archive(tmp_path, weight_dtyp
     for i in range(4):
         got = second.decode(flat(33 + i, 34 + i))
         assert np.array_equal(got.view(np.uint32), want[i].view(np.uint32))
+
+
+@pytest.mark.parametrize("logits_mode", ["last", "none"])
+def test_session_sampler_draws_what_the_cpu_restatement_draws(logits_mode):
+    """`tnsr_b200_decoder_set_sampler`: the ids a session returns are the CPU sampler's ids on the session's own
+    last-position logits, with the counter (position of the new token, session); the draw does not depend on whether
+    logits leave the device, on graph replay, or on the chunking; temperature 0 restores the greedy pick."""
+    from oracle import sampler
+    cfg = GptConfig(vocab_size=1536, max_sequence_length=64, embed_dim=128, num_heads=2, feed_forward_dim=256,
+                    num_layers=2, layer_norm_epsilon=1e-5, activation="swiglu", weight_dtype="bf16")
+    arrays = normal_model_arrays(cfg, seed=61, std=0.08)
+    ids = np.random.default_rng(62).integers(0, cfg.vocab_size, size=(5, 9)).astype(np.uint32)
+    seed, temperature, top_k = 424242, 0.9, 12
+
+    def session(mode):
+        s = B200Session(cfg, 5, 48, logits_mode=mode)
+        for i, a in enumerate(arrays):
+            s.refresh(i, a)
+        s.set_sampler(temperature, top_k, seed)
+        return s
+
+    ref = session("last")
+    s = session(logits_mode)
+    logits, want_ids = ref.decode_full(ids, 0)
+    _, got = s.decode_full(ids, 0)
+    assert np.array_equal(want_ids, sampler.sample(logits.reshape(5, -1), temperature, top_k, seed, 9))
+    assert np.array_equal(got, want_ids)
+    for t in range(6):                       # single-token steps: one direct, then graph replays
+        logits, want_ids = ref.decode_full(want_ids.reshape(5, 1), 9 + t)
+        assert np.array_equal(want_ids, sampler.sample(logits.reshape(5, -1), temperature, top_k, seed, 10 + t))
+        _, got = s.decode_full(got.reshape(5, 1), 9 + t)
+        assert np.array_equal(got, want_ids)
+    s.set_sampler(0.0, 0, 0)
+    ref.set_sampler(0.0, 0, 0)
+    logits, greedy = ref.decode_full(want_ids.reshape(5, 1), 15)
+    assert greedy.tolist() == [argmax_last(r) for r in logits.reshape(5, -1)]
+    _, got = s.decode_full(want_ids.reshape(5, 1), 15)
+    assert np.array_equal(got, greedy)

@@ -163,6 +163,11 @@ int launch_gather_last_rows(const float* x, float* out, uint32_t sessions, uint3
                             cudaStream_t stream);
 int launch_argmax(const float* logits, uint32_t* out, uint32_t rows, uint32_t vocab, uint32_t row_stride,
                   cudaStream_t stream);
+// Next-token sampling (temperature, top-k, Philox per (session, step)); see sampler.cu for the exact rule.  The step
+// of row r is (d_step[r * step_stride] if d_step is given, else 0) + step_add; row r belongs to session first_session + r.
+int launch_sample_top_k(const float* logits, uint32_t* out, uint32_t rows, uint32_t vocab, uint32_t row_stride,
+                        float temperature, uint32_t top_k, uint64_t seed, const uint32_t* d_step, uint32_t step_stride,
+                        uint32_t step_add, uint32_t first_session, cudaStream_t stream);
 int launch_swiglu(const bf16* gate, const bf16* up, bf16* out, uint64_t elems, cudaStream_t stream);
 int launch_transpose_bf16(const bf16* in, bf16* out, uint32_t k, uint32_t n, cudaStream_t stream);
 int launch_f32_to_bf16(const float* in, bf16* out, uint64_t elems, cudaStream_t stream);

@@ -108,6 +108,10 @@ struct tnsr_b200_decoder {
     cudaStream_t side_stream[3] = {nullptr, nullptr, nullptr};   // forked from and joined to `stream` by events
     cudaEvent_t ev_fork = nullptr, ev_join[3] = {nullptr, nullptr, nullptr};
     uint32_t parts = 1;
+    // next-token sampling instead of the greedy pick (temperature <= 0: greedy)
+    float sample_temperature = 0.0f;
+    uint32_t sample_top_k = 0;
+    uint64_t sample_seed = 0;
     uint32_t* d_positions = nullptr;   // [batch] per-session positions of a ragged step
     uint32_t* h_positions = nullptr;   // pinned staging for them
     // pinned staging
@@ -537,7 +541,8 @@ int run_step_direct(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t c
     const tnsr_b200_config& c = dec->cfg;
     const uint32_t rows = c.batch * chunk;
     const uint32_t logit_rows = c.logits_mode == TNSR_B200_LOGITS_ALL ? rows : c.batch;
-    const bool fuse_ids = dec->bf16_path && c.logits_mode == TNSR_B200_LOGITS_NONE && d_argmax_out && dec->lm_candidates;
+    const bool sampling = dec->sample_temperature > 0.0f;
+    const bool fuse_ids = dec->bf16_path && c.logits_mode == TNSR_B200_LOGITS_NONE && d_argmax_out && dec->lm_candidates && !sampling;
     t_attention_timer = dec->profile_attention ? &dec->attention_timer : nullptr;
     t_pdl = dec->use_pdl && dec->bf16_path && chunk == 1;
     int rc = dec->bf16_path ? step_bf16(dec, d_tokens, chunk, position, d_position, logit_rows, fuse_ids ? d_argmax_out : nullptr)
@@ -552,7 +557,11 @@ int run_step_direct(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t c
             base = dec->logits + (size_t)(chunk - 1) * c.vocab_size;
             stride = chunk * c.vocab_size;
         }
-        int arc = launch_argmax(base, d_argmax_out, c.batch, c.vocab_size, stride, dec->stream);
+        // the new token of a step that starts at `position` with `chunk` rows will sit at position + chunk
+        int arc = sampling ? launch_sample_top_k(base, d_argmax_out, c.batch, c.vocab_size, stride, dec->sample_temperature,
+                                                 dec->sample_top_k, dec->sample_seed, d_position, 0,
+                                                 (d_position ? 0 : position) + chunk, 0, dec->stream)
+                           : launch_argmax(base, d_argmax_out, c.batch, c.vocab_size, stride, dec->stream);
         if (arc) {
             t_pdl = false;
             dec->error = thread_error();
@@ -981,10 +990,14 @@ int tnsr_b200_decoder_decode_ragged(tnsr_b200_decoder* dec, const uint32_t* toke
     std::memcpy(dec->h_positions, positions, (size_t)c.batch * 4);
     CU(dec, cudaMemcpyAsync(dec->d_tokens, dec->h_tokens, (size_t)c.batch * 4, cudaMemcpyHostToDevice, dec->stream));
     CU(dec, cudaMemcpyAsync(dec->d_positions, dec->h_positions, (size_t)c.batch * 4, cudaMemcpyHostToDevice, dec->stream));
-    const bool fuse_ids = c.logits_mode == TNSR_B200_LOGITS_NONE && argmax_out && dec->lm_candidates;
+    const bool sampling = dec->sample_temperature > 0.0f;
+    const bool fuse_ids = c.logits_mode == TNSR_B200_LOGITS_NONE && argmax_out && dec->lm_candidates && !sampling;
     if ((rc = step_bf16(dec, dec->d_tokens, 1, 0, dec->d_positions, c.batch, fuse_ids ? dec->d_argmax : nullptr, true))) return rc;
     if (argmax_out && !fuse_ids) {
-        rc = launch_argmax(dec->logits, dec->d_argmax, c.batch, c.vocab_size, c.vocab_size, dec->stream);
+        // session b's new token will sit at positions[b] + 1
+        rc = sampling ? launch_sample_top_k(dec->logits, dec->d_argmax, c.batch, c.vocab_size, c.vocab_size, dec->sample_temperature,
+                                            dec->sample_top_k, dec->sample_seed, dec->d_positions, 1, 1, 0, dec->stream)
+                      : launch_argmax(dec->logits, dec->d_argmax, c.batch, c.vocab_size, c.vocab_size, dec->stream);
         if (rc) { dec->error = thread_error(); return rc; }
     }
     if (logits_out)
@@ -1015,6 +1028,19 @@ int tnsr_b200_decoder_decode_device(tnsr_b200_decoder* dec, const uint32_t* d_to
     const uint32_t logit_rows = c.logits_mode == TNSR_B200_LOGITS_ALL ? rows : c.batch;
     if ((rc = ensure_rows(dec, rows, logit_rows))) return rc;
     return run_step(dec, d_tokens, chunk, position, d_argmax_out);
+}
+
+int tnsr_b200_decoder_set_sampler(tnsr_b200_decoder* dec, float temperature, uint32_t top_k, uint64_t seed) {
+    if (!dec) return fail(nullptr, TNSR_B200_ERR_INVALID_ARGUMENT, "null decoder");
+    if (temperature > 0.0f && (!std::isfinite(temperature) || top_k == 0 || top_k > 256))
+        return fail(dec, TNSR_B200_ERR_INVALID_ARGUMENT, "sampling needs a finite temperature and 1 <= top_k <= 256");
+    CU(dec, cudaSetDevice(dec->cfg.device));
+    CU(dec, cudaStreamSynchronize(dec->stream));
+    drop_graphs(dec);   // captured steps contain the previous pick
+    dec->sample_temperature = temperature > 0.0f ? temperature : 0.0f;
+    dec->sample_top_k = top_k;
+    dec->sample_seed = seed;
+    return TNSR_B200_OK;
 }
 
 int tnsr_b200_decoder_synchronize(tnsr_b200_decoder* dec) {

@@ -142,6 +142,13 @@ int tnsr_b200_prefill_attention(const void* q, const void* k_cache, const void* 
                                     position, nullptr, capacity, heads, head_dim, as_stream(stream));
 }
 
+int tnsr_b200_sample_top_k(const float* logits, uint32_t* out, uint32_t rows, uint32_t vocab, float temperature,
+                           uint32_t top_k, uint64_t seed, uint32_t step, uint32_t first_session, void* stream) {
+    if (!logits || !out) return bad("sample_top_k: null pointer");
+    return launch_sample_top_k(logits, out, rows, vocab, vocab, temperature, top_k, seed, nullptr, 0, step, first_session,
+                               as_stream(stream));
+}
+
 int tnsr_b200_argmax(const float* logits, uint32_t* out, uint32_t rows, uint32_t vocab, void* stream) {
     if (!logits || !out || vocab == 0) return bad("argmax: null pointer or empty vocabulary");
     return launch_argmax(logits, out, rows, vocab, vocab, as_stream(stream));

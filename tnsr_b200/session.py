@@ -96,6 +96,10 @@ class B200Session:
     def decode_device(self, d_tokens_ptr: int, chunk: int, position: int, d_argmax_ptr: int) -> None:
         self._check(lib().tnsr_b200_decoder_decode_device(self.handle, d_tokens_ptr, chunk, position, d_argmax_ptr))
 
+    def set_sampler(self, temperature: float, top_k: int, seed: int) -> None:
+        """Greedy ids become top-k / temperature samples (temperature <= 0: back to greedy)."""
+        self._check(lib().tnsr_b200_decoder_set_sampler(self.handle, float(temperature), int(top_k), int(seed)))
+
     def synchronize(self) -> None:
         self._check(lib().tnsr_b200_decoder_synchronize(self.handle))
 
