@@ -385,6 +385,39 @@ TNSR_B200_API int tnsr_b200_prefill_attention(const void* q, const void* k_cache
                                               uint32_t position, uint32_t capacity, uint32_t heads,
                                               uint32_t head_dim, void* stream);
 
+/* ---- the forty_five token encoder's extra operators ---------------------- */
+/* tnsr's second model on this operator set is the token encoder of its
+ * forty_five example (examples/forty_five/mod.rs:329-407): a bidirectional
+ * pre-norm transformer with SwiGLU blocks over short token rows.  Its
+ * projections, LayerNorms and SwiGLU are the strict f32 operators above; these
+ * are the two operators it adds, plus two elementwise helpers.  All f32, in
+ * the reference's CPU operation order. */
+
+/* out[r, :] = mask[r] != 0 ? (token_table[ids[r]] + type_table[type_ids[r]])
+ *                            + position_table[position_ids[r % seq]] : 0
+ * (mod.rs:343-357).  rows = batch * seq.  Ids outside their table set *d_status
+ * (if non-NULL) to 1 and give a zero row. */
+TNSR_B200_API int tnsr_b200_encoder_embed(const float* token_table, const float* type_table,
+                                          const float* position_table, const uint32_t* ids,
+                                          const uint32_t* type_ids, const uint32_t* position_ids,
+                                          const float* mask, float* out, uint32_t rows, uint32_t seq,
+                                          uint32_t vocab, uint32_t type_vocab, uint32_t width,
+                                          int* d_status, void* stream);
+/* Bidirectional attention with an additive key mask (mod.rs:358-386):
+ * score = (q . k) * 1/sqrt(head_dim) + key_mask[sample, key]; softmax over all
+ * seq keys; out = weights . v.  q, k, v: [batch, seq, heads*head_dim] f32 rows
+ * `row_stride` floats apart (3 * width when they are slices of one fused
+ * projection); key_mask [batch, seq] f32 (0, or a large negative value such as
+ * f32::MIN for padding); out [batch, seq, heads*head_dim] contiguous. */
+TNSR_B200_API int tnsr_b200_encoder_attention(const float* q, const float* k, const float* v,
+                                              uint32_t row_stride, const float* key_mask, float* out,
+                                              uint32_t batch, uint32_t seq, uint32_t heads,
+                                              uint32_t head_dim, void* stream);
+/* out = a + b and out = silu(gate) * up (src/nn/activations.rs:5-20 op by op), f32. */
+TNSR_B200_API int tnsr_b200_add_f32(const float* a, const float* b, float* out, uint64_t elems, void* stream);
+TNSR_B200_API int tnsr_b200_swiglu_f32(const float* gate, const float* up, float* out, uint64_t elems,
+                                       void* stream);
+
 /* Next-token sampling on the device (no reference counterpart: tnsr's decode
  * loop is greedy, src/nn/kv_cache.rs:121-157).  Per row: the top_k entries
  * under IEEE totalOrder with ties towards the larger index (so top_k = 1 is

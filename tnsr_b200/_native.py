@@ -75,6 +75,10 @@ SIGNATURES = {
     "tnsr_b200_decode_attention_static": (_i, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _vp]),
     "tnsr_b200_prefill_attention": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _vp]),
     "tnsr_b200_argmax": (_i, [_vp, _vp, _u32, _u32, _vp]),
+    "tnsr_b200_encoder_embed": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _vp]),
+    "tnsr_b200_encoder_attention": (_i, [_vp, _vp, _vp, _u32, _vp, _vp, _u32, _u32, _u32, _u32, _vp]),
+    "tnsr_b200_add_f32": (_i, [_vp, _vp, _vp, _u64, _vp]),
+    "tnsr_b200_swiglu_f32": (_i, [_vp, _vp, _vp, _u64, _vp]),
     "tnsr_b200_sample_top_k": (_i, [_vp, _vp, _u32, _u32, _f, _u32, _u64, _u32, _u32, _vp]),
     "tnsr_b200_decoder_set_sampler": (_i, [_vp, _f, _u32, _u64]),
 }

@@ -4,8 +4,9 @@
 
 Every ``.cu`` file is compiled with ``-gencode arch=compute_100a,code=sm_100a``
 and linked into one shared library whose only exports are the ``extern "C"``
-entry points of ``include/tnsr_b200.h``.  ``strict.cu`` is compiled with
-``--fmad=false``: its kernels must round every product before adding it.
+entry points of ``include/tnsr_b200.h``.  ``strict.cu`` and ``encoder.cu`` are
+compiled with ``--fmad=false``: their kernels must round every product before
+adding it.
 """
 from __future__ import annotations
 
@@ -23,8 +24,8 @@ OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(CSRC, "libtnsr_b200.so")
 
 SOURCES = ["decoder.cu", "ops_api.cu", "elementwise.cu", "strict.cu", "gemm.cu", "gemm_skinny.cu", "attention.cu", "prefill.cu", "prefill_tc.cu",
-           "decode_attention_static.cu", "sampler.cu"]
-EXTRA = {"strict.cu": ["--fmad=false"]}
+           "decode_attention_static.cu", "sampler.cu", "encoder.cu"]
+EXTRA = {"strict.cu": ["--fmad=false"], "encoder.cu": ["--fmad=false"]}
 
 BASE_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
