@@ -114,6 +114,21 @@ typedef struct tnsr_b200_config {
      * rounding).  0 = automatic (2 from 192 sessions up, else 1), 1 = never
      * divide, 2..4 = that many parts. */
     uint32_t step_parts;
+    /* Paged K/V (no reference counterpart; the reference's cache is one
+     * [batch, capacity, width] slab per tensor and its documentation lists ragged
+     * batches as future work, docs/kv-cache.md:94-95).  kv_page_rows > 0 stores
+     * every cache tensor as a pool of kv_pool_pages pages of kv_page_rows rows
+     * shared by all sessions of the handle; a session gets a page when one of
+     * its rows is first written and gives its pages back through
+     * tnsr_b200_decoder_release or reset, so memory follows the live tokens
+     * instead of batch * capacity.  Requirements: bf16 weights, kv_page_rows a
+     * multiple of 16 that divides capacity.  kv_pool_pages = 0 sizes the pool
+     * for the worst case (batch * capacity / kv_page_rows).  A step that needs a
+     * page when none is free fails with TNSR_B200_ERR_CAPACITY and changes
+     * nothing.  Multi-token chunks run on the non-tiled attention scan in this
+     * mode. */
+    uint32_t kv_page_rows;
+    uint32_t kv_pool_pages;
 } tnsr_b200_config;
 
 typedef struct tnsr_b200_decoder tnsr_b200_decoder;
@@ -226,6 +241,11 @@ TNSR_B200_API int tnsr_b200_decoder_decode_device(tnsr_b200_decoder* dec, const 
  * device while a sampler is set, also with LOGITS_NONE. */
 TNSR_B200_API int tnsr_b200_decoder_set_sampler(tnsr_b200_decoder* dec, float temperature, uint32_t top_k,
                                                 uint64_t seed);
+/* Paged handles only: returns the pages of session `session` to the pool (its
+ * rows are gone; the caller restarts it at position 0).  Waits for queued work. */
+TNSR_B200_API int tnsr_b200_decoder_release(tnsr_b200_decoder* dec, uint32_t session);
+/* Paged handles only: pages currently not assigned to any session. */
+TNSR_B200_API uint32_t tnsr_b200_decoder_free_pages(const tnsr_b200_decoder* dec);
 /* Waits for the session's stream and reports any deferred device-side error. */
 TNSR_B200_API int tnsr_b200_decoder_synchronize(tnsr_b200_decoder* dec);
 /* The session's private stream as a cudaStream_t (for event timing). */

@@ -611,3 +611,75 @@ def test_session_sampler_draws_what_the_cpu_restatement_draws(logits_mode):
     assert greedy.tolist() == [argmax_last(r) for r in logits.reshape(5, -1)]
     _, got = s.decode_full(want_ids.reshape(5, 1), 15)
     assert np.array_equal(got, greedy)
+
+
+def test_paged_kv_cache_gives_the_same_bits_as_the_contiguous_one():
+    """kv_page_rows > 0: every cache tensor is a pool of pages handed to sessions on demand.  Same kernels, other
+    addresses: prefill (non-tiled scan in both handles), graph-replayed steps, ragged steps and the cache read back in
+    logical order must equal the contiguous handle bit for bit -- also when a step is divided over two streams."""
+    cfg = GptConfig(vocab_size=512, max_sequence_length=96, embed_dim=256, num_heads=4, feed_forward_dim=512,
+                    num_layers=2, layer_norm_epsilon=1e-5, activation="swiglu", weight_dtype="bf16")
+    arrays = normal_model_arrays(cfg, seed=81, std=0.05)
+    batch, capacity = 6, 96
+    ids = np.random.default_rng(82).integers(0, cfg.vocab_size, size=(batch, 40)).astype(np.uint32)
+
+    def run(**kw):
+        s = B200Session(cfg, batch, capacity, GptDecoderOptions(prefill=GptPrefillMode.Scalar), logits_mode="last", **kw)
+        for i, a in enumerate(arrays):
+            s.refresh(i, a)
+        out = [s.decode_full(ids[:, :21], 0)[0]]
+        for t in range(21, 36):                                   # crosses the page boundary at row 32
+            out.append(s.decode_full(ids[:, t:t + 1], t)[0])
+        positions = np.asarray([36, 30, 36, 17, 33, 36], dtype=np.uint32)
+        out.append(s.decode_ragged(ids[:, 36], positions)[0])
+        caches = [s.read_cache(i) for i in range(4)]
+        free = s.free_pages()
+        s.close()
+        return np.stack([o.reshape(batch, -1) for o in out]), caches, free
+
+    plain, plain_caches, _ = run()
+    paged, paged_caches, free = run(kv_page_rows=16)
+    assert free == batch * (capacity // 16) - batch * 3            # 37 rows per session -> 3 pages each
+    assert np.array_equal(paged.view(np.uint32), plain.view(np.uint32))
+    for a, b in zip(paged_caches, plain_caches):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    divided, _, _ = run(kv_page_rows=32, step_parts=2)
+    reference, _, _ = run(step_parts=2)
+    assert np.array_equal(divided.view(np.uint32), reference.view(np.uint32))
+
+
+def test_paged_kv_pool_smaller_than_the_worst_case():
+    """A pool of 7 pages for 4 sessions x 64 rows (worst case 16 pages): short sessions fit, a step that would need an
+    eighth page is refused with ERR_CAPACITY and changes nothing, releasing a session makes room again."""
+    from tnsr_b200 import _native
+    cfg = GptConfig(vocab_size=256, max_sequence_length=64, embed_dim=128, num_heads=2, feed_forward_dim=256,
+                    num_layers=2, layer_norm_epsilon=1e-5, activation="gelu", weight_dtype="bf16")
+    arrays = normal_model_arrays(cfg, seed=83, std=0.05)
+    s = B200Session(cfg, 4, 64, logits_mode="last", kv_page_rows=16, kv_pool_pages=7)
+    for i, a in enumerate(arrays):
+        s.refresh(i, a)
+    ids = np.random.default_rng(84).integers(0, cfg.vocab_size, size=(4, 64)).astype(np.uint32)
+    s.decode_full(ids[:, :16], 0)                                   # 4 pages
+    assert s.free_pages() == 3
+    positions = np.asarray([16, 16, 16, 5], dtype=np.uint32)        # three sessions open a second page
+    before, _ = s.decode_ragged(ids[:, 16], positions)
+    assert s.free_pages() == 0
+    u32p = _native.C.POINTER(_native.C.c_uint32)
+    pos2 = np.asarray([17, 17, 17, 16], dtype=np.uint32)            # session 3 now needs a page that is not there
+    tok = np.ascontiguousarray(ids[:, 17])
+    logits = np.empty(4 * cfg.vocab_size, dtype=np.float32)
+    code = _native.lib().tnsr_b200_decoder_decode_ragged(s.handle, tok.ctypes.data_as(u32p), pos2.ctypes.data_as(u32p),
+                                                        logits.ctypes.data_as(_native.C.POINTER(_native.C.c_float)), None)
+    assert code == -4 and "page pool exhausted" in _native.last_error(s.handle)
+    again, _ = s.decode_ragged(ids[:, 16], positions)                # the refused step left the session as it was
+    assert np.array_equal(again.view(np.uint32), before.view(np.uint32))
+    s.release(0)                                                     # two pages come back
+    assert s.free_pages() == 2
+    pos3 = np.asarray([0, 17, 17, 16], dtype=np.uint32)              # session 0 starts over, session 3 gets its page
+    out, _ = s.decode_ragged(ids[:, 17], pos3)
+    assert np.all(np.isfinite(out)) and s.free_pages() == 0
+    s.reset()
+    assert s.free_pages() == 7
+    s.close()
+    with pytest.raises(Exception):
+        B200Session(cfg, 4, 64, kv_page_rows=24)                     # not a multiple of 16

@@ -30,6 +30,7 @@ class Config(C.Structure):
         ("layer_norm_epsilon", C.c_float), ("activation", C.c_uint32), ("weight_dtype", C.c_uint32),
         ("kv_dtype", C.c_uint32), ("batch", C.c_uint32), ("capacity", C.c_uint32), ("device", C.c_int32),
         ("logits_mode", C.c_uint32), ("prefill_mode", C.c_uint32), ("step_parts", C.c_uint32),
+        ("kv_page_rows", C.c_uint32), ("kv_pool_pages", C.c_uint32),
     ]
 
 
@@ -81,6 +82,8 @@ SIGNATURES = {
     "tnsr_b200_swiglu_f32": (_i, [_vp, _vp, _vp, _u64, _vp]),
     "tnsr_b200_sample_top_k": (_i, [_vp, _vp, _u32, _u32, _f, _u32, _u64, _u32, _u32, _vp]),
     "tnsr_b200_decoder_set_sampler": (_i, [_vp, _f, _u32, _u64]),
+    "tnsr_b200_decoder_release": (_i, [_vp, _u32]),
+    "tnsr_b200_decoder_free_pages": (_u32, [_vp]),
 }
 
 _lib = None

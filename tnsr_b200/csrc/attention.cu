@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(128)
 attention_generic_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                          bf16* __restrict__ out, uint32_t total_queries, uint32_t chunk, uint32_t position,
                          const uint32_t* __restrict__ d_position, uint32_t capacity, uint32_t heads, uint32_t hd,
-                         float scale_log2) {
+                         float scale_log2, KvPaging paging) {
     pdl_wait();
     pdl_trigger();
     const uint32_t lane = threadIdx.x & 31;
@@ -63,10 +63,11 @@ attention_generic_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc
         qv[i] = c < hd ? __bfloat162float(qr[c]) * scale_log2 : 0.0f;
         acc[i] = 0.0f;
     }
-    const bf16* kb = kc + (size_t)s * capacity * d + (size_t)h * hd;
-    const bf16* vb = vc + (size_t)s * capacity * d + (size_t)h * hd;
+    const bf16* kb = kc + (size_t)h * hd;
+    const bf16* vb = vc + (size_t)h * hd;
     float m = -INFINITY, l = 0.0f;
-    for (uint32_t j = 0; j < total; ++j) {
+    for (uint32_t j0 = 0; j0 < total; ++j0) {
+        const size_t j = kv_row(paging, s, j0, capacity);
         float part = 0.0f;
 #pragma unroll
         for (int i = 0; i < GEN_MAX_SLOTS; ++i) {
@@ -96,7 +97,7 @@ attention_generic_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc
 int launch_attention_generic(const bf16* q, const bf16* k_cache, const bf16* v_cache, bf16* out,
                              uint32_t sessions, uint32_t chunk, uint32_t position,
                              const uint32_t* d_position, uint32_t capacity, uint32_t heads,
-                             uint32_t head_dim, cudaStream_t stream) {
+                             uint32_t head_dim, cudaStream_t stream, const KvPaging* paging) {
     if (sessions == 0 || chunk == 0) return TNSR_B200_OK;
     if (head_dim > 32 * GEN_MAX_SLOTS) {
         set_thread_error("attention: head_dim above 256 is outside the bf16 kernels");
@@ -106,7 +107,7 @@ int launch_attention_generic(const bf16* q, const bf16* k_cache, const bf16* v_c
     if (total > 0x7fffffffull) return TNSR_B200_ERR_UNSUPPORTED;
     const float scale_log2 = (1.0f / sqrtf((float)head_dim)) * 1.4426950408889634f;
     launch_kernel(attention_generic_kernel, dim3((unsigned)ceil_div64(total, 4)), dim3(128), 0, stream, q, k_cache, v_cache, out,
-                  (uint32_t)total, chunk, position, d_position, capacity, heads, head_dim, scale_log2);
+                  (uint32_t)total, chunk, position, d_position, capacity, heads, head_dim, scale_log2, paging ? *paging : KvPaging());
     count_launch();
     return check_launch("attention_generic");
 }
@@ -366,6 +367,7 @@ struct DaParams {
     float scale_log2;
     int* d_status;
     uint64_t wait_limit_ns;   // bound of every mbarrier wait (tnsr_b200_set_wait_limit_ns)
+    KvPaging paging;          // page pools instead of per-session slabs (page_rows is a multiple of the stage size)
 };
 
 // HD: head width; LPK = HD / 8 lanes share one (key, head) row slice, each lane
@@ -412,7 +414,6 @@ decode_attention_kernel(DaParams P) {
             for (uint32_t item = item_begin; ok && item < item_end; ++item) {
                 const DaItem it = nxt;
                 if (item + 1 < item_end) nxt = P.items[item + 1];
-                const size_t base = ((size_t)it.session * P.capacity + it.key0) * d;
                 const uint32_t n_stages = (it.nkeys + KS - 1) / KS;
                 for (uint32_t s = 0; s < n_stages; ++s) {
                     if (!da_mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, P.wait_limit_ns)) { ok = false; break; }
@@ -428,8 +429,10 @@ decode_attention_kernel(DaParams P) {
                     meta[stage] = mt;
                     const uint32_t bytes = nk * row_bytes;
                     da_mbar_expect_tx(full_bar + stage, 2 * bytes + (s == 0 ? row_bytes : 0));
-                    da_bulk_load_once(sk, P.kc + base + (size_t)s * KS * d, bytes, full_bar + stage, once);
-                    da_bulk_load_once(sk + k_bytes, P.vc + base + (size_t)s * KS * d, bytes, full_bar + stage, once);
+                    // a stage never straddles pages: key0 and the page size are multiples of the stage size
+                    const size_t base = kv_row(P.paging, it.session, it.key0 + s * KS, P.capacity) * d;
+                    da_bulk_load_once(sk, P.kc + base, bytes, full_bar + stage, once);
+                    da_bulk_load_once(sk + k_bytes, P.vc + base, bytes, full_bar + stage, once);
                     if (s == 0) da_bulk_load(sk + 2 * k_bytes, P.q + (size_t)it.session * d, row_bytes, full_bar + stage);
                     if (++stage == P.stages) { stage = 0; phase ^= 1; }
                 }
@@ -659,7 +662,8 @@ static int da_sm_count() {
 int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v_cache, const uint32_t* d_lengths,
                                const uint32_t* d_position, uint32_t extra, bf16* out, void* workspace,
                                uint64_t workspace_bytes, uint32_t batch, uint32_t capacity, uint32_t heads,
-                               uint32_t head_dim, bool plan, int* d_status, cudaStream_t stream, bool lean) {
+                               uint32_t head_dim, bool plan, int* d_status, cudaStream_t stream, bool lean,
+                               const KvPaging* paging) {
     if (batch == 0) return TNSR_B200_OK;
     if (!decode_attention_supported(heads, head_dim)) {
         set_thread_error("decode attention: head_dim must be 32, 64 or 128 and heads <= 32");
@@ -727,6 +731,13 @@ int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v
     P.scale_log2 = (1.0f / sqrtf((float)head_dim)) * 1.4426950408889634f;
     P.d_status = d_status;
     P.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
+    if (paging && paging->table) {
+        if (paging->page_rows == 0 || paging->page_rows % DA_KS != 0) {
+            set_thread_error("decode attention: the page size must be a multiple of 16 rows");
+            return TNSR_B200_ERR_INVALID_ARGUMENT;
+        }
+        P.paging = *paging;
+    }
     const uint32_t threads = (consumers + 1) * 32;
     if (lean) {
         if (hpw == 1) {

@@ -129,6 +129,21 @@ enum GemmMode : int {
     GEMM_SWIGLU = 2,  // n = 2*f packed in blocks of 16: out[m, f] bf16 = silu(gate) * up
     GEMM_ARGMAX = 3   // no matrix leaves the kernel: per (row, column tile) the greedy candidate (key, index)
 };
+// Paged K/V: a cache tensor is a pool [pages, page_rows, d] shared by all sessions; logical row r of session s lives
+// in page table[s * pages_per_session + r / page_rows] at row r % page_rows.  table == nullptr: the contiguous
+// [sessions, capacity, d] layout of the reference.
+struct KvPaging {
+    const uint32_t* table = nullptr;
+    uint32_t page_rows = 0, pages_per_session = 0;
+};
+#ifdef __CUDACC__
+// Physical row of logical row `r` of session `s` (contiguous layout: s * capacity + r).
+__device__ __forceinline__ size_t kv_row(const KvPaging& pg, uint32_t s, uint32_t r, uint32_t capacity) {
+    if (!pg.table) return (size_t)s * capacity + r;
+    return (size_t)pg.table[(size_t)s * pg.pages_per_session + r / pg.page_rows] * pg.page_rows + r % pg.page_rows;
+}
+#endif
+
 struct GemmQkvTargets {
     bf16* q = nullptr;        // [m, d]
     bf16* k_cache = nullptr;  // [sessions, capacity, d]
@@ -137,6 +152,7 @@ struct GemmQkvTargets {
     const uint32_t* d_position = nullptr;  // device scalar: first new row
     uint32_t position = 0;                 // used when d_position == nullptr
     uint32_t position_stride = 0;          // 1: d_position is an array with one entry per session (ragged batches)
+    KvPaging paging;                       // paged caches: k_cache / v_cache are page pools
 };
 int launch_gemm_bf16(const bf16* a, const bf16* bt, void* out, uint32_t ldc, uint32_t m, uint32_t n,
                      uint32_t k, GemmMode mode, const GemmEpilogue& ep, const GemmQkvTargets* qkv,
@@ -182,7 +198,8 @@ int launch_swiglu_strict(const float* gate, const float* up, float* out, size_t 
 int launch_decode_attention_ex(const bf16* q, const bf16* k_cache, const bf16* v_cache, const uint32_t* d_lengths,
                                const uint32_t* d_position, uint32_t extra, bf16* out, void* workspace,
                                uint64_t workspace_bytes, uint32_t batch, uint32_t capacity, uint32_t heads,
-                               uint32_t head_dim, bool plan, int* d_status, cudaStream_t stream, bool lean = false);
+                               uint32_t head_dim, bool plan, int* d_status, cudaStream_t stream, bool lean = false,
+                               const KvPaging* paging = nullptr);
 int launch_pack_gate_up(const bf16* wg, const bf16* wu, const float* bg, const float* bu, bf16* w_out,
                         float* b_out, uint32_t d, uint32_t f, cudaStream_t stream);
 int launch_fill_u32(uint32_t* p, uint32_t value, uint32_t n, cudaStream_t stream);
@@ -199,7 +216,7 @@ int launch_attention_strict(const float* q, const void* k_cache, const void* v_c
 int launch_attention_generic(const bf16* q, const bf16* k_cache, const bf16* v_cache, bf16* out,
                              uint32_t sessions, uint32_t chunk, uint32_t position,
                              const uint32_t* d_position, uint32_t capacity, uint32_t heads,
-                             uint32_t head_dim, cudaStream_t stream);
+                             uint32_t head_dim, cudaStream_t stream, const KvPaging* paging = nullptr);
 
 // Split-KV decode attention (one query per session/head) with per-session lengths.
 uint64_t decode_attention_workspace_bytes(uint32_t batch, uint32_t capacity, uint32_t heads,

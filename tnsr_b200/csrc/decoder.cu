@@ -42,6 +42,8 @@ using namespace tb;
 
 namespace {
 
+constexpr uint32_t kNoPage = 0xffffffffu;
+
 struct Buffer {
     void* ptr = nullptr;
     size_t bytes = 0;
@@ -108,6 +110,15 @@ struct tnsr_b200_decoder {
     cudaStream_t side_stream[3] = {nullptr, nullptr, nullptr};   // forked from and joined to `stream` by events
     cudaEvent_t ev_fork = nullptr, ev_join[3] = {nullptr, nullptr, nullptr};
     uint32_t parts = 1;
+    // paged K/V: every cache tensor is a pool [pool_pages, page_rows, d]; h_table[s * pps + i] is the pool page of
+    // session s's i-th page, kNoPage while unassigned (the device copy is refreshed before the step that needs it)
+    bool paged = false;
+    uint32_t page_rows = 0, pool_pages = 0, pps = 0;
+    std::vector<uint32_t> h_table_shadow;   // the table as the host knows it
+    std::vector<uint32_t> free_pages;       // stack of unassigned pool pages
+    uint32_t* h_table = nullptr;            // pinned copy used for the upload
+    uint32_t* d_table = nullptr;
+    bool table_dirty = false;
     // next-token sampling instead of the greedy pick (temperature <= 0: greedy)
     float sample_temperature = 0.0f;
     uint32_t sample_top_k = 0;
@@ -248,7 +259,8 @@ int allocate_weights(tnsr_b200_decoder* dec) {
     if ((rc = dev_alloc(dec, (void**)&dec->fnw, d * 4, true))) return rc;
     if ((rc = dev_alloc(dec, (void**)&dec->fnb, d * 4, true))) return rc;
     dec->layers.resize(c.num_layers);
-    const size_t cache_bytes = (size_t)c.batch * c.capacity * d * kv_elt(dec);
+    const size_t cache_bytes = dec->paged ? (size_t)dec->pool_pages * dec->page_rows * d * kv_elt(dec)
+                                          : (size_t)c.batch * c.capacity * d * kv_elt(dec);
     for (Layer& L : dec->layers) {
         if (dec->bf16_path) {
             if ((rc = dev_alloc(dec, (void**)&L.wqkv, 3 * d * d * 2, true))) return rc;
@@ -334,6 +346,53 @@ int ensure_rows(tnsr_b200_decoder* dec, uint32_t rows, uint32_t logit_rows) {
     return TNSR_B200_OK;
 }
 
+// ---- paged K/V bookkeeping -------------------------------------------------------
+// Makes sure session s owns pages for rows [0, rows_needed).  Pages are taken in one go per step: if the pool cannot
+// cover the whole request nothing is assigned.
+int reserve_pages(tnsr_b200_decoder* dec, const uint32_t* rows_needed /* [batch] */) {
+    if (!dec->paged) return TNSR_B200_OK;
+    const uint32_t B = dec->cfg.batch, pps = dec->pps;
+    uint64_t want = 0;
+    for (uint32_t s = 0; s < B; ++s) {
+        const uint32_t pages = (rows_needed[s] + dec->page_rows - 1) / dec->page_rows;
+        for (uint32_t i = 0; i < pages && i < pps; ++i)
+            if (dec->h_table_shadow[(size_t)s * pps + i] == kNoPage) ++want;
+    }
+    if (want > dec->free_pages.size()) return fail(dec, TNSR_B200_ERR_CAPACITY, "K/V page pool exhausted");
+    for (uint32_t s = 0; s < B; ++s) {
+        const uint32_t pages = (rows_needed[s] + dec->page_rows - 1) / dec->page_rows;
+        for (uint32_t i = 0; i < pages && i < pps; ++i) {
+            uint32_t& slot = dec->h_table_shadow[(size_t)s * pps + i];
+            if (slot == kNoPage) {
+                slot = dec->free_pages.back();
+                dec->free_pages.pop_back();
+                dec->table_dirty = true;
+            }
+        }
+    }
+    return TNSR_B200_OK;
+}
+
+// Queues the upload of the page table if it changed.  Unassigned entries go up as page 0: they are never followed,
+// because no kernel touches a row its session does not hold yet.
+int upload_page_table(tnsr_b200_decoder* dec) {
+    if (!dec->paged || !dec->table_dirty) return TNSR_B200_OK;
+    // the pinned copy may still be the source of a queued upload
+    CU(dec, cudaStreamSynchronize(dec->stream));
+    for (size_t i = 0; i < dec->h_table_shadow.size(); ++i)
+        dec->h_table[i] = dec->h_table_shadow[i] == kNoPage ? 0u : dec->h_table_shadow[i];
+    CU(dec, cudaMemcpyAsync(dec->d_table, dec->h_table, dec->h_table_shadow.size() * 4, cudaMemcpyHostToDevice, dec->stream));
+    dec->table_dirty = false;
+    return TNSR_B200_OK;
+}
+
+int reserve_uniform(tnsr_b200_decoder* dec, uint32_t rows_needed) {
+    if (!dec->paged) return TNSR_B200_OK;
+    std::vector<uint32_t> need(dec->cfg.batch, rows_needed);
+    int rc = reserve_pages(dec, need.data());
+    return rc ? rc : upload_page_table(dec);
+}
+
 // ---- one step on the strict f32 path -----------------------------------------
 // `d_position` (optional): the position as a device scalar, for replay from a captured graph.
 int step_strict(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, uint32_t position,
@@ -403,7 +462,9 @@ int layers_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk
     const uint32_t d = c.embed_dim, f = c.feed_forward_dim, H = c.num_heads, hd = d / H;
     const uint32_t rows = ns * chunk;
     const size_t r0 = (size_t)s0 * chunk;                       // first activation row of the range
-    const size_t cache0 = (size_t)s0 * c.capacity * d;          // first cache element of the range
+    const size_t cache0 = dec->paged ? 0 : (size_t)s0 * c.capacity * d;   // first cache element of the range
+    KvPaging pg;                                                // paged: the pools are shared, the table is per session
+    if (dec->paged) { pg.table = dec->d_table + (size_t)s0 * dec->pps; pg.page_rows = dec->page_rows; pg.pages_per_session = dec->pps; }
     float* h = dec->h + r0 * d;
     bf16* n = (bf16*)dec->n + r0 * d; bf16* q = (bf16*)dec->q + r0 * d; bf16* att = (bf16*)dec->att + r0 * d;
     bf16* ff = (bf16*)dec->ff + r0 * f;
@@ -424,22 +485,23 @@ int layers_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk
         tg.q = q; tg.k_cache = kcache; tg.v_cache = vcache;
         tg.d = d; tg.chunk = chunk; tg.capacity = c.capacity; tg.position = position; tg.d_position = pos_arg;
         tg.position_stride = ragged ? 1u : 0u;
+        tg.paging = pg;
         RUN(dec, launch_gemm_bf16(n, L.wqkv, nullptr, 0, rows, 3 * d, d, GEMM_QKV, eq, &tg, dec->d_status, st));
         if (fast_decode) {
             // every session holds position + 1 keys; the item list is the same for all layers of this step
             if (ragged)   // session b holds d_position[b] + 1 keys
                 RUN(dec, launch_decode_attention_ex(q, kcache, vcache, pos_arg, nullptr, 1, att, ws, dec->attn_ws_bytes, ns,
-                                                    c.capacity, H, hd, !planned, dec->d_status, st, lean));
+                                                    c.capacity, H, hd, !planned, dec->d_status, st, lean, &pg));
             else
                 RUN(dec, launch_decode_attention_ex(q, kcache, vcache, nullptr, d_position, d_position ? 1 : position + 1, att,
                                                     ws, dec->attn_ws_bytes, ns, c.capacity, H, hd, !planned, dec->d_status,
-                                                    st, lean));
+                                                    st, lean, &pg));
             planned = true;
-        } else if (chunk > 1 && prefill_attention_supported(hd) && c.prefill_mode != TNSR_B200_PREFILL_SCALAR) {
+        } else if (chunk > 1 && prefill_attention_supported(hd) && c.prefill_mode != TNSR_B200_PREFILL_SCALAR && !dec->paged) {
             RUN(dec, launch_prefill_attention(q, kcache, vcache, att, ns, chunk, position, d_position, c.capacity, H, hd,
                                               dec->d_status, st));
         } else {
-            RUN(dec, launch_attention_generic(q, kcache, vcache, att, ns, chunk, position, d_position, c.capacity, H, hd, st));
+            RUN(dec, launch_attention_generic(q, kcache, vcache, att, ns, chunk, position, d_position, c.capacity, H, hd, st, &pg));
         }
         GemmEpilogue eo;
         eo.bias = L.bo; eo.residual = h; eo.ldr = d; eo.out_dtype = TNSR_B200_F32;
@@ -635,6 +697,15 @@ int validate_config(const tnsr_b200_config* c, std::string& why) {
         return TNSR_B200_ERR_INVALID_ARGUMENT;
     }
     if (c->batch == 0) { why = "decoder batch size must be non-zero"; return TNSR_B200_ERR_INVALID_ARGUMENT; }
+    if (c->kv_page_rows) {
+        if (c->weight_dtype != TNSR_B200_BF16 || c->kv_page_rows % 16 != 0 || c->capacity % c->kv_page_rows != 0) {
+            why = "paged K/V needs bf16 weights and a page size that is a multiple of 16 rows and divides the capacity";
+            return TNSR_B200_ERR_INVALID_ARGUMENT;
+        }
+    } else if (c->kv_pool_pages) {
+        why = "kv_pool_pages without kv_page_rows";
+        return TNSR_B200_ERR_INVALID_ARGUMENT;
+    }
     if (c->capacity == 0 || c->capacity > c->max_sequence_length) {
         why = "decoder capacity must fit the model context";
         return TNSR_B200_ERR_INVALID_ARGUMENT;
@@ -724,6 +795,19 @@ int tnsr_b200_decoder_create(const tnsr_b200_config* config, tnsr_b200_decoder**
     cudaError_t e = cudaStreamCreateWithFlags(&dec->stream, cudaStreamNonBlocking);
     if (e != cudaSuccess) return bail(cuda_fail(dec, e, "cudaStreamCreate"));
     describe_params(dec);
+    if (config->kv_page_rows) {
+        dec->paged = true;
+        dec->page_rows = config->kv_page_rows;
+        dec->pps = config->capacity / config->kv_page_rows;
+        const uint64_t worst = (uint64_t)config->batch * dec->pps;
+        dec->pool_pages = config->kv_pool_pages ? config->kv_pool_pages : (uint32_t)std::min<uint64_t>(worst, 0xffffffffull);
+        if (dec->pool_pages > worst) dec->pool_pages = (uint32_t)worst;
+        dec->h_table_shadow.assign((size_t)config->batch * dec->pps, kNoPage);
+        for (uint32_t p = dec->pool_pages; p > 0; --p) dec->free_pages.push_back(p - 1);
+        if ((rc = dev_alloc(dec, (void**)&dec->d_table, dec->h_table_shadow.size() * 4, true))) return bail(rc);
+        if (cudaMallocHost((void**)&dec->h_table, dec->h_table_shadow.size() * 4) != cudaSuccess)
+            return bail(cuda_fail(dec, cudaGetLastError(), "cudaMallocHost"));
+    }
     if ((rc = allocate_weights(dec))) return bail(rc);
     const uint64_t d = config->embed_dim;
     if ((rc = dev_alloc(dec, (void**)&dec->hl, (size_t)config->batch * d * 4, false))) return bail(rc);
@@ -780,6 +864,7 @@ void tnsr_b200_decoder_destroy(tnsr_b200_decoder* dec) {
     if (dec->h_positions) cudaFreeHost(dec->h_positions);
     if (dec->h_status) cudaFreeHost(dec->h_status);
     if (dec->h_stage) cudaFreeHost(dec->h_stage);
+    if (dec->h_table) cudaFreeHost(dec->h_table);
     drop_graphs(dec);
     for (int i = 0; i < 3; ++i) {
         if (dec->side_stream[i]) { cudaStreamSynchronize(dec->side_stream[i]); cudaStreamDestroy(dec->side_stream[i]); }
@@ -899,7 +984,14 @@ int tnsr_b200_decoder_upload(tnsr_b200_decoder* dec, uint32_t index, const float
 int tnsr_b200_decoder_reset(tnsr_b200_decoder* dec) {
     if (!dec) return fail(nullptr, TNSR_B200_ERR_INVALID_ARGUMENT, "null decoder");
     CU(dec, cudaSetDevice(dec->cfg.device));
-    const size_t cache_bytes = (size_t)dec->cfg.batch * dec->cfg.capacity * dec->cfg.embed_dim * kv_elt(dec);
+    const size_t cache_bytes = dec->paged ? (size_t)dec->pool_pages * dec->page_rows * dec->cfg.embed_dim * kv_elt(dec)
+                                          : (size_t)dec->cfg.batch * dec->cfg.capacity * dec->cfg.embed_dim * kv_elt(dec);
+    if (dec->paged) {
+        dec->free_pages.clear();
+        for (uint32_t p = dec->pool_pages; p > 0; --p) dec->free_pages.push_back(p - 1);
+        std::fill(dec->h_table_shadow.begin(), dec->h_table_shadow.end(), kNoPage);
+        dec->table_dirty = true;
+    }
     for (Layer& L : dec->layers) {
         CU(dec, cudaMemsetAsync(L.kcache, 0, cache_bytes, dec->stream));
         CU(dec, cudaMemsetAsync(L.vcache, 0, cache_bytes, dec->stream));
@@ -943,6 +1035,7 @@ int tnsr_b200_decoder_decode(tnsr_b200_decoder* dec, const uint32_t* tokens, uin
     CU(dec, cudaSetDevice(c.device));
     const uint32_t logit_rows = c.logits_mode == TNSR_B200_LOGITS_ALL ? rows : c.batch;
     if ((rc = ensure_rows(dec, rows, logit_rows))) return rc;
+    if ((rc = reserve_uniform(dec, position + chunk))) return rc;
     dec->failed = true;  // poisoned until the step has completed (src/nn/kv_cache.rs:331)
     std::memcpy(dec->h_tokens, tokens, (size_t)rows * 4);
     CU(dec, cudaMemcpyAsync(dec->d_tokens, dec->h_tokens, (size_t)rows * 4, cudaMemcpyHostToDevice, dec->stream));
@@ -984,6 +1077,12 @@ int tnsr_b200_decoder_decode_ragged(tnsr_b200_decoder* dec, const uint32_t* toke
     if (!dec->d_positions) {
         if ((rc = dev_alloc(dec, (void**)&dec->d_positions, (size_t)c.batch * 4, true))) return rc;
         CU(dec, cudaMallocHost((void**)&dec->h_positions, (size_t)c.batch * 4));
+    }
+    if (dec->paged) {
+        std::vector<uint32_t> need(c.batch);
+        for (uint32_t b = 0; b < c.batch; ++b) need[b] = positions[b] + 1;
+        if ((rc = reserve_pages(dec, need.data()))) return rc;
+        if ((rc = upload_page_table(dec))) return rc;
     }
     dec->failed = true;
     std::memcpy(dec->h_tokens, tokens, (size_t)c.batch * 4);
@@ -1027,6 +1126,7 @@ int tnsr_b200_decoder_decode_device(tnsr_b200_decoder* dec, const uint32_t* d_to
     const uint32_t rows = c.batch * chunk;
     const uint32_t logit_rows = c.logits_mode == TNSR_B200_LOGITS_ALL ? rows : c.batch;
     if ((rc = ensure_rows(dec, rows, logit_rows))) return rc;
+    if ((rc = reserve_uniform(dec, position + chunk))) return rc;
     return run_step(dec, d_tokens, chunk, position, d_argmax_out);
 }
 
@@ -1042,6 +1142,25 @@ int tnsr_b200_decoder_set_sampler(tnsr_b200_decoder* dec, float temperature, uin
     dec->sample_seed = seed;
     return TNSR_B200_OK;
 }
+
+int tnsr_b200_decoder_release(tnsr_b200_decoder* dec, uint32_t session) {
+    if (!dec) return fail(nullptr, TNSR_B200_ERR_INVALID_ARGUMENT, "null decoder");
+    if (!dec->paged) return fail(dec, TNSR_B200_ERR_UNSUPPORTED, "release applies to paged handles only");
+    if (session >= dec->cfg.batch) return fail(dec, TNSR_B200_ERR_INVALID_ARGUMENT, "session index out of range");
+    CU(dec, cudaSetDevice(dec->cfg.device));
+    CU(dec, cudaStreamSynchronize(dec->stream));   // queued steps may still read the pages
+    for (uint32_t i = 0; i < dec->pps; ++i) {
+        uint32_t& slot = dec->h_table_shadow[(size_t)session * dec->pps + i];
+        if (slot != kNoPage) {
+            dec->free_pages.push_back(slot);
+            slot = kNoPage;
+            dec->table_dirty = true;
+        }
+    }
+    return TNSR_B200_OK;
+}
+
+uint32_t tnsr_b200_decoder_free_pages(const tnsr_b200_decoder* dec) { return dec && dec->paged ? (uint32_t)dec->free_pages.size() : 0; }
 
 int tnsr_b200_decoder_synchronize(tnsr_b200_decoder* dec) {
     if (!dec) return fail(nullptr, TNSR_B200_ERR_INVALID_ARGUMENT, "null decoder");
@@ -1088,6 +1207,33 @@ int tnsr_b200_decoder_read_cache(tnsr_b200_decoder* dec, uint32_t index, float* 
     const uint64_t elems = (uint64_t)dec->cfg.batch * dec->cfg.capacity * dec->cfg.embed_dim;
     Layer& L = dec->layers[index / 2];
     const void* src = (index & 1) ? L.vcache : L.kcache;
+    if (dec->paged) {
+        // the pool as f32 on the host, then every session's pages in logical order (rows of unassigned pages are zero)
+        const uint64_t d = dec->cfg.embed_dim, page_elems = (uint64_t)dec->page_rows * d, pool_elems = dec->pool_pages * page_elems;
+        float* tmp = nullptr;
+        int rc = dev_alloc(dec, (void**)&tmp, pool_elems * 4, false);
+        if (rc) return rc;
+        std::vector<float> pool(pool_elems);
+        rc = launch_bf16_to_f32((const bf16*)src, tmp, pool_elems, dec->stream);
+        if (rc == TNSR_B200_OK) {
+            cudaError_t e = cudaMemcpyAsync(pool.data(), tmp, pool_elems * 4, cudaMemcpyDeviceToHost, dec->stream);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(dec->stream);
+            if (e != cudaSuccess) rc = cuda_fail(dec, e, "read_cache copy");
+        } else {
+            dec->error = thread_error();
+        }
+        cudaStreamSynchronize(dec->stream);
+        dev_free(dec, tmp);
+        if (rc) return rc;
+        for (uint32_t s = 0; s < dec->cfg.batch; ++s)
+            for (uint32_t i = 0; i < dec->pps; ++i) {
+                float* dst = host_out + ((uint64_t)s * dec->cfg.capacity + (uint64_t)i * dec->page_rows) * d;
+                const uint32_t page = dec->h_table_shadow[(size_t)s * dec->pps + i];
+                if (page == kNoPage) std::memset(dst, 0, page_elems * 4);
+                else std::memcpy(dst, pool.data() + page * page_elems, page_elems * 4);
+            }
+        return TNSR_B200_OK;
+    }
     if (!dec->kv_bf16) {
         CU(dec, cudaMemcpyAsync(host_out, src, elems * 4, cudaMemcpyDeviceToHost, dec->stream));
         CU(dec, cudaStreamSynchronize(dec->stream));
@@ -1116,6 +1262,29 @@ int tnsr_b200_decoder_write_cache(tnsr_b200_decoder* dec, uint32_t index, const 
     const uint64_t elems = (uint64_t)dec->cfg.batch * dec->cfg.capacity * dec->cfg.embed_dim;
     Layer& L = dec->layers[index / 2];
     void* dst = (index & 1) ? L.vcache : L.kcache;
+    if (dec->paged) {
+        // writing whole tensors needs every page of every session; rows travel in pool order
+        int rc = reserve_uniform(dec, dec->cfg.capacity);
+        if (rc) return rc;
+        const uint64_t d = dec->cfg.embed_dim, page_elems = (uint64_t)dec->page_rows * d, pool_elems = dec->pool_pages * page_elems;
+        std::vector<float> pool(pool_elems, 0.0f);
+        for (uint32_t s = 0; s < dec->cfg.batch; ++s)
+            for (uint32_t i = 0; i < dec->pps; ++i)
+                std::memcpy(pool.data() + dec->h_table_shadow[(size_t)s * dec->pps + i] * page_elems,
+                            host_in + ((uint64_t)s * dec->cfg.capacity + (uint64_t)i * dec->page_rows) * d, page_elems * 4);
+        float* tmp = nullptr;
+        rc = dev_alloc(dec, (void**)&tmp, pool_elems * 4, false);
+        if (rc) return rc;
+        cudaError_t e = cudaMemcpyAsync(tmp, pool.data(), pool_elems * 4, cudaMemcpyHostToDevice, dec->stream);
+        if (e != cudaSuccess) rc = cuda_fail(dec, e, "write_cache copy");
+        if (rc == TNSR_B200_OK) {
+            rc = launch_f32_to_bf16(tmp, (bf16*)dst, pool_elems, dec->stream);
+            if (rc) dec->error = thread_error();
+        }
+        cudaStreamSynchronize(dec->stream);
+        dev_free(dec, tmp);
+        return rc;
+    }
     if (!dec->kv_bf16) {
         CU(dec, cudaMemcpyAsync(dst, host_in, elems * 4, cudaMemcpyHostToDevice, dec->stream));
         CU(dec, cudaStreamSynchronize(dec->stream));

@@ -62,7 +62,7 @@ __device__ __forceinline__ void store_qkv(const EpiParams& P, uint32_t row, uint
     } else {
         const uint32_t session = row / P.qkv.chunk;
         uint32_t pos = P.qkv.d_position ? P.qkv.d_position[session * P.qkv.position_stride] : P.qkv.position;
-        size_t crow = (size_t)session * P.qkv.capacity + pos + row % P.qkv.chunk;
+        size_t crow = kv_row(P.qkv.paging, session, pos + row % P.qkv.chunk, P.qkv.capacity);
         (which == 1 ? P.qkv.k_cache : P.qkv.v_cache)[crow * d + c] = __float2bfloat16_rn(v);
     }
 }
@@ -459,7 +459,7 @@ __device__ __forceinline__ void epilogue_block(const EpiParams& P, float* stage,
                     if (MODE == GEMM_QKV) {
                         const uint32_t session = row / P.qkv.chunk;
                         const uint32_t p = P.qkv.position_stride ? P.qkv.d_position[session] : pos;   // ragged: one position per session
-                        orow = which == 0 ? row : (size_t)session * P.qkv.capacity + p + row % P.qkv.chunk;
+                        orow = which == 0 ? row : kv_row(P.qkv.paging, session, p + row % P.qkv.chunk, P.qkv.capacity);
                     }
                     else orow = map_out_row(P.ep, row);
                     *reinterpret_cast<uint4*>(base + orow * ld + cbase + c8) =
@@ -882,7 +882,8 @@ static int launch_gemm_impl(const bf16* a, const bf16* bt, void* out, uint32_t l
             okm = bf16_map(&mo[0], out, n, m, ldc, 32, CU_TENSOR_MAP_SWIZZLE_64B);
         } else if (mode == GEMM_SWIGLU) {
             okm = bf16_map(&mo[0], out, n / 2, m, ldc, 16, CU_TENSOR_MAP_SWIZZLE_32B);
-        } else if (qkv && qkv->chunk % 32 == 0 && qkv->d % 32 == 0 && qkv->position_stride == 0 && m % qkv->chunk == 0) {
+        } else if (qkv && qkv->chunk % 32 == 0 && qkv->d % 32 == 0 && qkv->position_stride == 0 && m % qkv->chunk == 0 &&
+                   !qkv->paging.table) {
             okm = bf16_map(&mo[0], qkv->q, qkv->d, m, qkv->d, 32, CU_TENSOR_MAP_SWIZZLE_64B);
             for (int which = 1; okm && which <= 2; ++which) {
                 void* base = which == 1 ? (void*)qkv->k_cache : (void*)qkv->v_cache;

@@ -13,7 +13,7 @@ from ._native import ACT, DTYPE, LOGITS, PREFILL, Config, NativeError, check, li
 
 class B200Session:
     def __init__(self, config, batch: int, capacity: int, options=None, device: int = 0,
-                 logits_mode: str = "all", step_parts: int = 0):
+                 logits_mode: str = "all", step_parts: int = 0, kv_page_rows: int = 0, kv_pool_pages: int = 0):
         from .nn import GptAttentionPrecision, TnsrError
         weight_dtype = getattr(config, "weight_dtype", "f32")
         kv = "bf16" if weight_dtype == "bf16" else "f32"
@@ -23,7 +23,8 @@ class B200Session:
                           config.feed_forward_dim, config.num_layers, config.layer_norm_epsilon,
                           ACT[getattr(config, "activation", "relu")], DTYPE[weight_dtype], DTYPE[kv], batch,
                           capacity, device, LOGITS[logits_mode],
-                          PREFILL[options.prefill.value] if options is not None else PREFILL["auto"], step_parts)
+                          PREFILL[options.prefill.value] if options is not None else PREFILL["auto"], step_parts,
+                          kv_page_rows, kv_pool_pages)
         self.handle = C.c_void_p()
         self.batch, self.capacity, self.vocab = batch, capacity, config.vocab_size
         self.embed_dim = config.embed_dim
@@ -99,6 +100,13 @@ class B200Session:
     def set_sampler(self, temperature: float, top_k: int, seed: int) -> None:
         """Greedy ids become top-k / temperature samples (temperature <= 0: back to greedy)."""
         self._check(lib().tnsr_b200_decoder_set_sampler(self.handle, float(temperature), int(top_k), int(seed)))
+
+    def release(self, session: int) -> None:
+        """Paged handles: give the pages of one session back to the pool."""
+        self._check(lib().tnsr_b200_decoder_release(self.handle, int(session)))
+
+    def free_pages(self) -> int:
+        return int(lib().tnsr_b200_decoder_free_pages(self.handle))
 
     def synchronize(self) -> None:
         self._check(lib().tnsr_b200_decoder_synchronize(self.handle))
