@@ -129,6 +129,12 @@ typedef struct tnsr_b200_config {
      * mode. */
     uint32_t kv_page_rows;
     uint32_t kv_pool_pages;
+    /* Single-token steps of at most 64 sessions (bf16 weights, SwiGLU, width <=
+     * 1024): 0 = everything between two attention scans runs as one persistent
+     * kernel with grid-wide barriers (the default), 1 = one kernel per operator
+     * as at larger batches.  No reference counterpart; the two differ by rounding
+     * only. */
+    uint32_t small_batch_mode;
 } tnsr_b200_config;
 
 typedef struct tnsr_b200_decoder tnsr_b200_decoder;

@@ -683,3 +683,45 @@ def test_paged_kv_pool_smaller_than_the_worst_case():
     s.close()
     with pytest.raises(Exception):
         B200Session(cfg, 4, 64, kv_page_rows=24)                     # not a multiple of 16
+
+
+@pytest.mark.parametrize("batch", [3, 24, 57])
+def test_small_batch_fused_layer_kernel_matches_the_operator_by_operator_step(batch):
+    """Up to 64 sessions a single-token step runs each layer's projections, LayerNorms and SwiGLU as one persistent
+    kernel with grid barriers (warp-level MMA, weights streamed once); `small_batch_mode=1` keeps the operator-by-operator
+    kernels.  Same arithmetic up to summation order: logits within the bf16-path tolerance of each other and of the CPU
+    checker, K/V rows equal to bf16 resolution; 3, 24 and 57 sessions take the 16-, 32- and 64-row forms; ragged and paged
+    steps go through the same kernel."""
+    from oracle import oracle
+    cfg = GptConfig(vocab_size=640, max_sequence_length=64, embed_dim=256, num_heads=4, feed_forward_dim=1088,
+                    num_layers=3, layer_norm_epsilon=1e-5, activation="swiglu", weight_dtype="bf16")
+    arrays = normal_model_arrays(cfg, seed=91, std=0.05, bias_std=0.02)
+    ids = np.random.default_rng(92).integers(0, cfg.vocab_size, size=(batch, 20)).astype(np.uint32)
+
+    def run(**kw):
+        s = B200Session(cfg, batch, 48, logits_mode="last", **kw)
+        for i, a in enumerate(arrays):
+            s.refresh(i, a)
+        out = [s.decode_full(ids[:, :12], 0)[0]]
+        for t in range(12, 18):
+            out.append(s.decode_full(ids[:, t:t + 1], t)[0])
+        positions = (np.arange(batch, dtype=np.uint32) % 5) + 14
+        out.append(s.decode_ragged(ids[:, 18], positions)[0])
+        caches = [s.read_cache(i) for i in (0, 1, 2 * cfg.num_layers - 1)]
+        s.close()
+        return np.stack([o.reshape(batch, -1) for o in out]), caches
+
+    fused, fused_caches = run()
+    classic, classic_caches = run(small_batch_mode=1)
+    assert np.all(np.isfinite(fused))
+    assert rel_err(fused, classic) <= 1e-2
+    for a, b in zip(fused_caches, classic_caches):
+        assert np.max(np.abs(a - b)) <= max(1.0, float(np.max(np.abs(b)))) / 64
+    paged, _ = run(kv_page_rows=16)                  # the prefill takes another attention kernel when paged
+    assert rel_err(paged, fused) <= 1e-2
+    ref = oracle.OracleModel(cfg.vocab_size, cfg.max_sequence_length, cfg.embed_dim, cfg.num_heads, cfg.feed_forward_dim,
+                             cfg.num_layers, cfg.layer_norm_epsilon, "swiglu")
+    ref.set_params([oracle.bf16_round_np(a) if a.ndim == 2 else a for a in arrays])
+    want = ref.forward(ids[:, :18])
+    for t in range(12, 18):
+        assert rel_err(fused[t - 11], want[:, t]) <= 2e-2

@@ -30,7 +30,7 @@ class Config(C.Structure):
         ("layer_norm_epsilon", C.c_float), ("activation", C.c_uint32), ("weight_dtype", C.c_uint32),
         ("kv_dtype", C.c_uint32), ("batch", C.c_uint32), ("capacity", C.c_uint32), ("device", C.c_int32),
         ("logits_mode", C.c_uint32), ("prefill_mode", C.c_uint32), ("step_parts", C.c_uint32),
-        ("kv_page_rows", C.c_uint32), ("kv_pool_pages", C.c_uint32),
+        ("kv_page_rows", C.c_uint32), ("kv_pool_pages", C.c_uint32), ("small_batch_mode", C.c_uint32),
     ]
 
 

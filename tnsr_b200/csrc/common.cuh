@@ -205,6 +205,36 @@ int launch_pack_gate_up(const bf16* wg, const bf16* wu, const float* bg, const f
 int launch_fill_u32(uint32_t* p, uint32_t value, uint32_t n, cudaStream_t stream);
 int launch_add_u32(uint32_t* p, uint32_t delta, cudaStream_t stream);
 
+// Everything between two attention scans of a single-token step at small batch (<= 64 sessions) as one persistent
+// kernel with grid-wide barriers (decode_tail.cu): [output projection + residual] -> [LayerNorm, gate/up, SwiGLU] ->
+// [down projection + residual] -> [next layer's LayerNorm, QKV projection, K/V cache rows].  run_o / run_ffn / run_qkv
+// select the parts; weights are the session's K-major bf16 matrices (gate/up packed in blocks of 16).
+struct DecodeTailArgs {
+    bool run_o = false, run_ffn = false, run_qkv = false;
+    uint32_t rows = 0, d = 0, f = 0;
+    float eps = 0.0f;
+    float* h = nullptr;
+    const bf16* att = nullptr;
+    bf16* ff = nullptr;
+    bf16* q = nullptr;
+    const bf16* wo = nullptr; const float* bo = nullptr;
+    const float* ln2w = nullptr; const float* ln2b = nullptr;
+    const bf16* wgu = nullptr; const float* bgu = nullptr;
+    const bf16* wdown = nullptr; const float* bdown = nullptr;
+    const float* ln1w = nullptr; const float* ln1b = nullptr;
+    const bf16* wqkv = nullptr; const float* bqkv = nullptr;
+    bf16* k_cache = nullptr; bf16* v_cache = nullptr;
+    uint32_t capacity = 0;
+    const uint32_t* d_position = nullptr; uint32_t position = 0, position_stride = 0;
+    uint32_t first_session = 0;
+    const KvPaging* paging = nullptr;
+    void* workspace = nullptr;     // decode_tail_workspace_bytes(), zeroed once; every completed launch leaves it zeroed
+    int* d_status = nullptr;
+};
+uint64_t decode_tail_workspace_bytes();
+bool decode_tail_supported(uint32_t rows, uint32_t d, uint32_t f);
+int launch_decode_tail(const DecodeTailArgs& args, cudaStream_t stream);
+
 // Strict f32 attention in the reference's order over a cache that already holds
 // the new rows: q [sessions*chunk, d] f32; caches f32 or bf16 [sessions, capacity, d].
 int launch_attention_strict(const float* q, const void* k_cache, const void* v_cache, float* out,

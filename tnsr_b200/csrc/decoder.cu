@@ -110,6 +110,9 @@ struct tnsr_b200_decoder {
     cudaStream_t side_stream[3] = {nullptr, nullptr, nullptr};   // forked from and joined to `stream` by events
     cudaEvent_t ev_fork = nullptr, ev_join[3] = {nullptr, nullptr, nullptr};
     uint32_t parts = 1;
+    // small batches: one persistent kernel per layer between the attention scans (decode_tail.cu); its barrier words
+    void* tail_ws = nullptr;
+    bool use_tail = true;
     // paged K/V: every cache tensor is a pool [pool_pages, page_rows, d]; h_table[s * pps + i] is the pool page of
     // session s's i-th page, kNoPage while unassigned (the device copy is refreshed before the step that needs it)
     bool paged = false;
@@ -475,6 +478,47 @@ int layers_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk
     const bool fast_decode = chunk == 1 && ws && decode_attention_supported(H, hd);
     if (ragged && !fast_decode) return fail(dec, TNSR_B200_ERR_UNSUPPORTED, "ragged decode needs the split-KV attention kernel (head width 32, 64 or 128)");
     bool planned = false;
+    // Small batch: everything between two attention scans is one persistent kernel (decode_tail.cu).
+    if (fast_decode && !lean && dec->fused_gu && dec->tail_ws && dec->use_tail && decode_tail_supported(ns, d, f)) {
+        const size_t layers = dec->layers.size();
+        auto tail = [&](size_t prev, bool with_prev, bool with_next) -> int {
+            DecodeTailArgs a;
+            a.rows = ns; a.d = d; a.f = f; a.eps = c.layer_norm_epsilon;
+            a.h = h; a.att = att; a.ff = ff; a.q = q;
+            a.workspace = dec->tail_ws; a.d_status = dec->d_status;
+            if (with_prev) {
+                const Layer& L = dec->layers[prev];
+                a.run_o = a.run_ffn = true;
+                a.wo = (const bf16*)L.wo; a.bo = L.bo; a.ln2w = L.ln2w; a.ln2b = L.ln2b; a.wgu = L.wgu; a.bgu = L.bgu;
+                a.wdown = (const bf16*)L.w_out; a.bdown = L.b_out;
+            }
+            if (with_next) {
+                const Layer& N = dec->layers[with_prev ? prev + 1 : prev];
+                a.run_qkv = true;
+                a.ln1w = N.ln1w; a.ln1b = N.ln1b; a.wqkv = N.wqkv; a.bqkv = N.bqkv;
+                a.k_cache = (bf16*)N.kcache + cache0; a.v_cache = (bf16*)N.vcache + cache0;
+                a.capacity = c.capacity; a.d_position = pos_arg; a.position = position; a.position_stride = ragged ? 1u : 0u;
+                a.paging = &pg;
+            }
+            return launch_decode_tail(a, st);
+        };
+        RUN(dec, tail(0, false, true));
+        for (size_t l = 0; l < layers; ++l) {
+            Layer& L = dec->layers[l];
+            bf16* kcache = (bf16*)L.kcache + cache0;
+            bf16* vcache = (bf16*)L.vcache + cache0;
+            if (ragged)
+                RUN(dec, launch_decode_attention_ex(q, kcache, vcache, pos_arg, nullptr, 1, att, ws, dec->attn_ws_bytes, ns,
+                                                    c.capacity, H, hd, !planned, dec->d_status, st, false, &pg));
+            else
+                RUN(dec, launch_decode_attention_ex(q, kcache, vcache, nullptr, d_position, d_position ? 1 : position + 1, att,
+                                                    ws, dec->attn_ws_bytes, ns, c.capacity, H, hd, !planned, dec->d_status,
+                                                    st, false, &pg));
+            planned = true;
+            RUN(dec, tail(l, true, l + 1 < layers));
+        }
+        return TNSR_B200_OK;
+    }
     for (Layer& L : dec->layers) {
         bf16* kcache = (bf16*)L.kcache + cache0;
         bf16* vcache = (bf16*)L.vcache + cache0;
@@ -659,7 +703,7 @@ int run_step(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, u
             if (graph) cudaGraphDestroy(graph);
             cudaGetLastError();
             dec->use_graphs = false;  // fall back to direct launches for the rest of this session
-            if (rc != TNSR_B200_OK) return rc;
+            dec->failed = false;      // a launch that capture refuses is not a device failure; a real one shows again below
             return run_step_direct(dec, d_tokens, chunk, position, nullptr, d_argmax_out);
         }
         cudaGraphExec_t exec = nullptr;
@@ -688,7 +732,7 @@ int validate_config(const tnsr_b200_config* c, std::string& why) {
         return TNSR_B200_ERR_INVALID_ARGUMENT;
     }
     if (c->activation > TNSR_B200_ACT_SWIGLU || c->weight_dtype > TNSR_B200_BF16 || c->kv_dtype > TNSR_B200_BF16 ||
-        c->logits_mode > TNSR_B200_LOGITS_NONE || c->prefill_mode > TNSR_B200_PREFILL_SCALAR || c->step_parts > 4) {
+        c->logits_mode > TNSR_B200_LOGITS_NONE || c->prefill_mode > TNSR_B200_PREFILL_SCALAR || c->step_parts > 4 || c->small_batch_mode > 1) {
         why = "invalid enum value in configuration";
         return TNSR_B200_ERR_INVALID_ARGUMENT;
     }
@@ -843,6 +887,10 @@ int tnsr_b200_decoder_create(const tnsr_b200_config* config, tnsr_b200_decoder**
                 return bail(cuda_fail(dec, cudaGetLastError(), "side stream of the divided step"));
         }
         dec->parts = parts;
+        if (config->batch <= 64) {
+            if ((rc = dev_alloc(dec, &dec->tail_ws, decode_tail_workspace_bytes(), true))) return bail(rc);
+            dec->use_tail = config->small_batch_mode == 0;
+        }
     }
     if (dec->bf16_path) {
         dec->host_bqkv.assign((size_t)config->num_layers * 3 * d, 0.0f);
@@ -997,6 +1045,7 @@ int tnsr_b200_decoder_reset(tnsr_b200_decoder* dec) {
         CU(dec, cudaMemsetAsync(L.vcache, 0, cache_bytes, dec->stream));
     }
     CU(dec, cudaMemsetAsync(dec->d_status, 0, 16, dec->stream));
+    if (dec->tail_ws) CU(dec, cudaMemsetAsync(dec->tail_ws, 0, decode_tail_workspace_bytes(), dec->stream));
     CU(dec, cudaStreamSynchronize(dec->stream));
     dec->failed = false;
     return TNSR_B200_OK;

@@ -13,7 +13,8 @@ from ._native import ACT, DTYPE, LOGITS, PREFILL, Config, NativeError, check, li
 
 class B200Session:
     def __init__(self, config, batch: int, capacity: int, options=None, device: int = 0,
-                 logits_mode: str = "all", step_parts: int = 0, kv_page_rows: int = 0, kv_pool_pages: int = 0):
+                 logits_mode: str = "all", step_parts: int = 0, kv_page_rows: int = 0, kv_pool_pages: int = 0,
+                 small_batch_mode: int = 0):
         from .nn import GptAttentionPrecision, TnsrError
         weight_dtype = getattr(config, "weight_dtype", "f32")
         kv = "bf16" if weight_dtype == "bf16" else "f32"
@@ -24,7 +25,7 @@ class B200Session:
                           ACT[getattr(config, "activation", "relu")], DTYPE[weight_dtype], DTYPE[kv], batch,
                           capacity, device, LOGITS[logits_mode],
                           PREFILL[options.prefill.value] if options is not None else PREFILL["auto"], step_parts,
-                          kv_page_rows, kv_pool_pages)
+                          kv_page_rows, kv_pool_pages, small_batch_mode)
         self.handle = C.c_void_p()
         self.batch, self.capacity, self.vocab = batch, capacity, config.vocab_size
         self.embed_dim = config.embed_dim
