@@ -81,6 +81,8 @@ def parse_args():
                          "greedy steps; c1: GEMM sweep; c2: SwiGLU MLP; c3: ragged decode attention -- each with the CPU "
                          "restatement timed beside it (1 GPU)")
     ap.add_argument("--samples", type=int, default=20, help="timed launches per case of the operator workloads")
+    ap.add_argument("--step-parts", type=int, default=0, help="session configuration: parts a single-token step is divided into (0 = automatic)")
+    ap.add_argument("--small-batch-mode", type=int, default=0, help="session configuration: 1 = operator-by-operator step also at <= 64 sessions")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -422,7 +424,8 @@ def measure_decode(args, cfg, sessions, rank, local_rank, world, barrier, reduce
         return args.prefill + step % span
     lib = _native.lib()
     arrays = normal_model_arrays(cfg, seed=5, std=0.02)
-    sess = B200Session(cfg, sessions, capacity, device=local_rank, logits_mode="none")
+    sess = B200Session(cfg, sessions, capacity, device=local_rank, logits_mode="none", step_parts=args.step_parts,
+                       small_batch_mode=args.small_batch_mode)
     for i, a in enumerate(arrays):
         sess.refresh(i, a)
     del arrays

@@ -129,7 +129,7 @@ typedef struct tnsr_b200_config {
      * mode. */
     uint32_t kv_page_rows;
     uint32_t kv_pool_pages;
-    /* Single-token steps of at most 64 sessions (bf16 weights, SwiGLU, width <=
+    /* Single-token steps of at most 32 sessions (bf16 weights, SwiGLU, width <=
      * 1024): 0 = everything between two attention scans runs as one persistent
      * kernel with grid-wide barriers (the default), 1 = one kernel per operator
      * as at larger batches.  No reference counterpart; the two differ by rounding

@@ -685,13 +685,13 @@ def test_paged_kv_pool_smaller_than_the_worst_case():
         B200Session(cfg, 4, 64, kv_page_rows=24)                     # not a multiple of 16
 
 
-@pytest.mark.parametrize("batch", [3, 24, 57])
+@pytest.mark.parametrize("batch", [3, 16, 29])
 def test_small_batch_fused_layer_kernel_matches_the_operator_by_operator_step(batch):
-    """Up to 64 sessions a single-token step runs each layer's projections, LayerNorms and SwiGLU as one persistent
+    """Up to 32 sessions a single-token step runs each layer's projections, LayerNorms and SwiGLU as one persistent
     kernel with grid barriers (warp-level MMA, weights streamed once); `small_batch_mode=1` keeps the operator-by-operator
     kernels.  Same arithmetic up to summation order: logits within the bf16-path tolerance of each other and of the CPU
-    checker, K/V rows equal to bf16 resolution; 3, 24 and 57 sessions take the 16-, 32- and 64-row forms; ragged and paged
-    steps go through the same kernel."""
+    checker, K/V rows equal to bf16 resolution; 3 and 16 sessions take the 16-row form, 29 the 32-row form; ragged and
+    paged steps go through the same kernel."""
     from oracle import oracle
     cfg = GptConfig(vocab_size=640, max_sequence_length=64, embed_dim=256, num_heads=4, feed_forward_dim=1088,
                     num_layers=3, layer_norm_epsilon=1e-5, activation="swiglu", weight_dtype="bf16")
