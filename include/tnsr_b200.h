@@ -153,8 +153,10 @@ TNSR_B200_API uint64_t tnsr_b200_kernel_launches(void);
 /* GEMM engine of the bf16 path: 0 = tcgen05/TMEM kernel where the shape
  * allows it, else the CUDA-core kernel (default); 1 = always the CUDA-core
  * kernel; 2 = tcgen05 only (unsupported shapes fail); 3 = as 0, but products
- * of at most 64 rows always take the few-row engine (by default only those
- * shapes do for which it is the faster one).  Process-wide.  Engine 1
+ * of at most 64 rows always take the tcgen05 few-row engine with split-K (by
+ * default only those shapes do for which it is the faster one); 4 = as 0, but
+ * products of at most 16 rows always take the weight-streaming engine (by
+ * default from 4 M weight elements up).  Process-wide.  Engine 1
  * also keeps prefill attention off tcgen05 (the warp-level mma.sync kernel
  * runs), which is how tests compare the two. */
 TNSR_B200_API int tnsr_b200_set_gemm_engine(int engine);

@@ -507,3 +507,41 @@ def test_sample_top_k_matches_the_cpu_restatement(vocab, top_k, temperature):
         assert torch.equal(out, greedy)
     assert lib().tnsr_b200_sample_top_k(ptr(d_logits), ptr(out), rows, vocab, 0.0, top_k, 1, 0, 0, stream()) == -1
     assert lib().tnsr_b200_sample_top_k(ptr(d_logits), ptr(out), rows, vocab, 1.0, 257, 1, 0, 0, stream()) == -1
+
+
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (8, 4096, 4096), (16, 32000, 768), (13, 100, 528), (5, 48, 16),
+                                   (16, 1000, 1040), (9, 2304, 768)])
+def test_gemm_bf16_weight_streaming_engine_matches_f64(shape):
+    """m <= 16: one pass over the weights, 16 weight rows per CTA at a time, no split-K and no scratch (gemm_stream.cu).
+    Same tolerance as the other engines, two runs bit-identical, epilogues (bias, activation, residual, bf16 output,
+    in place on the residual stream) included; engine 4 forces it also below the size from which it is the default."""
+    m, n, k = shape
+    a, bt, ref = gemm_case(m, n, k, seed=13)
+    rng = np.random.default_rng(14)
+    bias = rng.standard_normal(n).astype(np.float32)
+    resid = rng.standard_normal((m, n)).astype(np.float32)
+    da, dbt, dbias, dres = dev(a, torch.bfloat16), dev(bt, torch.bfloat16), dev(bias), dev(resid)
+    tol = 4e-6 * k
+    before = lib().tnsr_b200_kernel_launches()
+    ok(lib().tnsr_b200_set_gemm_engine(4))
+    try:
+        first = gemm_bf16(da, dbt)
+        assert lib().tnsr_b200_kernel_launches() - before == 1
+        assert np.max(np.abs(first.cpu().numpy() - ref)) <= tol
+        assert torch.equal(first, gemm_bf16(da, dbt))
+        fused = gemm_bf16(da, dbt, bias=dbias, residual=dres).cpu().numpy()
+        assert np.max(np.abs(fused - (ref + bias + resid))) <= tol + 1e-5
+        relu = gemm_bf16(da, dbt, bias=dbias, activation=0, out_dtype=BF16).float().cpu().numpy()
+        assert rel_err(relu, np.maximum(ref + bias, 0)) <= 1 / 128
+        stream_buf = dres.clone()
+        ok(lib().tnsr_b200_gemm_bf16(ptr(da), ptr(dbt), ptr(dbias), ptr(stream_buf), ptr(stream_buf), m, n, k, -1, 0, stream()))
+        torch.cuda.synchronize()
+        assert np.array_equal(stream_buf.cpu().numpy(), fused)
+    finally:
+        lib().tnsr_b200_set_gemm_engine(0)
+    ok(lib().tnsr_b200_set_gemm_engine(2))          # against the tcgen05 engine on the same operands
+    try:
+        other = gemm_bf16(da, dbt).cpu().numpy()
+    finally:
+        lib().tnsr_b200_set_gemm_engine(0)
+    assert np.max(np.abs(other - first.cpu().numpy())) <= tol

@@ -24,7 +24,7 @@ OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(CSRC, "libtnsr_b200.so")
 
 SOURCES = ["decoder.cu", "ops_api.cu", "elementwise.cu", "strict.cu", "gemm.cu", "gemm_skinny.cu", "attention.cu", "prefill.cu", "prefill_tc.cu",
-           "decode_attention_static.cu", "sampler.cu", "encoder.cu", "decode_tail.cu"]
+           "decode_attention_static.cu", "sampler.cu", "encoder.cu", "decode_tail.cu", "gemm_stream.cu"]
 EXTRA = {"strict.cu": ["--fmad=false"], "encoder.cu": ["--fmad=false"]}
 
 BASE_FLAGS = [

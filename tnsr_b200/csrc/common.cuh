@@ -157,12 +157,16 @@ struct GemmQkvTargets {
 int launch_gemm_bf16(const bf16* a, const bf16* bt, void* out, uint32_t ldc, uint32_t m, uint32_t n,
                      uint32_t k, GemmMode mode, const GemmEpilogue& ep, const GemmQkvTargets* qkv,
                      int* d_status, cudaStream_t stream);
-extern int g_gemm_engine;  // 0 auto, 1 CUDA-core only, 2 tcgen05 only, 3 auto + the few-row engine for every eligible shape
+extern int g_gemm_engine;  // 0 auto, 1 CUDA-core only, 2 tcgen05 only, 3 auto + the tcgen05 few-row engine for every eligible shape, 4 auto + the streaming engine for every eligible shape
 // Few rows (m <= 64): weights on the M side of the MMA, optional split-K (gemm_skinny.cu).
 uint64_t gemm_skinny_workspace_bytes();
 bool gemm_skinny_eligible(const bf16* a, const bf16* bt, uint32_t m, uint32_t n, uint32_t k, const GemmEpilogue& ep);
 int launch_gemm_skinny(const bf16* a, const bf16* bt, void* out, uint32_t ldc, uint32_t m, uint32_t n, uint32_t k,
                        const GemmEpilogue& ep, void* scratch, uint64_t scratch_bytes, int* d_status, cudaStream_t stream);
+// At most 16 rows: the weights stream once through a cp.async ring, no split-K and no scratch (gemm_stream.cu).
+bool gemm_stream_eligible(const bf16* a, const bf16* bt, uint32_t m, uint32_t n, uint32_t k, const GemmEpilogue& ep);
+int launch_gemm_stream(const bf16* a, const bf16* bt, void* out, uint32_t ldc, uint32_t m, uint32_t n, uint32_t k,
+                       const GemmEpilogue& ep, int* d_status, cudaStream_t stream);
 // Greedy ids straight from the LM-head GEMM: ids[r] = last index of the maximum of row r of a . bt^T
 // under IEEE totalOrder.  `candidates` is scratch for rows * ceil(n / 32) uint2 values.
 uint64_t lm_head_argmax_scratch_bytes(uint32_t rows, uint32_t n);

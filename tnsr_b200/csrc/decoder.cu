@@ -805,7 +805,7 @@ int tnsr_b200_test_lose_gemm_stage(uint32_t k_block) {
 }
 
 int tnsr_b200_set_gemm_engine(int engine) {
-    if (engine < 0 || engine > 3) return TNSR_B200_ERR_INVALID_ARGUMENT;
+    if (engine < 0 || engine > 4) return TNSR_B200_ERR_INVALID_ARGUMENT;
     g_gemm_engine = engine;
     return TNSR_B200_OK;
 }

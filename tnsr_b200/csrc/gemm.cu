@@ -813,6 +813,11 @@ static int launch_gemm_impl(const bf16* a, const bf16* bt, void* out, uint32_t l
     // 28 us for the engine below; at 64 rows (33.6 against 21.5 us) and for the small matrices of a decode step (the
     // split-K hand-over through L2 costs more than it saves) the engine below is the faster one.
     // Engine 3 (tests) takes it for every eligible shape up to 64 rows.
+    // Up to 16 rows against at least 4 M weight elements: one pass over the weights with no split-K (gemm_stream.cu).
+    // Engine 4 (tests) takes it for every eligible shape.
+    if (mode == GEMM_PLAIN && m <= 16 && (g_gemm_engine == 0 || g_gemm_engine == 4) && gemm_stream_eligible(a, bt, m, n, k, ep) &&
+        ((uint64_t)n * k >= (4ull << 20) || g_gemm_engine == 4))
+        return launch_gemm_stream(a, bt, out, ldc, m, n, k, ep, d_status, stream);
     if (mode == GEMM_PLAIN && m <= 64 && g_gemm_engine != 1 && gemm_skinny_eligible(a, bt, m, n, k, ep)) {
         const bool pays = m <= 16 && (uint64_t)n * k >= (4ull << 20) &&
                           ((ep.skinny_ws && ep.skinny_ws_bytes >= gemm_skinny_workspace_bytes()) ||
