@@ -93,8 +93,8 @@ gemm_stream_kernel(GsParams P) {
     // Slot s = chunk (s % chunks) of this CTA's (s / chunks)-th column tile; one cp.async group per slot.  (Starting
     // every tile's walk over K at a different chunk, so that the CTAs do not all read the same column range at the same
     // moment, was measured and is slower: 15.5 against 14.2 us.)
-    auto chunk_of = [&](uint32_t s) { return s % chunks; };  A thread always
-    // copies the same four (row, column) pieces of a chunk: rows r0, r0 + 4, r0 + 8, r0 + 12 at column kk.
+    auto chunk_of = [&](uint32_t s) { return s % chunks; };
+    // A thread always copies the same four (row, column) pieces of a chunk: rows r0, r0 + 4, r0 + 8, r0 + 12 at column kk.
     const uint32_t r0 = threadIdx.x >> 6, kk = (threadIdx.x & 63) * 8;
     const uint32_t dst_off = r0 * GS_PITCH + kk;
     auto issue = [&](uint32_t s) {
