@@ -1,6 +1,7 @@
 """Operator-level measurements of the kernels behind the C ABI.
 
     python -m tnsr_b200.opbench gemm        # configuration 1: square sweep + skinny decode shapes
+    python -m tnsr_b200.opbench skinny_gemm # only the skinny decode shapes of configuration 1 (M = 1, 8, 64; bf16 out)
     python -m tnsr_b200.opbench serving_gemms  # configuration 4's projection shapes at prefill and decode size
     python -m tnsr_b200.opbench mlp         # configuration 2: fused SwiGLU MLP 4096 x 2048 -> 5632 -> 2048
     python -m tnsr_b200.opbench attention   # configuration 3: 64 sessions x 16 heads x 64, ragged lengths <= 4096
@@ -294,7 +295,7 @@ def bench_elementwise(samples):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "serving_gemms", "mlp", "attention", "serving_attention", "elementwise", "prefill_attention", "all"])
+    ap.add_argument("what", choices=["gemm", "skinny_gemm", "serving_gemms", "mlp", "attention", "serving_attention", "elementwise", "prefill_attention", "all"])
     ap.add_argument("--samples", type=int, default=20)
     args = ap.parse_args()
     if not torch.cuda.is_available():
@@ -302,7 +303,8 @@ def main():
     todo = (["gemm", "serving_gemms", "mlp", "attention", "serving_attention", "elementwise", "prefill_attention"]
             if args.what == "all" else [args.what])
     for name in todo:
-        {"gemm": bench_gemm, "serving_gemms": bench_serving_gemms, "mlp": bench_mlp, "attention": bench_attention,
+        {"gemm": bench_gemm, "skinny_gemm": lambda n: bench_gemm(n, shapes=[(m, 4096, 4096) for m in (1, 8, 64)], outs=("bf16",)),
+         "serving_gemms": bench_serving_gemms, "mlp": bench_mlp, "attention": bench_attention,
          "serving_attention": lambda n: bench_attention(n, serving=True),
          "elementwise": bench_elementwise, "prefill_attention": bench_prefill_attention}[name](args.samples)
 
