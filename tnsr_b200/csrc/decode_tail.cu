@@ -1,4 +1,4 @@
-// One kernel for everything between two attention scans of a single-token step at small batch (<= 64 sessions):
+// One kernel for everything between two attention scans of a single-token step at small batch (<= 32 sessions):
 // output projection + residual, LayerNorm, gate/up projection + SwiGLU, down projection + residual, the next layer's
 // LayerNorm and its QKV projection with the K/V cache write.
 //
@@ -9,13 +9,28 @@
 // already in flight while a CTA waits at the barrier (weights never depend on activations); the two LayerNorms are
 // recomputed by every CTA from the f32 residual rows (a few dozen rows: cheaper than two more barriers).
 //
+// What a launch costs is neither HBM bandwidth nor the barriers themselves (all 148 CTAs copy the same 96 KB out of L2
+// in 0.9 us, a grid barrier takes 1.1 us, both measured) but what each SM does alone, timed per phase with %globaltimer:
+//   * dependent instruction chains, with one CTA per SM and little to switch to while a load, a shuffle or an MMA is in
+//     flight: hence 16 warps, a LayerNorm row per 16 or 32 threads with all of its loads issued at once, the k-steps of
+//     a chunk dealt over 8 or 16 groups of warps, and every global value an epilogue needs (bias, residual, position)
+//     requested before the MMA loop rather than after it;
+//   * shared-memory bandwidth in the MMA loop: a warp loads a weight fragment once and uses it for two session tiles
+//     (one fragment load per MMA kept the loop at 0.7 us per 512-wide chunk);
+//   * a few KB that every warp of every CTA wants at the same moment (LayerNorm scale and shift) sit in one or two L2
+//     slices: fetched per warp they cost 4 us per LayerNorm, staged once per CTA into shared memory nothing measurable;
+//   * an SM takes in about 64 bytes per clock from L2: the down projection's 131 KB of activations per CTA are 1.1 us
+//     whatever the copy instruction (bulk copies of one row each were slower than 16-byte cp.async here).
+//
 // Shape of the work: with so few rows the projections are weight streaming, not tensor-core throughput.  A CTA owns 16
 // output columns (32 packed gate/up columns) of a projection: its weight rows are read exactly once by the grid, the
-// activation rows (<= 64) are re-read by every CTA from L2.  The products run on warp-level mma.sync.m16n8k16 (bf16 in,
+// activation rows (<= 32) are re-read by every CTA from L2.  The products run on warp-level mma.sync.m16n8k16 (bf16 in,
 // f32 out) with the weight rows as the M side and 8 sessions as the N side -- tcgen05's 64/128-row M side would leave a
-// CTA either most of a projection or most of the MMA empty at this size.  K is walked in chunks of 512 through a
-// double-buffered cp.async pipeline; inside a chunk the k-steps alternate between two groups of warps whose partial
-// sums are added in a fixed order, so results do not depend on the number of sessions or on timing.
+// CTA either most of a projection or most of the MMA empty at this size.  K is walked in chunks of 512 through a ring of
+// cp.async stages (four of 16 weight rows or two of 32, three of activation rows): for widths up to 2048 every weight
+// chunk of a CTA's next tile is requested between arriving at the barrier and waiting on it.  Inside a chunk the k-steps alternate between
+// the k-groups of warps, whose partial sums are added in a fixed order, so results do not depend on the number of
+// sessions or on timing.
 //
 // Cross-CTA data (residual rows, attention output, the SwiGLU hidden rows) is read with L2-only loads (ld.global.cg,
 // cp.async.cg): another CTA wrote it during this launch.  Every barrier wait is bounded; on expiry the kernel records
@@ -26,11 +41,14 @@ namespace tb {
 
 namespace {
 
-constexpr int DT_THREADS = 256;
+constexpr int DT_THREADS = 512;
+constexpr int DT_WARPS = DT_THREADS / 32;
 constexpr int DT_KCH = 512;                     // K elements per pipeline chunk
 constexpr int DT_PITCH = DT_KCH + 8;            // shared-memory row pitch in elements: 1040 bytes, conflict-free ldmatrix
-constexpr int DT_MAX_COLS = 32;                 // packed gate/up tile; plain projections use 16
-constexpr int DT_MAX_D = 1024;                  // LayerNorm rows stay in registers up to this width
+constexpr int DT_W_ROWS = 64;                   // weight rows in the ring: 4 stages of 16 or 2 stages of 32
+constexpr int DT_A_STAGES = 3;                  // activation stages of MT rows each
+constexpr int DT_RED_PITCH = 33;                // floats per session row of a k-group's partial sums: conflict-free both ways
+constexpr int DT_MAX_D = 1024;                  // widest model: a LayerNorm row is held in the registers of its threads
 
 enum : uint32_t { DT_PHASE_O = 1, DT_PHASE_GU = 2, DT_PHASE_DOWN = 4, DT_PHASE_QKV = 8 };
 
@@ -80,9 +98,6 @@ __device__ __forceinline__ void dt_ldmatrix_x4(uint32_t (&r)[4], const void* p) 
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(dt_smem(p)));
 }
-__device__ __forceinline__ void dt_ldmatrix_x2(uint32_t (&r)[2], const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(dt_smem(p)));
-}
 __device__ __forceinline__ void dt_mma(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -95,12 +110,18 @@ __device__ __forceinline__ uint64_t dt_timer() {
     return t;
 }
 
-// Grid-wide barrier number `index` (0, 1, ...) of this launch.  Returns false if the wait ran out.
-__device__ __forceinline__ bool dt_grid_barrier(const DtParams& P, uint32_t index, int* s_abort) {
+// Grid-wide barrier number `index` (0, 1, ...) of this launch, in two halves so that work which does not depend on the
+// other CTAs (requests for the next phase's weights) sits between arriving and waiting.
+__device__ __forceinline__ void dt_grid_arrive(const DtParams& P) {
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();                                   // this CTA's writes before its arrival
         atomicAdd(&P.barrier->arrived, 1u);
+    }
+}
+// Returns false if the wait ran out.
+__device__ __forceinline__ bool dt_grid_wait(const DtParams& P, uint32_t index, int* s_abort) {
+    if (threadIdx.x == 0) {
         const uint32_t target = (index + 1) * gridDim.x;
         const uint64_t start = dt_timer();
         uint32_t seen;
@@ -129,287 +150,312 @@ struct DtGemm {
     const bf16* act;      // streamed activation rows [rows, k] (global), or nullptr: the rows are resident in `nbuf`
 };
 
-// Copies chunk `chunk` of the tile's weight rows (and, if streamed, of the activation rows) into pipeline buffer `buf`.
-template <int MT>
-__device__ __forceinline__ void dt_issue_w(const DtGemm& g, uint32_t n0, uint32_t chunk, bf16* wbuf) {
+// Copies chunk `chunk` of the tile's weight rows (and, if streamed, of the activation rows) into a ring stage.
+__device__ __forceinline__ void dt_issue_w(const DtGemm& g, uint32_t n0, uint32_t chunk, bf16* wstage) {
     const uint32_t k0 = chunk * DT_KCH;
-    const uint32_t pieces_per_row = DT_KCH / 8;
-    for (uint32_t i = threadIdx.x; i < g.cols * pieces_per_row; i += DT_THREADS) {
-        const uint32_t r = i / pieces_per_row, kk = (i % pieces_per_row) * 8;
+    const uint32_t kk = (threadIdx.x & 63u) * 8;                       // 64 pieces of 16 bytes per row
+#pragma unroll 1
+    for (uint32_t r = threadIdx.x >> 6; r < g.cols; r += DT_THREADS / 64) {
         const bool valid = n0 + r < g.n && k0 + kk < g.k;
-        dt_cp16(wbuf + (size_t)r * DT_PITCH + kk, g.w + (valid ? (size_t)(n0 + r) * g.k + k0 + kk : 0), valid);
+        dt_cp16(wstage + (size_t)r * DT_PITCH + kk, g.w + (valid ? (size_t)(n0 + r) * g.k + k0 + kk : 0), valid);
     }
 }
-template <int MT>
-__device__ __forceinline__ void dt_issue_a(const DtGemm& g, uint32_t rows, uint32_t chunk, bf16* abuf) {
+__device__ __forceinline__ void dt_issue_a(const DtGemm& g, uint32_t rows, uint32_t mt, uint32_t chunk, bf16* astage) {
     if (!g.act) return;
     const uint32_t k0 = chunk * DT_KCH;
-    const uint32_t pieces_per_row = DT_KCH / 8;
-    for (uint32_t i = threadIdx.x; i < MT * pieces_per_row; i += DT_THREADS) {
-        const uint32_t r = i / pieces_per_row, kk = (i % pieces_per_row) * 8;
+    const uint32_t kk = (threadIdx.x & 63u) * 8;
+#pragma unroll 1
+    for (uint32_t r = threadIdx.x >> 6; r < mt; r += DT_THREADS / 64) {
         const bool valid = r < rows && k0 + kk < g.k;
-        dt_cp16(abuf + (size_t)r * DT_PITCH + kk, g.act + (valid ? (size_t)r * g.k + k0 + kk : 0), valid);
+        dt_cp16(astage + (size_t)r * DT_PITCH + kk, g.act + (valid ? (size_t)r * g.k + k0 + kk : 0), valid);
     }
 }
+__device__ __forceinline__ uint32_t dt_stages(const DtGemm& g) {
+    const uint32_t ws = DT_W_ROWS / g.cols;
+    return g.act ? min(ws, (uint32_t)DT_A_STAGES) : ws;
+}
+__device__ __forceinline__ void dt_wait_pending(uint32_t n) {
+    if (n == 0) dt_wait<0>();
+    else if (n == 1) dt_wait<1>();
+    else if (n == 2) dt_wait<2>();
+    else dt_wait<3>();
+}
 
-// LayerNorm of the residual rows into `nbuf` ([MT][d + 8] bf16), one warp per row, the arithmetic of
-// layernorm_warp_kernel (two passes over registers, rsqrt of the biased variance).  Rows past `rows` become zeros.
+// LayerNorm of the residual rows into `nbuf` ([MT][d + 8] bf16): two passes over registers, rsqrt of the biased variance,
+// as layernorm_warp_kernel does.  Scale and shift come from shared memory: a few KB that every warp of every CTA wants
+// at the same moment sit in one or two L2 slices, and fetched per warp they cost 4 us.  A row belongs to TPR = 512 / MT consecutive lanes (16 or 32), thread p of them holding
+// the float4s p, p + TPR, ...; all loads of a thread are in flight together and the two sums are butterfly reductions
+// over the row's lanes.  Rows past `rows` become zeros.
 template <int MT>
-__device__ __forceinline__ void dt_layernorm(const DtParams& P, const float* __restrict__ w, const float* __restrict__ b, bf16* nbuf) {
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t d = P.d, nvec = d >> 2, pitch = d + 8;
-    for (uint32_t r = warp; r < (uint32_t)MT; r += DT_THREADS / 32) {
-        uint2* out = reinterpret_cast<uint2*>(nbuf + (size_t)r * pitch);
-        if (r >= P.rows) {
-            for (uint32_t c = lane; c < nvec; c += 32) out[c] = make_uint2(0u, 0u);
-            continue;
+__device__ __forceinline__ void dt_layernorm(const DtParams& P, const float* lnbuf, bf16* nbuf) {
+    constexpr uint32_t TPR = DT_THREADS / MT;              // threads per row
+    constexpr int NV = DT_MAX_D / 4 / TPR;                 // float4 per thread: 16 or 8
+    const uint32_t r = threadIdx.x / TPR, p = threadIdx.x % TPR;
+    const uint32_t d = P.d, nvec = d >> 2;
+    const bool live = r < P.rows;
+    const float4* xr = reinterpret_cast<const float4*>(P.h + (size_t)r * d);
+    float4 v[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const uint32_t c = p + i * TPR;
+        v[i] = (live && c < nvec) ? __ldcg(xr + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+#pragma unroll
+    for (uint32_t o = TPR / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float mean = sum / (float)d;
+    float sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        if (p + i * TPR < nvec) {
+            v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+            sq += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
         }
-        const float4* xr = reinterpret_cast<const float4*>(P.h + (size_t)r * d);
-        float4 v[DT_MAX_D / 128];
-        float sum = 0.0f;
+    }
 #pragma unroll
-        for (int i = 0; i < DT_MAX_D / 128; ++i) {
-            const uint32_t c = lane + i * 32;
-            if (c < nvec) {
-                v[i] = __ldcg(xr + c);
-                sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
-            }
-        }
+    for (uint32_t o = TPR / 2; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    const float inv = rsqrtf(sq / (float)d + P.eps);
+    const float4* wr = reinterpret_cast<const float4*>(lnbuf);               // scale, then shift: copies in shared memory
+    const float4* br = reinterpret_cast<const float4*>(lnbuf + DT_MAX_D);
+    uint2* out = reinterpret_cast<uint2*>(nbuf + (size_t)r * (d + 8));
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        const float mean = sum / (float)d;
-        float sq = 0.0f;
-#pragma unroll
-        for (int i = 0; i < DT_MAX_D / 128; ++i) {
-            const uint32_t c = lane + i * 32;
-            if (c < nvec) {
-                v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
-                sq += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
-            }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-        const float inv = rsqrtf(sq / (float)d + P.eps);
-        const float4* wr = reinterpret_cast<const float4*>(w);
-        const float4* br = reinterpret_cast<const float4*>(b);
-#pragma unroll
-        for (int i = 0; i < DT_MAX_D / 128; ++i) {
-            const uint32_t c = lane + i * 32;
-            if (c < nvec) {
-                const float4 ww = __ldg(wr + c), bb = __ldg(br + c);
-                out[c] = make_uint2(pack_bf16x2(v[i].x * inv * ww.x + bb.x, v[i].y * inv * ww.y + bb.y),
-                                    pack_bf16x2(v[i].z * inv * ww.z + bb.z, v[i].w * inv * ww.w + bb.w));
-            }
+    for (int i = 0; i < NV; ++i) {
+        const uint32_t c = p + i * TPR;
+        if (c < nvec) {
+            const float4 ww = wr[c], bb = br[c];
+            out[c] = live ? make_uint2(pack_bf16x2(v[i].x * inv * ww.x + bb.x, v[i].y * inv * ww.y + bb.y),
+                                       pack_bf16x2(v[i].z * inv * ww.z + bb.z, v[i].w * inv * ww.w + bb.w))
+                          : make_uint2(0u, 0u);
         }
     }
 }
 
-// One tile of a projection: acc[c][m] for the tile's columns c and all MT session rows, left in `red` as
-// red[c * MT + m] (f32).  The pipeline's first weight chunk may already be in flight (`w0_issued`).
+// Requests a LayerNorm's scale and shift into `lnbuf` ([2][DT_MAX_D] f32) as one cp.async group.  They are weights: the
+// request can go out before the barrier that the rows wait for.
+__device__ __forceinline__ void dt_issue_ln(const float* w, const float* b, uint32_t d, float* lnbuf) {
+    const uint32_t nvec = d >> 2;
+    for (uint32_t i = threadIdx.x; i < 2 * nvec; i += DT_THREADS) {
+        const bool shift = i >= nvec;
+        const uint32_t c = shift ? i - nvec : i;
+        dt_cp16(lnbuf + (shift ? DT_MAX_D : 0) + c * 4, (shift ? b : w) + c * 4, true);
+    }
+    dt_commit();
+}
+
+// Requests the first weight chunks of tile `n0` (as many as the ring holds), one cp.async group each; returns how many.
+__device__ __forceinline__ uint32_t dt_prefetch_w(const DtGemm& g, uint32_t n0, bf16* wbuf) {
+    const uint32_t chunks = (g.k + DT_KCH - 1) / DT_KCH;
+    const uint32_t pre = min(dt_stages(g), chunks);
+#pragma unroll 1
+    for (uint32_t c = 0; c < pre; ++c) {
+        dt_issue_w(g, n0, c, wbuf + (size_t)c * g.cols * DT_PITCH);
+        dt_commit();
+    }
+    return pre;
+}
+
+// One tile of a projection: the products of the tile's columns c with all MT session rows, left in `red` as one partial
+// sum per k-group: red[kg * MT * 33 + m * 33 + c] (f32).  The first `w_issued` weight chunks are already in flight
+// (dt_prefetch_w).
 //
-// Warp w: k-group kp = w / 4 takes the k-steps kp, kp + 2, ... of every chunk; ng = w % 4 takes the session tiles
-// ng and ng + 4 (8 sessions each).  The two k-groups are added as (group 0) + (group 1).
+// A warp takes two session tiles (16 sessions) and the k-steps kp, kp + KG, ... of every chunk, kp being its k-group:
+// every weight fragment it loads from shared memory feeds two MMAs (four for the packed gate/up tile), which is what
+// keeps the loop under the shared-memory bandwidth that one fragment load per MMA would need.
 template <int MT>
 __device__ __forceinline__ void dt_gemm_tile(const DtGemm& g, uint32_t rows, uint32_t n0, bf16* wbuf, bf16* abuf, const bf16* nbuf,
-                                             uint32_t npitch, float* red, bool w0_issued) {
-    constexpr int NT = MT / 8;                      // session tiles
-    constexpr int NPW = (NT + 3) / 4;               // session tiles per warp: 1 (MT <= 32) or 2 (MT 64)
+                                             uint32_t npitch, float* red, uint32_t w_issued) {
+    constexpr uint32_t NP = MT / 16;                // pairs of session tiles: 1 or 2
+    constexpr uint32_t KG = DT_WARPS / NP;          // k-groups: 16 or 8
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t kp = warp >> 2, ng = warp & 3;
+    const uint32_t kp = warp / NP, np = warp % NP;
     const uint32_t chunks = (g.k + DT_KCH - 1) / DT_KCH;
-    const uint32_t atiles = g.cols / 16;
-    float acc[2][NPW][4];
+    const bool two = g.cols == 32;                  // a second 16-row weight tile (packed gate/up)
+    const uint32_t S = dt_stages(g);
+    const size_t wstage = (size_t)g.cols * DT_PITCH, astage = (size_t)MT * DT_PITCH;
+    float acc[2][2][4];                             // [weight tile][session tile of the pair][fragment]
 #pragma unroll
     for (int a = 0; a < 2; ++a)
 #pragma unroll
-        for (int j = 0; j < NPW; ++j)
+        for (int t = 0; t < 2; ++t)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) acc[a][j][e] = 0.0f;
+            for (int e = 0; e < 4; ++e) acc[a][t][e] = 0.0f;
 
-    // every chunk is two cp.async groups: weights, then activations (empty when the rows are resident)
-    if (!w0_issued) dt_issue_w<MT>(g, n0, 0, wbuf);
-    dt_commit();
-    dt_issue_a<MT>(g, rows, 0, abuf);
-    dt_commit();
+    // one cp.async group per chunk: its weights (unless already requested) and its activation rows (unless resident)
+    const uint32_t pre = min(S, chunks);
+#pragma unroll 1
+    for (uint32_t c = 0; c < pre; ++c) {
+        if (c >= w_issued) dt_issue_w(g, n0, c, wbuf + c * wstage);
+        dt_issue_a(g, rows, MT, c, abuf + c * astage);
+        dt_commit();
+    }
+#pragma unroll 1
     for (uint32_t ch = 0; ch < chunks; ++ch) {
-        const uint32_t cur = ch & 1, nxt = cur ^ 1;
-        if (ch + 1 < chunks) {
-            dt_issue_w<MT>(g, n0, ch + 1, wbuf + (size_t)nxt * DT_MAX_COLS * DT_PITCH);
-            dt_commit();
-            dt_issue_a<MT>(g, rows, ch + 1, abuf + (size_t)nxt * MT * DT_PITCH);
-            dt_commit();
-            dt_wait<2>();
-        } else {
-            dt_wait<0>();
-        }
+        const uint32_t st = ch % S;
+        dt_wait_pending(min(chunks - 1 - ch, S - 1));     // groups requested after this chunk's may still be in flight
         __syncthreads();
-        const bf16* wt = wbuf + (size_t)cur * DT_MAX_COLS * DT_PITCH;
-        const bf16* at = g.act ? abuf + (size_t)cur * MT * DT_PITCH : nbuf + (size_t)ch * DT_KCH;
+        const bf16* wt = wbuf + st * wstage;
+        const bf16* at = g.act ? abuf + st * astage : nbuf + (size_t)ch * DT_KCH;
         const uint32_t apitch = g.act ? (uint32_t)DT_PITCH : npitch;
         const uint32_t ksteps = min((uint32_t)DT_KCH, g.k - ch * DT_KCH) / 16;
-        for (uint32_t ks = kp; ks < ksteps; ks += 2) {
-            uint32_t a[2][4];
-            for (uint32_t t = 0; t < atiles; ++t)
-                dt_ldmatrix_x4(a[t], wt + (size_t)(t * 16 + (lane & 15)) * DT_PITCH + ks * 16 + (lane >> 4) * 8);
-#pragma unroll
-            for (int j = 0; j < NPW; ++j) {
-                const uint32_t nt = ng + 4 * j;
-                if (nt >= (uint32_t)NT) continue;
-                uint32_t b[2];
-                dt_ldmatrix_x2(b, at + (size_t)(nt * 8 + (lane & 7)) * apitch + ks * 16 + ((lane >> 3) & 1) * 8);
-                for (uint32_t t = 0; t < atiles; ++t) dt_mma(acc[t][j], a[t], b);
+        const bf16* wp = wt + (size_t)(lane & 15) * DT_PITCH + (lane >> 4) * 8;
+        // sessions np * 16 + [0, 16): matrices (rows 0-7, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 0-7), (rows 8-15, k 8-15)
+        const bf16* ap = at + (size_t)(np * 16 + (lane >> 4) * 8 + (lane & 7)) * apitch + ((lane >> 3) & 1) * 8;
+#pragma unroll 2
+        for (uint32_t ks = kp; ks < ksteps; ks += KG) {
+            uint32_t a0[4], a1[4], b[4];
+            dt_ldmatrix_x4(a0, wp + ks * 16);
+            dt_ldmatrix_x4(b, ap + ks * 16);
+            if (two) dt_ldmatrix_x4(a1, wp + (size_t)16 * DT_PITCH + ks * 16);
+            const uint32_t bl[2] = {b[0], b[1]}, bh[2] = {b[2], b[3]};
+            dt_mma(acc[0][0], a0, bl);
+            dt_mma(acc[0][1], a0, bh);
+            if (two) {
+                dt_mma(acc[1][0], a1, bl);
+                dt_mma(acc[1][1], a1, bh);
             }
         }
-        __syncthreads();        // the buffers of this chunk are free for the chunk after next
-    }
-    // (k-group 0) + (k-group 1), through shared memory: red[c * MT + m]
-    const uint32_t row = lane >> 2, col = (lane & 3) * 2;
-    if (kp == 1) {
-#pragma unroll
-        for (int j = 0; j < NPW; ++j) {
-            const uint32_t nt = ng + 4 * j;
-            if (nt >= (uint32_t)NT) continue;
-            for (uint32_t t = 0; t < atiles; ++t) {
-                const uint32_t c = t * 16 + row, m = nt * 8 + col;
-                red[c * MT + m] = acc[t][j][0];
-                red[c * MT + m + 1] = acc[t][j][1];
-                red[(c + 8) * MT + m] = acc[t][j][2];
-                red[(c + 8) * MT + m + 1] = acc[t][j][3];
-            }
+        if (ch + S < chunks) {
+            __syncthreads();        // every warp is done with this stage: refill it
+            dt_issue_w(g, n0, ch + S, wbuf + st * wstage);
+            dt_issue_a(g, rows, MT, ch + S, abuf + st * astage);
+            dt_commit();
         }
     }
-    __syncthreads();
-    if (kp == 0) {
+    // this k-group's partial sums: red[kp][m * 33 + c]
+    const uint32_t row = lane >> 2;
+    float* mine = red + (size_t)kp * MT * DT_RED_PITCH;
 #pragma unroll
-        for (int j = 0; j < NPW; ++j) {
-            const uint32_t nt = ng + 4 * j;
-            if (nt >= (uint32_t)NT) continue;
-            for (uint32_t t = 0; t < atiles; ++t) {
-                const uint32_t c = t * 16 + row, m = nt * 8 + col;
-                red[c * MT + m] = acc[t][j][0] + red[c * MT + m];
-                red[c * MT + m + 1] = acc[t][j][1] + red[c * MT + m + 1];
-                red[(c + 8) * MT + m] = acc[t][j][2] + red[(c + 8) * MT + m];
-                red[(c + 8) * MT + m + 1] = acc[t][j][3] + red[(c + 8) * MT + m + 1];
-            }
+    for (int t = 0; t < 2; ++t) {
+        if (t == 1 && !two) break;
+        const uint32_t c = t * 16 + row;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint32_t m = np * 16 + j * 8 + (lane & 3) * 2;
+            mine[m * DT_RED_PITCH + c] = acc[t][j][0];
+            mine[(m + 1) * DT_RED_PITCH + c] = acc[t][j][1];
+            mine[m * DT_RED_PITCH + c + 8] = acc[t][j][2];
+            mine[(m + 1) * DT_RED_PITCH + c + 8] = acc[t][j][3];
         }
     }
     __syncthreads();
+}
+
+// Sum over the k-groups of one output, in a fixed order.
+template <int MT>
+__device__ __forceinline__ float dt_reduced(const float* red, uint32_t idx) {
+    constexpr uint32_t KG = DT_WARPS / (MT / 16);
+    constexpr uint32_t STRIDE = MT * DT_RED_PITCH;
+    float s[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        s[q] = 0.0f;
+#pragma unroll
+        for (uint32_t i = 0; i < KG / 4; ++i) s[q] += red[idx + (q * (KG / 4) + i) * STRIDE];
+    }
+    return (s[0] + s[1]) + (s[2] + s[3]);
+}
+
+// The projection of phase `ph` (0: attention output, 1: gate/up, 2: down, 3: next layer's QKV).
+__device__ __forceinline__ DtGemm dt_phase_gemm(const DtParams& P, uint32_t ph) {
+    DtGemm g;
+    g.w = ph == 0 ? P.wo : ph == 1 ? P.wgu : ph == 2 ? P.wdown : P.wqkv;
+    g.n = ph == 1 ? 2 * P.f : ph == 3 ? 3 * P.d : P.d;
+    g.k = ph == 2 ? P.f : P.d;
+    g.cols = ph == 1 ? 32u : 16u;
+    g.act = ph == 0 ? P.att : ph == 2 ? P.ff : nullptr;
+    return g;
 }
 
 template <int MT>
 __global__ void __launch_bounds__(DT_THREADS, 1)
 decode_tail_kernel(DtParams P) {
     extern __shared__ __align__(128) uint8_t smem[];
-    bf16* wbuf = reinterpret_cast<bf16*>(smem);                                   // [2][32][PITCH]
-    bf16* abuf = wbuf + (size_t)2 * DT_MAX_COLS * DT_PITCH;                       // [2][MT][PITCH], or the resident rows
-    bf16* nbuf = abuf;                                                            // [MT][d + 8] (phases GU and QKV)
-    const size_t act_elems = max((size_t)2 * MT * DT_PITCH, (size_t)MT * (DT_MAX_D + 8));
-    float* red = reinterpret_cast<float*>(abuf + act_elems);                      // [32 * MT]
-    int* s_abort = reinterpret_cast<int*>(red + DT_MAX_COLS * MT);
+    constexpr uint32_t KG = DT_WARPS / (MT / 16);
+    bf16* wbuf = reinterpret_cast<bf16*>(smem);                                   // [DT_W_ROWS][PITCH]
+    bf16* abuf = wbuf + (size_t)DT_W_ROWS * DT_PITCH;                             // [DT_A_STAGES][MT][PITCH], or the LayerNorm rows
+    constexpr size_t act_elems = (size_t)DT_A_STAGES * MT * DT_PITCH;
+    static_assert((size_t)MT * (DT_MAX_D + 8) <= act_elems, "LayerNorm rows must fit the activation ring");
+    static_assert(16 * MT <= DT_THREADS, "one output per thread in the epilogue");
+    float* red = reinterpret_cast<float*>(abuf + act_elems);                      // [KG][MT][33]
+    float* lnbuf = red + (size_t)KG * MT * DT_RED_PITCH;                           // [2][DT_MAX_D]
+    int* s_abort = reinterpret_cast<int*>(lnbuf + 2 * DT_MAX_D);
     if (threadIdx.x == 0) *s_abort = 0;
     __syncthreads();
 
     const uint32_t d = P.d, f = P.f, rows = P.rows;
     const uint32_t npitch = d + 8;
-    uint32_t barriers = 0;
-    bool ok = true;
+    uint32_t barriers = 0, w0 = 0;
+    bool ok = true, ln_ready = false;
+    // the output of a tile this thread finishes: column c of the tile, session m
+    const uint32_t c = threadIdx.x % 16, m = threadIdx.x / 16;
 
-    DtGemm go = {P.wo, d, d, 16, P.att};
-    DtGemm ggu = {P.wgu, 2 * f, d, 32, nullptr};
-    DtGemm gdown = {P.wdown, d, f, 16, P.ff};
-    DtGemm gqkv = {P.wqkv, 3 * d, d, 16, nullptr};
-
-    // first weight chunk of the phase after `done`, for the tile this CTA will take there (if any)
-    auto prefetch_next = [&](uint32_t done) -> bool {
-        const DtGemm* g = nullptr;
-        if (done < DT_PHASE_GU && (P.phases & DT_PHASE_GU)) g = &ggu;
-        else if (done < DT_PHASE_DOWN && (P.phases & DT_PHASE_DOWN)) g = &gdown;
-        else if (done < DT_PHASE_QKV && (P.phases & DT_PHASE_QKV)) g = &gqkv;
-        if (!g) return false;
-        const uint32_t n0 = blockIdx.x * g->cols;
-        if (n0 >= g->n) return false;
-        dt_issue_w<MT>(*g, n0, 0, wbuf);
-        return true;
-    };
-
-    bool w0 = false;
-    // ---------------- output projection: h += att . Wo^T + bo ----------------
-    if (P.phases & DT_PHASE_O) {
-        for (uint32_t n0 = blockIdx.x * 16; n0 < d; n0 += gridDim.x * 16) {
-            dt_gemm_tile<MT>(go, rows, n0, wbuf, abuf, nullptr, 0, red, false);
-            for (uint32_t o = threadIdx.x; o < 16u * MT; o += DT_THREADS) {
-                const uint32_t c = o % 16, m = o / 16;
-                if (m < rows && n0 + c < d) {
-                    float* p = P.h + (size_t)m * d + n0 + c;
-                    *p = __ldcg(p) + (red[c * MT + m] + __ldg(P.bo + n0 + c));
-                }
-            }
+#pragma unroll 1
+    for (uint32_t ph = 0; ph < 4 && ok; ++ph) {
+        if (!((P.phases >> ph) & 1u)) continue;
+        const DtGemm g = dt_phase_gemm(P, ph);
+        const float* bias = ph == 0 ? P.bo : ph == 1 ? P.bgu : ph == 2 ? P.bdown : P.bqkv;
+        if (ph & 1u) {
+            // gate/up and QKV read the LayerNorm of the residual rows, which lives where the streamed activation
+            // chunks of the other two phases do
+            if (!ln_ready) dt_issue_ln(ph == 1 ? P.ln2w : P.ln1w, ph == 1 ? P.ln2b : P.ln1b, d, lnbuf);
+            dt_wait_pending(w0);                 // the parameters' group is older than the w0 weight groups
+            __syncthreads();
+            ln_ready = false;
+            dt_layernorm<MT>(P, lnbuf, abuf);
             __syncthreads();
         }
-        w0 = prefetch_next(DT_PHASE_O);
-        if (P.phases & ~(DT_PHASE_O | (DT_PHASE_O - 1))) ok = dt_grid_barrier(P, barriers++, s_abort);
-    }
-    // ---------------- LayerNorm, gate/up projection, SwiGLU -> ff ----------------
-    if (ok && (P.phases & DT_PHASE_GU)) {
-        // the LayerNorm output lives where the streamed activation chunks would: this phase streams none
-        dt_layernorm<MT>(P, P.ln2w, P.ln2b, nbuf);
-        __syncthreads();
-        for (uint32_t n0 = blockIdx.x * 32; n0 < 2 * f; n0 += gridDim.x * 32) {
-            dt_gemm_tile<MT>(ggu, rows, n0, wbuf, abuf, nbuf, npitch, red, w0);
-            w0 = false;
-            // packed columns [0, 16) are gate, [16, 32) the matching up columns -> 16 outputs
-            for (uint32_t o = threadIdx.x; o < 16u * MT; o += DT_THREADS) {
-                const uint32_t j = o % 16, m = o / 16;
-                if (m < rows) {
-                    const float gte = red[j * MT + m] + __ldg(P.bgu + n0 + j);
-                    const float up = red[(16 + j) * MT + m] + __ldg(P.bgu + n0 + 16 + j);
-                    P.ff[(size_t)m * f + n0 / 2 + j] = __float2bfloat16_rn(fast_silu(gte) * up);
-                }
+#pragma unroll 1
+        for (uint32_t n0 = blockIdx.x * g.cols; n0 < g.n; n0 += gridDim.x * g.cols) {
+            // what the epilogue will need from global memory, requested before the products
+            const uint32_t col = n0 + c;
+            const bool mine = m < rows && (ph == 1 || col < g.n);
+            float b0 = 0.0f, b1 = 0.0f, hold = 0.0f;
+            uint32_t pos = 0;
+            if (mine) {
+                b0 = __ldg(bias + col);
+                if (ph == 1) b1 = __ldg(bias + col + 16);
+                if (ph == 0 || ph == 2) hold = __ldcg(P.h + (size_t)m * d + col);
+                if (ph == 3) pos = P.d_position ? P.d_position[(size_t)m * P.position_stride] : P.position;
             }
-            __syncthreads();
-        }
-        w0 = prefetch_next(DT_PHASE_GU);
-        if (P.phases & (DT_PHASE_DOWN | DT_PHASE_QKV)) ok = dt_grid_barrier(P, barriers++, s_abort);
-    }
-    // ---------------- down projection: h += ff . Wdown^T + bdown ----------------
-    if (ok && (P.phases & DT_PHASE_DOWN)) {
-        for (uint32_t n0 = blockIdx.x * 16; n0 < d; n0 += gridDim.x * 16) {
-            dt_gemm_tile<MT>(gdown, rows, n0, wbuf, abuf, nullptr, 0, red, w0);
-            w0 = false;
-            for (uint32_t o = threadIdx.x; o < 16u * MT; o += DT_THREADS) {
-                const uint32_t c = o % 16, m = o / 16;
-                if (m < rows && n0 + c < d) {
-                    float* p = P.h + (size_t)m * d + n0 + c;
-                    *p = __ldcg(p) + (red[c * MT + m] + __ldg(P.bdown + n0 + c));
-                }
-            }
-            __syncthreads();
-        }
-        w0 = prefetch_next(DT_PHASE_DOWN);
-        if (P.phases & DT_PHASE_QKV) ok = dt_grid_barrier(P, barriers++, s_abort);
-    }
-    // ---------------- next layer: LayerNorm, QKV projection, K/V rows into the cache ----------------
-    if (ok && (P.phases & DT_PHASE_QKV)) {
-        dt_layernorm<MT>(P, P.ln1w, P.ln1b, nbuf);
-        __syncthreads();
-        for (uint32_t n0 = blockIdx.x * 16; n0 < 3 * d; n0 += gridDim.x * 16) {
-            dt_gemm_tile<MT>(gqkv, rows, n0, wbuf, abuf, nbuf, npitch, red, w0);
-            w0 = false;
-            for (uint32_t o = threadIdx.x; o < 16u * MT; o += DT_THREADS) {
-                const uint32_t c = o % 16, m = o / 16, col = n0 + c;
-                if (m < rows && col < 3 * d) {
-                    const bf16 v = __float2bfloat16_rn(red[c * MT + m] + __ldg(P.bqkv + col));
-                    const uint32_t which = col / d, cc = col % d;
+            dt_gemm_tile<MT>(g, rows, n0, wbuf, abuf, abuf, npitch, red, w0);
+            w0 = 0;
+            if (mine) {
+                const float v = dt_reduced<MT>(red, m * DT_RED_PITCH + c) + b0;
+                if (ph == 1) {
+                    // packed columns [0, 16) are gate, [16, 32) the matching up columns -> 16 outputs
+                    const float up = dt_reduced<MT>(red, m * DT_RED_PITCH + 16 + c) + b1;
+                    P.ff[(size_t)m * f + n0 / 2 + c] = __float2bfloat16_rn(fast_silu(v) * up);
+                } else if (ph != 3) {
+                    P.h[(size_t)m * d + col] = hold + v;                   // h += projection + bias
+                } else {
+                    const bf16 vb = __float2bfloat16_rn(v);
+                    const uint32_t which = col / d, cc = col - which * d;
                     if (which == 0) {
-                        P.q[(size_t)m * d + cc] = v;
+                        P.q[(size_t)m * d + cc] = vb;
                     } else {
-                        const uint32_t pos = P.d_position ? P.d_position[(size_t)m * P.position_stride] : P.position;
                         const size_t crow = kv_row(P.paging, P.first_session + m, pos, P.capacity);
-                        (which == 1 ? P.k_cache : P.v_cache)[crow * d + cc] = v;
+                        (which == 1 ? P.k_cache : P.v_cache)[crow * d + cc] = vb;
                     }
                 }
             }
             __syncthreads();
+        }
+        // the next phase of this launch, if any: its weights and LayerNorm parameters do not depend on what the other
+        // CTAs are still writing, so they are requested before the barrier
+        uint32_t nx = ph + 1;
+        while (nx < 4 && !((P.phases >> nx) & 1u)) ++nx;
+        if (nx < 4) {
+            dt_grid_arrive(P);
+            const DtGemm gn = dt_phase_gemm(P, nx);
+            if (nx & 1u) {
+                dt_issue_ln(nx == 1 ? P.ln2w : P.ln1w, nx == 1 ? P.ln2b : P.ln1b, d, lnbuf);
+                ln_ready = true;
+            }
+            const uint32_t n0 = blockIdx.x * gn.cols;
+            if (n0 < gn.n) w0 = dt_prefetch_w(gn, n0, wbuf);
+            ok = dt_grid_wait(P, barriers++, s_abort);
         }
     }
     // ---------------- leave: the last CTA out re-arms the barrier words for the next launch ----------------
@@ -427,8 +473,8 @@ decode_tail_kernel(DtParams P) {
 
 template <int MT>
 size_t dt_smem_bytes() {
-    const size_t act = std::max((size_t)2 * MT * DT_PITCH, (size_t)MT * (DT_MAX_D + 8));
-    return (size_t)2 * DT_MAX_COLS * DT_PITCH * 2 + act * 2 + (size_t)DT_MAX_COLS * MT * 4 + 16;
+    return (size_t)DT_W_ROWS * DT_PITCH * 2 + (size_t)DT_A_STAGES * MT * DT_PITCH * 2 +
+           (size_t)(DT_WARPS / (MT / 16)) * MT * DT_RED_PITCH * 4 + 2 * DT_MAX_D * 4 + 16;
 }
 
 int dt_sm_count() {
@@ -474,7 +520,7 @@ int dt_launch(const DtParams& P, cudaStream_t stream) {
 uint64_t decode_tail_workspace_bytes() { return 256; }
 
 bool decode_tail_supported(uint32_t rows, uint32_t d, uint32_t f) {
-    return rows >= 1 && rows <= 64 && d % 16 == 0 && d <= DT_MAX_D && f % 16 == 0 && f >= 16;
+    return rows >= 1 && rows <= 32 && d % 16 == 0 && d <= DT_MAX_D && f % 16 == 0 && f >= 16;
 }
 
 int launch_decode_tail(const DecodeTailArgs& a, cudaStream_t stream) {
@@ -497,8 +543,7 @@ int launch_decode_tail(const DecodeTailArgs& a, cudaStream_t stream) {
     P.d_status = a.d_status;
     P.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
     if (a.rows <= 16) return dt_launch<16>(P, stream);
-    if (a.rows <= 32) return dt_launch<32>(P, stream);
-    return dt_launch<64>(P, stream);
+    return dt_launch<32>(P, stream);
 }
 
 }  // namespace tb
