@@ -382,6 +382,9 @@ decode_tail_kernel(DtParams P) {
     float* lnbuf = red + (size_t)KG * MT * DT_RED_PITCH;                           // [2][DT_MAX_D]
     int* s_abort = reinterpret_cast<int*>(lnbuf + 2 * DT_MAX_D);
     if (threadIdx.x == 0) *s_abort = 0;
+    // the next kernel of the stream may take each SM as this CTA leaves it, instead of after the grid has drained (it
+    // cannot start earlier: this CTA's shared memory leaves it no room, and it waits for this grid in its pdl_wait)
+    pdl_trigger();
     __syncthreads();
 
     const uint32_t d = P.d, f = P.f, rows = P.rows;
