@@ -115,7 +115,19 @@ struct GemmEpilogue {
     // launch; not to be shared by launches that may overlap): lets it divide K over several CTAs per tile.
     void* skinny_ws = nullptr;
     uint64_t skinny_ws_bytes = 0;
+    // Split-K for the in-place residual form (f32, residual == out) with few rows: the k-blocks are divided over
+    // `split_k` CTAs per tile (gemm_split_k() says how many), CTA s stores its partial sums (the first one with the
+    // bias) into split_partials[(s * split_rows + row) * ldc + col] and neither reads nor writes `out`; the caller adds
+    // them to the residual in a fixed order (launch_layernorm_fold).  split_rows: a multiple of 32, >= m.
+    float* split_partials = nullptr;
+    uint32_t split_k = 0;
+    uint32_t split_rows = 0;
 };
+
+// How many ways launch_gemm_bf16 can divide the k-blocks of a plain f32 residual GEMM with `m` rows (0: do not).  The
+// answer depends on n and k only (not on m, as long as m is small enough to split at all), so that the partial sums of
+// an output element, and with them its bits, are the same however the rows are batched.
+uint32_t gemm_split_k(const bf16* a, const bf16* bt, uint32_t m, uint32_t n, uint32_t k);
 
 // strict f32: out = a[m,k] . b (+bias)(act)(+residual), reference operation order.
 int launch_gemm_strict(const float* a, const float* b, void* out, uint32_t ldc, uint32_t m, uint32_t k,
@@ -196,6 +208,11 @@ int launch_bf16_to_f32(const bf16* in, float* out, uint64_t elems, cudaStream_t 
 int launch_transpose_f32_to_bf16(const float* in, bf16* out, uint32_t k, uint32_t n, cudaStream_t stream);
 int launch_transpose_f32_to_bf16_mapped(const float* in, bf16* out, uint32_t k, uint32_t n, uint32_t row0,
                                         uint32_t block, uint32_t block_stride, cudaStream_t stream);
+// h[row] += partials[0][row] + partials[1][row] + ... (in that order; partial s of row r at (s * split_rows + r) * width),
+// written back, then out = LayerNorm(h) as bf16: the other half of a split-K residual GEMM (GemmEpilogue::split_k).
+bool layernorm_fold_supported(uint32_t width);
+int launch_layernorm_fold(float* h, const float* partials, uint32_t split_k, uint32_t split_rows, const float* w, const float* b,
+                          void* out, uint32_t rows, uint32_t width, float eps, cudaStream_t stream);
 int launch_layernorm_strict(const float* x, const float* w, const float* b, float* out, uint32_t rows,
                             uint32_t width, float eps, cudaStream_t stream);
 int launch_swiglu_strict(const float* gate, const float* up, float* out, size_t n, cudaStream_t stream);

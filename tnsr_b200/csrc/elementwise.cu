@@ -143,6 +143,70 @@ layernorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ w, 
     }
 }
 
+// The same row-per-warp LayerNorm (bf16 out) on h + the partial sums of a split-K residual GEMM: the row is first
+// completed (h + p0 + p1 + ..., in that order) and written back, then normalised.
+__global__ void __launch_bounds__(128)
+layernorm_fold_kernel(float* __restrict__ h, const float* __restrict__ partials, uint32_t split_k, uint32_t split_rows,
+                      const float* __restrict__ w, const float* __restrict__ b, bf16* __restrict__ out, uint32_t rows,
+                      uint32_t width, float eps) {
+    pdl_wait();
+    pdl_trigger();
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    float4* xr = reinterpret_cast<float4*>(h + (size_t)row * width);
+    const uint32_t nvec = width >> 2;
+    float4 v[LN_MAX_VEC];
+#pragma unroll
+    for (int i = 0; i < LN_MAX_VEC; ++i) {
+        uint32_t c = lane + i * 32;
+        if (c < nvec) v[i] = xr[c];
+    }
+    for (uint32_t s = 0; s < split_k; ++s) {
+        const float4* pr = reinterpret_cast<const float4*>(partials + ((size_t)s * split_rows + row) * width);
+#pragma unroll
+        for (int i = 0; i < LN_MAX_VEC; ++i) {
+            uint32_t c = lane + i * 32;
+            if (c < nvec) {
+                const float4 p = pr[c];
+                v[i].x += p.x; v[i].y += p.y; v[i].z += p.z; v[i].w += p.w;
+            }
+        }
+    }
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < LN_MAX_VEC; ++i) {
+        uint32_t c = lane + i * 32;
+        if (c < nvec) {
+            xr[c] = v[i];
+            sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        }
+    }
+    const float mean = warp_sum(sum) / (float)width;
+    float sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < LN_MAX_VEC; ++i) {
+        uint32_t c = lane + i * 32;
+        if (c < nvec) {
+            v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+            sq += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+        }
+    }
+    const float inv = rsqrtf(warp_sum(sq) / (float)width + eps);
+    const float4* wr = reinterpret_cast<const float4*>(w);
+    const float4* br = reinterpret_cast<const float4*>(b);
+#pragma unroll
+    for (int i = 0; i < LN_MAX_VEC; ++i) {
+        uint32_t c = lane + i * 32;
+        if (c < nvec) {
+            float4 ww = wr[c], bb = br[c];
+            uint2 p = make_uint2(pack_bf16x2(v[i].x * inv * ww.x + bb.x, v[i].y * inv * ww.y + bb.y),
+                                 pack_bf16x2(v[i].z * inv * ww.z + bb.z, v[i].w * inv * ww.w + bb.w));
+            reinterpret_cast<uint2*>(out + (size_t)row * width)[c] = p;
+        }
+    }
+}
+
 // Any width: one block per row, three passes over global memory (L2-resident).
 template <bool OUT_BF16>
 __global__ void __launch_bounds__(256)
@@ -216,6 +280,24 @@ int launch_layernorm(const float* x, const float* w, const float* b, void* out, 
     }
     count_launch();
     return check_launch("layernorm");
+}
+
+bool layernorm_fold_supported(uint32_t width) { return width % 4 == 0 && width <= LN_MAX_VEC * 128; }
+
+int launch_layernorm_fold(float* h, const float* partials, uint32_t split_k, uint32_t split_rows, const float* w, const float* b,
+                          void* out, uint32_t rows, uint32_t width, float eps, cudaStream_t stream) {
+    if (rows == 0) return TNSR_B200_OK;
+    const bool aligned = (reinterpret_cast<uintptr_t>(h) % 16 == 0) && (reinterpret_cast<uintptr_t>(partials) % 16 == 0) &&
+                         (reinterpret_cast<uintptr_t>(w) % 16 == 0) && (reinterpret_cast<uintptr_t>(b) % 16 == 0) &&
+                         (reinterpret_cast<uintptr_t>(out) % 8 == 0);
+    if (!layernorm_fold_supported(width) || !aligned || split_k == 0 || split_rows < rows) {
+        set_thread_error("layernorm_fold: width, alignment or partial layout outside the kernel");
+        return TNSR_B200_ERR_UNSUPPORTED;
+    }
+    launch_kernel(layernorm_fold_kernel, dim3(ceil_div(rows, 4)), dim3(128), 0, stream, h, partials, split_k, split_rows, w, b,
+                  reinterpret_cast<bf16*>(out), rows, width, eps);
+    count_launch();
+    return check_launch("layernorm_fold");
 }
 
 // ---------------------------------------------------------------------------

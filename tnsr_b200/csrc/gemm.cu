@@ -215,7 +215,10 @@ struct TcParams {
     int* d_status;
     // 1: f32 output accumulated in place on the residual (out == residual): the epilogue hands each 32 x 32 block of
     // act(acc + bias) to a TMA reduce-add on `map_out` instead of reading, adding and storing the rows itself
+    // 2: split-K: tile t is the k-block range (t % split_k) of output tile t / split_k, and its blocks are STORED into
+    // the partial-sum buffer behind `map_out` at row (t % split_k) * split_rows + row (the first range adds the bias)
     uint32_t tma_reduce;
+    uint32_t split_k, split_rows;
     // 1: bf16 destinations are written with bulk tensor stores of 32-row blocks (map_out; map_k / map_v for the caches
     // of the QKV routing) instead of per-lane stores
     uint32_t tma_store;
@@ -283,18 +286,19 @@ __device__ __forceinline__ void load_residual_block(const EpiParams& P, uint32_t
 // columns outside the matrix are clipped by the tensor map.  One add per element, so the result is the same
 // residual + value an explicit read-add-store gives.
 __device__ __forceinline__ void epilogue_block_reduce(const EpiParams& P, const CUtensorMap* map_out, float* stage,
-                                                      uint32_t row0, uint32_t col0, const float* acc, uint32_t lane) {
+                                                      uint32_t row0, uint32_t col0, const float* acc, uint32_t lane,
+                                                      bool store = false, bool with_bias = true, uint32_t row_out = 0) {
     // the previous box of this warp must have been read out of the buffer
     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     __syncwarp();
     float4* row = reinterpret_cast<float4*>(stage) + lane * 8;
-    const bool bias_vec = P.ep.bias && (reinterpret_cast<uintptr_t>(P.ep.bias) & 15) == 0 && col0 + 32 <= P.n;
+    const bool bias_vec = with_bias && P.ep.bias && (reinterpret_cast<uintptr_t>(P.ep.bias) & 15) == 0 && col0 + 32 <= P.n;
 #pragma unroll
     for (int g = 0; g < 8; ++g) {
         float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
         if (bias_vec) {
             b = __ldg(reinterpret_cast<const float4*>(P.ep.bias + col0 + 4 * g));
-        } else if (P.ep.bias) {
+        } else if (with_bias && P.ep.bias) {
             const uint32_t c = col0 + 4 * g;
             b = make_float4(c < P.n ? P.ep.bias[c] : 0.f, c + 1 < P.n ? P.ep.bias[c + 1] : 0.f,
                             c + 2 < P.n ? P.ep.bias[c + 2] : 0.f, c + 3 < P.n ? P.ep.bias[c + 3] : 0.f);
@@ -306,8 +310,12 @@ __device__ __forceinline__ void epilogue_block_reduce(const EpiParams& P, const 
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
     if (lane == 0) {
-        asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
-                     ::"l"(map_out), "r"((int32_t)col0), "r"((int32_t)row0), "r"(smem_u32(stage)) : "memory");
+        if (store)   // split-K: a partial sum of its own, added to the residual later in a fixed order
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                         ::"l"(map_out), "r"((int32_t)col0), "r"((int32_t)row_out), "r"(smem_u32(stage)) : "memory");
+        else
+            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                         ::"l"(map_out), "r"((int32_t)col0), "r"((int32_t)row0), "r"(smem_u32(stage)) : "memory");
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
     }
 }
@@ -538,8 +546,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t num_tiles = prm.tiles_m * prm.tiles_n;
+    const uint32_t split = (MODE == GEMM_PLAIN && prm.tma_reduce == 2) ? prm.split_k : 1u;
+    const uint32_t num_tiles = prm.tiles_m * prm.tiles_n * split;
     const uint32_t num_kb = (prm.k + BK - 1) / BK;
+    const uint32_t kb_per = (num_kb + split - 1) / split;    // the host picks split so that no range is empty
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S::STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
@@ -566,8 +576,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             bool ok = true;
             for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
                 uint32_t tm, tn;
-                tile_coords(tile, prm.tiles_m, prm.tiles_n, tm, tn);
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                tile_coords(tile / split, prm.tiles_m, prm.tiles_n, tm, tn);
+                const uint32_t kb0 = (tile % split) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+                for (uint32_t kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, prm.wait_limit_ns)) { ok = false; break; }
                     uint8_t* sa = smem + stage * S::STAGE_BYTES;
                     const bool lost = prm.lose_kb && blockIdx.x == 0 && tile == blockIdx.x && kb + 1 == prm.lose_kb;
@@ -591,7 +602,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (!mbar_wait(acc_empty + ab, aphase ^ 1, abort_flag, prm.wait_limit_ns)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + ab * BN;
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                const uint32_t kb0 = (tile % split) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+                for (uint32_t kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(full_bar + stage, phase, abort_flag, prm.wait_limit_ns)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + stage * S::STAGE_BYTES);
@@ -600,7 +612,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (uint32_t kk = 0; kk < BK / UMMA_K; ++kk) {
                         // advancing K by 16 elements = 32 bytes inside the swizzle row: +2 in the address field
-                        umma_bf16(d_tmem, adesc + kk * 2, bdesc + kk * 2, idesc, (kb | kk) != 0);
+                        umma_bf16(d_tmem, adesc + kk * 2, bdesc + kk * 2, idesc, ((kb - kb0) | kk) != 0);
                     }
                     umma_commit(empty_bar + stage);  // stage reusable once these MMAs have read it
                     if (++stage == S::STAGES) { stage = 0; phase ^= 1; }
@@ -621,7 +633,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
             const uint32_t ab = it & 1, aphase = (it >> 1) & 1;
             uint32_t tm, tn;
-            tile_coords(tile, prm.tiles_m, prm.tiles_n, tm, tn);
+            tile_coords(tile / split, prm.tiles_m, prm.tiles_n, tm, tn);
+            const uint32_t ks = tile % split;
             const uint32_t row0 = tm * BM + quarter * 32;
             // f32 output with a residual: fetch this warp's first block of residual rows while the tile is still
             // being accumulated (the rows are final: only this warp rewrites them, after this read)
@@ -667,7 +680,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tmem_ld_wait();
                     const uint32_t col0 = tn * BN + c;
                     if (reduce) {
-                        if (row0 < prm.epi.m && col0 < prm.epi.n) epilogue_block_reduce(prm.epi, &map_out, stage, row0, col0, acc, lane);
+                        if (row0 < prm.epi.m && col0 < prm.epi.n)
+                            epilogue_block_reduce(prm.epi, &map_out, stage, row0, col0, acc, lane, prm.tma_reduce == 2, ks == 0,
+                                                  ks * prm.split_rows + row0);
                     } else if (prm.tma_store) {
                         if (row0 < prm.epi.m && col0 < prm.epi.n)
                             epilogue_block_store<MODE>(prm.epi, &map_out, &map_k, &map_v, stage, row0, col0, acc, lane, store_parity++, qkv_pos);
@@ -738,7 +753,7 @@ static int launch_tc_e(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
             return check_launch("gemm_tc attribute");
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    uint32_t tiles = prm.tiles_m * prm.tiles_n;
+    uint32_t tiles = prm.tiles_m * prm.tiles_n * (prm.tma_reduce == 2 ? prm.split_k : 1u);
     uint32_t grid = tiles < (uint32_t)sm_count() ? tiles : (uint32_t)sm_count();
     launch_kernel(gemm_tc_kernel<BN, MODE, EPI>, dim3(grid), dim3(S::THREADS), S::SMEM_BYTES, stream, ma, mb, mo[0], mo[1], mo[2], prm);
     count_launch();
@@ -801,11 +816,28 @@ static int launch_gemm_impl(const bf16* a, const bf16* bt, void* out, uint32_t l
         return launch_simple(a, lda, bt, P, k, mode, stream);
     };
     if (g_gemm_engine == 1 || !can_tc) {
+        if (ep.split_k > 1) {
+            set_thread_error("gemm: split-K needs the tcgen05 engine");
+            return TNSR_B200_ERR_INVALID_ARGUMENT;
+        }
         if (g_gemm_engine == 2) {
             set_thread_error("gemm: shape or alignment outside the tcgen05 engine (k % 8, 16-byte pointers)");
             return TNSR_B200_ERR_UNSUPPORTED;
         }
         return simple();
+    }
+    const bool split_req = ep.split_k > 1;
+    if (split_req) {
+        // the caller planned with gemm_split_k(): anything that engine cannot honour is an error, not a silent fallback,
+        // because the caller will add the partial sums it expects to find
+        const bool form = mode == GEMM_PLAIN && ep.out_dtype == TNSR_B200_F32 && ep.residual && ep.residual == out && ep.ldr == ldc &&
+                          ep.rows_per_session == 0 && !ep.round_bf16 && ep.activation == ACT_NONE && ldc % 4 == 0 && ep.split_partials &&
+                          reinterpret_cast<uintptr_t>(ep.split_partials) % 16 == 0 && ep.split_rows % 32 == 0 && ep.split_rows >= m &&
+                          ep.split_k == gemm_split_k(a, bt, m, n, k);
+        if (!form) {
+            set_thread_error("gemm: split-K asked for a form or a count the engine does not split");
+            return TNSR_B200_ERR_INVALID_ARGUMENT;
+        }
     }
     // A handful of rows against a large weight matrix: stream the weights with the operands swapped (gemm_skinny.cu)
     // when that engine can fill the GPU, i.e. with split-K scratch lent by the caller or with at least half as many
@@ -815,10 +847,10 @@ static int launch_gemm_impl(const bf16* a, const bf16* bt, void* out, uint32_t l
     // Engine 3 (tests) takes it for every eligible shape up to 64 rows.
     // Up to 16 rows against at least 4 M weight elements: one pass over the weights with no split-K (gemm_stream.cu).
     // Engine 4 (tests) takes it for every eligible shape.
-    if (mode == GEMM_PLAIN && m <= 16 && (g_gemm_engine == 0 || g_gemm_engine == 4) && gemm_stream_eligible(a, bt, m, n, k, ep) &&
+    if (!split_req && mode == GEMM_PLAIN && m <= 16 && (g_gemm_engine == 0 || g_gemm_engine == 4) && gemm_stream_eligible(a, bt, m, n, k, ep) &&
         ((uint64_t)n * k >= (4ull << 20) || g_gemm_engine == 4))
         return launch_gemm_stream(a, bt, out, ldc, m, n, k, ep, d_status, stream);
-    if (mode == GEMM_PLAIN && m <= 64 && g_gemm_engine != 1 && gemm_skinny_eligible(a, bt, m, n, k, ep)) {
+    if (!split_req && mode == GEMM_PLAIN && m <= 64 && g_gemm_engine != 1 && gemm_skinny_eligible(a, bt, m, n, k, ep)) {
         const bool pays = m <= 16 && (uint64_t)n * k >= (4ull << 20) &&
                           ((ep.skinny_ws && ep.skinny_ws_bytes >= gemm_skinny_workspace_bytes()) ||
                            2 * ceil_div(n, 128u) >= (uint32_t)sm_count());
@@ -830,10 +862,13 @@ static int launch_gemm_impl(const bf16* a, const bf16* bt, void* out, uint32_t l
     uint32_t bn = 256;
     while (bn > 64 && (uint64_t)tiles_m * ceil_div(n, bn) < (uint64_t)sm_count()) bn >>= 1;
     if (bn == 64 && 2ull * tiles_m * ceil_div(n, 64) <= (uint64_t)sm_count()) bn = 32;  // very few tiles: halve once more
+    if (split_req) bn = 32;   // many small tiles: every CTA takes in as little of both operands as possible
     TcParams prm;
     prm.k = k;
     prm.tiles_m = tiles_m;
     prm.tiles_n = ceil_div(n, bn);
+    prm.split_k = 1;
+    prm.split_rows = 0;
     prm.d_status = d_status;
     prm.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
     prm.lose_kb = t_lose_gemm_stage;   // one-shot test hook, see TcParams
@@ -852,7 +887,21 @@ static int launch_gemm_impl(const bf16* a, const bf16* bt, void* out, uint32_t l
     CUtensorMap mo[3] = {ma, ma, ma};   // output map, K-cache map, V-cache map; placeholders when unused
     prm.tma_reduce = 0;
     prm.tma_store = 0;
-    if (mode == GEMM_PLAIN && ep.out_dtype == TNSR_B200_F32 && ep.residual && ep.residual == out && ep.ldr == ldc &&
+    if (split_req) {
+        EncodeTiledFn fn = encode_fn();
+        cuuint64_t dims[2] = {n, (cuuint64_t)(ep.split_k - 1) * ep.split_rows + (uint64_t)ceil_div(m, 32u) * 32};
+        cuuint64_t strides[1] = {(cuuint64_t)ldc * 4};
+        cuuint32_t box[2] = {32, 32};
+        cuuint32_t estr[2] = {1, 1};
+        if (!fn || fn(&mo[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ep.split_partials, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+            set_thread_error("gemm: tensor map encoding failed");
+            return TNSR_B200_ERR_CUDA;
+        }
+        prm.tma_reduce = 2;
+        prm.split_k = ep.split_k;
+        prm.split_rows = ep.split_rows;
+    } else if (mode == GEMM_PLAIN && ep.out_dtype == TNSR_B200_F32 && ep.residual && ep.residual == out && ep.ldr == ldc &&
         ep.rows_per_session == 0 && !ep.round_bf16 && ldc % 4 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) {
         EncodeTiledFn fn = encode_fn();
         cuuint64_t dims[2] = {n, m};
@@ -911,6 +960,19 @@ static int launch_gemm_impl(const bf16* a, const bf16* bt, void* out, uint32_t l
         case 64: return launch_tc_mode<64>(ma, mb, mo, prm, mode, stream);
         default: return launch_tc_mode<32>(ma, mb, mo, prm, mode, stream);
     }
+}
+
+// Few rows against a narrow weight matrix (the attention-output and FFN-down projections of a decode step: 24 column
+// tiles at d 768) leave most SMs without a tile while each of the others takes in its whole K extent at one SM's rate;
+// dividing K puts the same bytes through four times as many SMs.
+uint32_t gemm_split_k(const bf16* a, const bf16* bt, uint32_t m, uint32_t n, uint32_t k) {
+    if (g_gemm_engine == 1 || !tc_eligible(a, k, bt, k)) return 0;
+    if (m == 0 || m > 256 || k % BK != 0) return 0;
+    if (m <= 64 && (uint64_t)n * k >= (4ull << 20)) return 0;   // the few-row engines take these shapes
+    const uint32_t num_kb = k / BK, tiles_n = ceil_div(n, 32u);
+    for (uint32_t s = 4; s >= 2; --s)
+        if (num_kb % s == 0 && num_kb / s >= 2 && tiles_n * s <= (uint32_t)sm_count()) return s;
+    return 0;
 }
 
 int launch_gemm_bf16(const bf16* a, const bf16* bt, void* out, uint32_t ldc, uint32_t m, uint32_t n,
