@@ -550,6 +550,39 @@ def test_divided_single_token_step_matches_the_undivided_one(parts):
     assert np.array_equal(caches_a[0].view(np.uint32), caches_b[0].view(np.uint32))
 
 
+def test_split_k_projections_are_deterministic_and_match_the_checker():
+    """Between 33 and 256 sessions the attention-output and FFN-down projections of a single-token step divide their K
+    extent over several CTAs per tile; the partial sums are added to the residual in a fixed order by the LayerNorm that
+    follows.  So two runs give the same bits (no atomics, no arrival order), a session's logits do not depend on how many
+    other sessions share the batch, and the result stays within the bf16-path tolerance of the CPU checker."""
+    from oracle import oracle
+    cfg = GptConfig(vocab_size=640, max_sequence_length=64, embed_dim=256, num_heads=4, feed_forward_dim=512,
+                    num_layers=3, layer_norm_epsilon=1e-5, activation="swiglu", weight_dtype="bf16")
+    arrays = normal_model_arrays(cfg, seed=57, std=0.05, bias_std=0.02)
+    ids = np.random.default_rng(58).integers(0, cfg.vocab_size, size=(72, 20)).astype(np.uint32)
+
+    def run(batch):
+        s = B200Session(cfg, batch, 48, logits_mode="last")
+        for i, a in enumerate(arrays):
+            s.refresh(i, a)
+        out = [s.decode_full(ids[:batch, :12], 0)[0]]
+        for t in range(12, 18):
+            out.append(s.decode_full(ids[:batch, t:t + 1], t)[0])
+        s.close()
+        return np.stack([o.reshape(batch, -1) for o in out])
+
+    a, b = run(72), run(72)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    fewer = run(40)                                   # another batch size on the same path: the same k-ranges per element
+    assert np.array_equal(fewer.view(np.uint32), a[:, :40].view(np.uint32))
+    ref = oracle.OracleModel(cfg.vocab_size, cfg.max_sequence_length, cfg.embed_dim, cfg.num_heads, cfg.feed_forward_dim,
+                             cfg.num_layers, cfg.layer_norm_epsilon, "swiglu")
+    ref.set_params([oracle.bf16_round_np(x) if x.ndim == 2 else x for x in arrays])
+    want = ref.forward(ids[:16, :18])
+    for t in range(12, 18):
+        assert rel_err(a[t - 11, :16], want[:, t]) <= 2e-2
+
+
 @pytest.mark.parametrize("weight_dtype", ["f32", "bf16"])
 def test_gpu_decoder_state_round_trips_through_the_archive(tmp_path, weight_dtype):
     """Serialised decoder state on the device: K/V rows read back through the C ABI, written as a tensor archive,
