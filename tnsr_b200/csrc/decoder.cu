@@ -109,6 +109,7 @@ struct tnsr_b200_decoder {
     // partial sums of the split-K projections of an undivided single-token step: [4][split_rows][d] f32
     float* split_ws = nullptr;
     uint32_t split_rows = 0;
+    uint32_t split_pending = 0;   // partial sums of the last layer's down projection, for the final LayerNorm to add
     uint64_t attn_ws_bytes = 0;
     cudaStream_t side_stream[3] = {nullptr, nullptr, nullptr};   // forked from and joined to `stream` by events
     cudaEvent_t ev_fork = nullptr, ev_join[3] = {nullptr, nullptr, nullptr};
@@ -472,6 +473,7 @@ int layers_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk
     const tnsr_b200_config& c = dec->cfg;
     const uint32_t d = c.embed_dim, f = c.feed_forward_dim, H = c.num_heads, hd = d / H;
     const uint32_t rows = ns * chunk;
+    dec->split_pending = 0;
     const size_t r0 = (size_t)s0 * chunk;                       // first activation row of the range
     const size_t cache0 = dec->paged ? 0 : (size_t)s0 * c.capacity * d;   // first cache element of the range
     KvPaging pg;                                                // paged: the pools are shared, the table is per session
@@ -530,17 +532,14 @@ int layers_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk
     }
     // Single-token steps of up to 256 rows: the two narrow projections (attention output, FFN down) divide their K extent
     // over several CTAs per tile; the partial sums are added to the residual, in a fixed order, by the LayerNorm that
-    // follows.  The last layer's down projection keeps the in-place form: what follows it is not in this function.
+    // follows (for the last layer's down projection that is the final LayerNorm in step_bf16: dec->split_pending).
     // Measured on B200, 12 layers of d 768, ms per step without / with: 64 sessions 0.840 / 0.789, 128 sessions 1.007 /
     // 0.954.  Not in a divided step (`lean`): there four times as many projection CTAs take the room on the SMs that
     // the other range's attention CTAs are waiting for (256 sessions in two ranges: 1.365 without, 1.549 with).
     const bool splitk = chunk == 1 && !lean && dec->split_ws && layernorm_fold_supported(d);
     float* part_ws = splitk ? dec->split_ws + (size_t)(s0 + 31) / 32 * 32 * d : nullptr;
     uint32_t pending = 0;                                       // partial sums of the previous layer's down projection
-    const size_t n_layers = dec->layers.size();
-    size_t li = 0;
     for (Layer& L : dec->layers) {
-        const bool last_layer = ++li == n_layers;
         bf16* kcache = (bf16*)L.kcache + cache0;
         bf16* vcache = (bf16*)L.vcache + cache0;
         if (pending)
@@ -598,11 +597,12 @@ int layers_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk
             RUN(dec, launch_gemm_bf16(n, (const bf16*)L.w_in, ff, f, rows, f, d, GEMM_PLAIN, ei, nullptr, dec->d_status, st));
         }
         GemmEpilogue ef; ef.bias = L.b_out; ef.residual = h; ef.ldr = d; ef.out_dtype = TNSR_B200_F32;
-        const uint32_t split_d = (splitk && !last_layer) ? gemm_split_k(ff, (const bf16*)L.w_out, rows, d, f) : 0;
+        const uint32_t split_d = splitk ? gemm_split_k(ff, (const bf16*)L.w_out, rows, d, f) : 0;
         if (split_d) { ef.split_k = split_d; ef.split_partials = part_ws; ef.split_rows = dec->split_rows; }
         RUN(dec, launch_gemm_bf16(ff, (const bf16*)L.w_out, h, d, rows, d, f, GEMM_PLAIN, ef, nullptr, dec->d_status, st));
         pending = split_d;
     }
+    dec->split_pending = pending;   // only an undivided step (one range: all rows) gets here with partial sums left
     return TNSR_B200_OK;
 }
 
@@ -662,7 +662,13 @@ int step_bf16(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t chunk, 
         RUN(dec, launch_gather_last_rows(dec->h, dec->hl, B, chunk, d, st));
         src = dec->hl;
     }
-    RUN(dec, launch_layernorm(src, dec->fnw, dec->fnb, n, logit_rows, d, c.layer_norm_epsilon, TNSR_B200_BF16, false, st));
+    const uint32_t pending = dec->split_pending;
+    dec->split_pending = 0;
+    if (pending && src == dec->h)   // split-K is for single-token steps, whose logit rows are all rows
+        RUN(dec, launch_layernorm_fold(dec->h, dec->split_ws, pending, dec->split_rows, dec->fnw, dec->fnb, n, logit_rows, d,
+                                       c.layer_norm_epsilon, st));
+    else
+        RUN(dec, launch_layernorm(src, dec->fnw, dec->fnb, n, logit_rows, d, c.layer_norm_epsilon, TNSR_B200_BF16, false, st));
     // the tied head: the token table [vocab, d] already is the K-major operand
     if (fused_ids) {
         RUN(dec, launch_lm_head_argmax(n, (const bf16*)dec->tok, logit_rows, c.vocab_size, d, dec->lm_candidates, fused_ids,
