@@ -54,6 +54,9 @@ extern thread_local KernelTimer* t_attention_timer;
 // stream is still draining.  Every kernel launched this way starts with pdl_wait(), which blocks until the
 // predecessor has completed and its writes are visible, so only launch latency overlaps, never data.
 extern thread_local bool t_pdl;
+// Set by the session around single-token steps: their LayerNorms have few rows and take the block-per-row kernel.  The
+// choice follows the kind of step, never the row count, so that a session's bits do not depend on the batch it is in.
+extern thread_local bool t_single_token_step;
 
 // Asks (once per kernel and device) for the largest shared-memory carve-out whenever `kernel` runs.  The split between
 // L1 and shared memory is a per-SM setting that can only change while the SM is empty, so two kernels can share an SM

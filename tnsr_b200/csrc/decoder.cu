@@ -690,10 +690,11 @@ int run_step_direct(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t c
     const bool fuse_ids = dec->bf16_path && c.logits_mode == TNSR_B200_LOGITS_NONE && d_argmax_out && dec->lm_candidates && !sampling;
     t_attention_timer = dec->profile_attention ? &dec->attention_timer : nullptr;
     t_pdl = dec->use_pdl && dec->bf16_path && chunk == 1;
+    t_single_token_step = chunk == 1;
     int rc = dec->bf16_path ? step_bf16(dec, d_tokens, chunk, position, d_position, logit_rows, fuse_ids ? d_argmax_out : nullptr)
                             : step_strict(dec, d_tokens, chunk, position, d_position, logit_rows);
     t_attention_timer = nullptr;
-    if (rc) { t_pdl = false; return rc; }
+    if (rc) { t_pdl = t_single_token_step = false; return rc; }
     if (d_argmax_out && !fuse_ids) {
         // last position of every session
         const float* base = dec->logits;
@@ -708,12 +709,12 @@ int run_step_direct(tnsr_b200_decoder* dec, const uint32_t* d_tokens, uint32_t c
                                                  (d_position ? 0 : position) + chunk, 0, dec->stream)
                            : launch_argmax(base, d_argmax_out, c.batch, c.vocab_size, stride, dec->stream);
         if (arc) {
-            t_pdl = false;
+            t_pdl = t_single_token_step = false;
             dec->error = thread_error();
             return arc;
         }
     }
-    t_pdl = false;
+    t_pdl = t_single_token_step = false;
     return TNSR_B200_OK;
 }
 

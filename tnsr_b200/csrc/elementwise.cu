@@ -5,6 +5,9 @@
 
 namespace tb {
 
+thread_local bool t_single_token_step = false;
+
+
 int launch_layernorm_strict(const float* x, const float* w, const float* b, float* out, uint32_t rows,
                             uint32_t width, float eps, cudaStream_t stream);
 
@@ -143,68 +146,60 @@ layernorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ w, 
     }
 }
 
-// The same row-per-warp LayerNorm (bf16 out) on h + the partial sums of a split-K residual GEMM: the row is first
-// completed (h + p0 + p1 + ..., in that order) and written back, then normalised.
-__global__ void __launch_bounds__(128)
+// LayerNorm (bf16 out) of h + the partial sums of a split-K residual GEMM: the row is first completed (h + p0 + p1 +
+// ..., in that order) and written back, then normalised (two passes, rsqrt of the biased variance).  One block per row,
+// one float4 per thread: the row, its partial rows and the scale and shift are up to seven independent loads per thread,
+// one L2 round trip in all (a warp per row with the partial rows fetched one after the other took 7.7 us per launch,
+// and with all 40 loads of a lane written ahead of their uses 15 us: they came out one by one).
+constexpr uint32_t LN_FOLD_MAX = 4;        // partial rows per call (gemm_split_k never asks for more)
+constexpr uint32_t LN_FOLD_THREADS = 256;  // float4 per row: widths up to 1024
+
+__device__ __forceinline__ float ln_fold_block_sum(float x, float* red) {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    x = warp_sum(x);
+    if (lane == 0) red[warp] = x;
+    __syncthreads();
+    float t = 0.0f;
+#pragma unroll
+    for (uint32_t i = 0; i < LN_FOLD_THREADS / 32; ++i) t += red[i];
+    __syncthreads();           // `red` is reused by the next sum
+    return t;
+}
+
+__global__ void __launch_bounds__(LN_FOLD_THREADS)
 layernorm_fold_kernel(float* __restrict__ h, const float* __restrict__ partials, uint32_t split_k, uint32_t split_rows,
                       const float* __restrict__ w, const float* __restrict__ b, bf16* __restrict__ out, uint32_t rows,
                       uint32_t width, float eps) {
+    __shared__ float red[LN_FOLD_THREADS / 32];
     pdl_wait();
     pdl_trigger();
-    const uint32_t lane = threadIdx.x & 31;
-    const uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= rows) return;
+    const uint32_t row = blockIdx.x, c = threadIdx.x;
+    const bool live = c < (width >> 2);
     float4* xr = reinterpret_cast<float4*>(h + (size_t)row * width);
-    const uint32_t nvec = width >> 2;
-    float4 v[LN_MAX_VEC];
-#pragma unroll
-    for (int i = 0; i < LN_MAX_VEC; ++i) {
-        uint32_t c = lane + i * 32;
-        if (c < nvec) v[i] = xr[c];
+    const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float4 v = zero, ww = zero, bb = zero, p[LN_FOLD_MAX];
+    if (live) {
+        v = xr[c];
+        ww = reinterpret_cast<const float4*>(w)[c];
+        bb = reinterpret_cast<const float4*>(b)[c];
     }
-    for (uint32_t s = 0; s < split_k; ++s) {
-        const float4* pr = reinterpret_cast<const float4*>(partials + ((size_t)s * split_rows + row) * width);
 #pragma unroll
-        for (int i = 0; i < LN_MAX_VEC; ++i) {
-            uint32_t c = lane + i * 32;
-            if (c < nvec) {
-                const float4 p = pr[c];
-                v[i].x += p.x; v[i].y += p.y; v[i].z += p.z; v[i].w += p.w;
-            }
-        }
-    }
-    float sum = 0.0f;
+    for (uint32_t s = 0; s < LN_FOLD_MAX; ++s)
+        p[s] = (live && s < split_k) ? reinterpret_cast<const float4*>(partials + ((size_t)s * split_rows + row) * width)[c] : zero;
 #pragma unroll
-    for (int i = 0; i < LN_MAX_VEC; ++i) {
-        uint32_t c = lane + i * 32;
-        if (c < nvec) {
-            xr[c] = v[i];
-            sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
-        }
+    for (uint32_t s = 0; s < LN_FOLD_MAX; ++s) {
+        if (s < split_k) { v.x += p[s].x; v.y += p[s].y; v.z += p[s].z; v.w += p[s].w; }
     }
-    const float mean = warp_sum(sum) / (float)width;
-    float sq = 0.0f;
-#pragma unroll
-    for (int i = 0; i < LN_MAX_VEC; ++i) {
-        uint32_t c = lane + i * 32;
-        if (c < nvec) {
-            v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
-            sq += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
-        }
-    }
-    const float inv = rsqrtf(warp_sum(sq) / (float)width + eps);
-    const float4* wr = reinterpret_cast<const float4*>(w);
-    const float4* br = reinterpret_cast<const float4*>(b);
-#pragma unroll
-    for (int i = 0; i < LN_MAX_VEC; ++i) {
-        uint32_t c = lane + i * 32;
-        if (c < nvec) {
-            float4 ww = wr[c], bb = br[c];
-            uint2 p = make_uint2(pack_bf16x2(v[i].x * inv * ww.x + bb.x, v[i].y * inv * ww.y + bb.y),
-                                 pack_bf16x2(v[i].z * inv * ww.z + bb.z, v[i].w * inv * ww.w + bb.w));
-            reinterpret_cast<uint2*>(out + (size_t)row * width)[c] = p;
-        }
-    }
+    if (live && split_k) xr[c] = v;
+    const float mean = ln_fold_block_sum(live ? (v.x + v.y) + (v.z + v.w) : 0.0f, red) / (float)width;
+    v.x -= mean; v.y -= mean; v.z -= mean; v.w -= mean;
+    const float sq = ln_fold_block_sum(live ? (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w) : 0.0f, red);
+    const float inv = rsqrtf(sq / (float)width + eps);
+    if (live)
+        reinterpret_cast<uint2*>(out + (size_t)row * width)[c] =
+            make_uint2(pack_bf16x2(v.x * inv * ww.x + bb.x, v.y * inv * ww.y + bb.y),
+                       pack_bf16x2(v.z * inv * ww.z + bb.z, v.w * inv * ww.w + bb.w));
+    (void)rows;
 }
 
 // Any width: one block per row, three passes over global memory (L2-resident).
@@ -266,6 +261,16 @@ int launch_layernorm(const float* x, const float* w, const float* b, void* out, 
     const bool vec_ok = width % 4 == 0 && width <= 32 * 4 * LN_MAX_VEC &&
                         (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (reinterpret_cast<uintptr_t>(w) % 16 == 0) &&
                         (reinterpret_cast<uintptr_t>(b) % 16 == 0) && (reinterpret_cast<uintptr_t>(out) % 16 == 0);
+    // Single-token steps (few rows): one block per row with every load of a thread issued at once (layernorm_fold_kernel
+    // with nothing to fold); the row-per-warp kernel fetches scale and shift only after the statistics, a second round
+    // trip that a launch of a few hundred rows has nothing to hide behind.  Many rows (prefill): row per warp, which
+    // runs at 0.94 of the HBM copy rate.
+    if (vec_ok && out_dtype == TNSR_B200_BF16 && t_single_token_step) {
+        launch_kernel(layernorm_fold_kernel, dim3(rows), dim3(LN_FOLD_THREADS), 0, stream, const_cast<float*>(x),
+                      static_cast<const float*>(nullptr), 0u, 0u, w, b, reinterpret_cast<bf16*>(out), rows, width, eps);
+        count_launch();
+        return check_launch("layernorm");
+    }
     if (vec_ok) {
         dim3 grid(ceil_div(rows, 4));
         if (out_dtype == TNSR_B200_BF16)
@@ -282,7 +287,7 @@ int launch_layernorm(const float* x, const float* w, const float* b, void* out, 
     return check_launch("layernorm");
 }
 
-bool layernorm_fold_supported(uint32_t width) { return width % 4 == 0 && width <= LN_MAX_VEC * 128; }
+bool layernorm_fold_supported(uint32_t width) { return width % 4 == 0 && width <= LN_FOLD_THREADS * 4; }
 
 int launch_layernorm_fold(float* h, const float* partials, uint32_t split_k, uint32_t split_rows, const float* w, const float* b,
                           void* out, uint32_t rows, uint32_t width, float eps, cudaStream_t stream) {
@@ -290,11 +295,11 @@ int launch_layernorm_fold(float* h, const float* partials, uint32_t split_k, uin
     const bool aligned = (reinterpret_cast<uintptr_t>(h) % 16 == 0) && (reinterpret_cast<uintptr_t>(partials) % 16 == 0) &&
                          (reinterpret_cast<uintptr_t>(w) % 16 == 0) && (reinterpret_cast<uintptr_t>(b) % 16 == 0) &&
                          (reinterpret_cast<uintptr_t>(out) % 8 == 0);
-    if (!layernorm_fold_supported(width) || !aligned || split_k == 0 || split_rows < rows) {
+    if (!layernorm_fold_supported(width) || !aligned || split_k == 0 || split_k > LN_FOLD_MAX || split_rows < rows) {
         set_thread_error("layernorm_fold: width, alignment or partial layout outside the kernel");
         return TNSR_B200_ERR_UNSUPPORTED;
     }
-    launch_kernel(layernorm_fold_kernel, dim3(ceil_div(rows, 4)), dim3(128), 0, stream, h, partials, split_k, split_rows, w, b,
+    launch_kernel(layernorm_fold_kernel, dim3(rows), dim3(LN_FOLD_THREADS), 0, stream, h, partials, split_k, split_rows, w, b,
                   reinterpret_cast<bf16*>(out), rows, width, eps);
     count_launch();
     return check_launch("layernorm_fold");
