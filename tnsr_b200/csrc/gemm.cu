@@ -648,6 +648,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     have_pre = true;
                 }
             }
+            // what the epilogue reads besides the accumulator (the tile's bias columns, the step's position) is asked into
+            // L1 while the tile is still being accumulated: a first-touch load after the wait is a whole L2 round trip
+            // on the critical path of a one-tile launch (with many tiles per CTA the loads hit anyway: not done there)
+            if (MODE != GEMM_ARGMAX && num_tiles <= gridDim.x) {
+                const float* bias0 = prm.epi.ep.bias ? prm.epi.ep.bias + (size_t)tn * BN : nullptr;
+                if (bias0 && lane * 32 < (uint32_t)BN && tn * BN + lane * 32 < prm.epi.n)
+                    asm volatile("prefetch.global.L1 [%0];" ::"l"(bias0 + lane * 32));
+                if (MODE == GEMM_QKV && lane == 31 && prm.epi.qkv.d_position)
+                    asm volatile("prefetch.global.L1 [%0];" ::"l"(prm.epi.qkv.d_position));
+            }
             if (!mbar_wait(acc_full + ab, aphase, abort_flag, prm.wait_limit_ns)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + ab * BN;
