@@ -578,17 +578,45 @@ decode_attention_kernel(DaParams P) {
                         const float* base = P.partial + ((size_t)mt.first_slot * P.heads + h) * (HD + 2);
                         const size_t step = (size_t)P.heads * (HD + 2);
                         float mx = -INFINITY;
-                        for (uint32_t i = 0; i < n_parts; ++i) mx = fmaxf(mx, __ldcg(base + i * step + HD));
-                        const float ms = (mx == -INFINITY) ? 0.0f : mx;
                         float lt = 0.0f, o[DPL];
 #pragma unroll
                         for (int e = 0; e < DPL; ++e) o[e] = 0.0f;
-                        for (uint32_t i = 0; i < n_parts; ++i) {
-                            const float* pp = base + i * step;
-                            const float w = ex2(__ldcg(pp + HD) - ms);
-                            lt = fmaf(__ldcg(pp + HD + 1), w, lt);
+                        constexpr uint32_t FEW = 4;
+                        if (n_parts <= FEW) {
+                            // the usual case (a session cut in two to four pieces): every value of every piece is
+                            // requested before the first is used, one L2 round trip instead of two dependent ones
+                            float pm[FEW], pl[FEW], pn[FEW][DPL];
 #pragma unroll
-                            for (int e = 0; e < DPL; ++e) o[e] = fmaf(__ldcg(pp + lane * DPL + e), w, o[e]);
+                            for (uint32_t i = 0; i < FEW; ++i) {
+                                const float* pp = base + i * step;
+                                const bool have = i < n_parts;
+                                pm[i] = have ? __ldcg(pp + HD) : -INFINITY;
+                                pl[i] = have ? __ldcg(pp + HD + 1) : 0.0f;
+#pragma unroll
+                                for (int e = 0; e < DPL; ++e) pn[i][e] = have ? __ldcg(pp + lane * DPL + e) : 0.0f;
+                            }
+#pragma unroll
+                            for (uint32_t i = 0; i < FEW; ++i) mx = fmaxf(mx, pm[i]);
+                            const float ms = (mx == -INFINITY) ? 0.0f : mx;
+#pragma unroll
+                            for (uint32_t i = 0; i < FEW; ++i) {
+                                if (i < n_parts) {
+                                    const float w = ex2(pm[i] - ms);
+                                    lt = fmaf(pl[i], w, lt);
+#pragma unroll
+                                    for (int e = 0; e < DPL; ++e) o[e] = fmaf(pn[i][e], w, o[e]);
+                                }
+                            }
+                        } else {
+                            for (uint32_t i = 0; i < n_parts; ++i) mx = fmaxf(mx, __ldcg(base + i * step + HD));
+                            const float ms = (mx == -INFINITY) ? 0.0f : mx;
+                            for (uint32_t i = 0; i < n_parts; ++i) {
+                                const float* pp = base + i * step;
+                                const float w = ex2(__ldcg(pp + HD) - ms);
+                                lt = fmaf(__ldcg(pp + HD + 1), w, lt);
+#pragma unroll
+                                for (int e = 0; e < DPL; ++e) o[e] = fmaf(__ldcg(pp + lane * DPL + e), w, o[e]);
+                            }
                         }
                         const float inv = 1.0f / lt;
                         bf16* orow = P.out + (size_t)mt.session * d + (size_t)h * HD + lane * DPL;
