@@ -576,8 +576,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             bool ok = true;
             for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
                 uint32_t tm, tn;
-                tile_coords(tile / split, prm.tiles_m, prm.tiles_n, tm, tn);
-                const uint32_t kb0 = (tile % split) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+                tile_coords(split == 1 ? tile : tile / split, prm.tiles_m, prm.tiles_n, tm, tn);
+                const uint32_t kb0 = split == 1 ? 0u : (tile % split) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
                 for (uint32_t kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, prm.wait_limit_ns)) { ok = false; break; }
                     uint8_t* sa = smem + stage * S::STAGE_BYTES;
@@ -602,7 +602,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (!mbar_wait(acc_empty + ab, aphase ^ 1, abort_flag, prm.wait_limit_ns)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + ab * BN;
-                const uint32_t kb0 = (tile % split) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+                const uint32_t kb0 = split == 1 ? 0u : (tile % split) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
                 for (uint32_t kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(full_bar + stage, phase, abort_flag, prm.wait_limit_ns)) { ok = false; break; }
                     tc_fence_after();
@@ -633,8 +633,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
             const uint32_t ab = it & 1, aphase = (it >> 1) & 1;
             uint32_t tm, tn;
-            tile_coords(tile / split, prm.tiles_m, prm.tiles_n, tm, tn);
-            const uint32_t ks = tile % split;
+            tile_coords(split == 1 ? tile : tile / split, prm.tiles_m, prm.tiles_n, tm, tn);
+            const uint32_t ks = split == 1 ? 0u : tile % split;
             const uint32_t row0 = tm * BM + quarter * 32;
             // f32 output with a residual: fetch this warp's first block of residual rows while the tile is still
             // being accumulated (the rows are final: only this warp rewrites them, after this read)
