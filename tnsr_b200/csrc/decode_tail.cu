@@ -183,51 +183,63 @@ __device__ __forceinline__ void dt_wait_pending(uint32_t n) {
 
 // LayerNorm of the residual rows into `nbuf` ([MT][d + 8] bf16): two passes over registers, rsqrt of the biased variance,
 // as layernorm_warp_kernel does.  Scale and shift come from shared memory: a few KB that every warp of every CTA wants
-// at the same moment sit in one or two L2 slices, and fetched per warp they cost 4 us.  A row belongs to TPR = 512 / MT consecutive lanes (16 or 32), thread p of them holding
-// the float4s p, p + TPR, ...; all loads of a thread are in flight together and the two sums are butterfly reductions
-// over the row's lanes.  Rows past `rows` become zeros.
+// at the same moment sit in one or two L2 slices, and fetched per warp they cost 4 us.  Warp w owns rows w and (MT 32)
+// w + 16, lane l the float4s l, l + 32, ... of both: all loads of a thread are in flight together, the two rows' sums are
+// independent butterfly reductions, and each scale / shift value read from shared memory serves both rows (with a row per
+// 16 lanes the output pass ran at the shared-memory load rate: 24 16-byte loads per thread).  Rows past `rows` become zeros.
 template <int MT>
 __device__ __forceinline__ void dt_layernorm(const DtParams& P, const float* lnbuf, bf16* nbuf) {
-    constexpr uint32_t TPR = DT_THREADS / MT;              // threads per row
-    constexpr int NV = DT_MAX_D / 4 / TPR;                 // float4 per thread: 16 or 8
-    const uint32_t r = threadIdx.x / TPR, p = threadIdx.x % TPR;
+    constexpr int RPW = MT / DT_WARPS;                     // rows per warp: 1 or 2
+    constexpr int NV = DT_MAX_D / 128;                     // float4 per lane and row
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t d = P.d, nvec = d >> 2;
-    const bool live = r < P.rows;
-    const float4* xr = reinterpret_cast<const float4*>(P.h + (size_t)r * d);
-    float4 v[NV];
+    float4 v[RPW][NV];
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        const uint32_t c = p + i * TPR;
-        v[i] = (live && c < nvec) ? __ldcg(xr + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    }
-    float sum = 0.0f;
+    for (int j = 0; j < RPW; ++j) {
+        const uint32_t r = warp + j * DT_WARPS;
+        const float4* xr = reinterpret_cast<const float4*>(P.h + (size_t)r * d);
 #pragma unroll
-    for (int i = 0; i < NV; ++i) sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
-#pragma unroll
-    for (uint32_t o = TPR / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    const float mean = sum / (float)d;
-    float sq = 0.0f;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        if (p + i * TPR < nvec) {
-            v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
-            sq += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+        for (int i = 0; i < NV; ++i) {
+            const uint32_t c = lane + i * 32;
+            v[j][i] = (r < P.rows && c < nvec) ? __ldcg(xr + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
     }
+    float inv[RPW];
 #pragma unroll
-    for (uint32_t o = TPR / 2; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-    const float inv = rsqrtf(sq / (float)d + P.eps);
+    for (int j = 0; j < RPW; ++j) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) sum += (v[j][i].x + v[j][i].y) + (v[j][i].z + v[j][i].w);
+#pragma unroll
+        for (uint32_t o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float mean = sum / (float)d;
+        float sq = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (lane + i * 32 < nvec) {
+                v[j][i].x -= mean; v[j][i].y -= mean; v[j][i].z -= mean; v[j][i].w -= mean;
+                sq += (v[j][i].x * v[j][i].x + v[j][i].y * v[j][i].y) + (v[j][i].z * v[j][i].z + v[j][i].w * v[j][i].w);
+            }
+        }
+#pragma unroll
+        for (uint32_t o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        inv[j] = rsqrtf(sq / (float)d + P.eps);
+    }
     const float4* wr = reinterpret_cast<const float4*>(lnbuf);               // scale, then shift: copies in shared memory
     const float4* br = reinterpret_cast<const float4*>(lnbuf + DT_MAX_D);
-    uint2* out = reinterpret_cast<uint2*>(nbuf + (size_t)r * (d + 8));
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-        const uint32_t c = p + i * TPR;
+        const uint32_t c = lane + i * 32;
         if (c < nvec) {
             const float4 ww = wr[c], bb = br[c];
-            out[c] = live ? make_uint2(pack_bf16x2(v[i].x * inv * ww.x + bb.x, v[i].y * inv * ww.y + bb.y),
-                                       pack_bf16x2(v[i].z * inv * ww.z + bb.z, v[i].w * inv * ww.w + bb.w))
-                          : make_uint2(0u, 0u);
+#pragma unroll
+            for (int j = 0; j < RPW; ++j) {
+                const uint32_t r = warp + j * DT_WARPS;
+                uint2* out = reinterpret_cast<uint2*>(nbuf + (size_t)r * (d + 8));
+                out[c] = r < P.rows ? make_uint2(pack_bf16x2(v[j][i].x * inv[j] * ww.x + bb.x, v[j][i].y * inv[j] * ww.y + bb.y),
+                                                 pack_bf16x2(v[j][i].z * inv[j] * ww.z + bb.z, v[j][i].w * inv[j] * ww.w + bb.w))
+                                    : make_uint2(0u, 0u);
+            }
         }
     }
 }
