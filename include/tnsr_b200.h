@@ -111,8 +111,9 @@ typedef struct tnsr_b200_config {
      * is divided into, each on its own stream so that one range's short
      * projection kernels run while another range streams its K/V rows (no
      * reference counterpart; results differ from the undivided step only by
-     * rounding).  0 = automatic (2 from 192 sessions up, else 1), 1 = never
-     * divide, 2..4 = that many parts. */
+     * rounding).  0 = automatic (from 192 sessions up ranges of about 128
+     * sessions, two to four of them; else 1), 1 = never divide, 2..4 = that
+     * many parts. */
     uint32_t step_parts;
     /* Paged K/V (no reference counterpart; the reference's cache is one
      * [batch, capacity, width] slab per tensor and its documentation lists ragged
