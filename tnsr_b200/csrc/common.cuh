@@ -55,7 +55,7 @@ extern thread_local KernelTimer* t_attention_timer;
 // predecessor has completed and its writes are visible, so only launch latency overlaps, never data.
 extern thread_local bool t_pdl;
 // Set by the session around single-token steps: their LayerNorms have few rows and take the block-per-row kernel.  The
-// choice follows the kind of step, never the row count, so that a session's bits do not depend on the batch it is in.
+// choice follows the kind of step, never the row count, so that a session's LayerNorm bits do not depend on the batch it is in.
 extern thread_local bool t_single_token_step;
 
 // Asks (once per kernel and device) for the largest shared-memory carve-out whenever `kernel` runs.  The split between
